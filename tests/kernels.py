@@ -1,0 +1,178 @@
+"""Triton kernels used by the tests, the smoke check and the benchmark.
+
+They are written in the style of the reference's python/examples (one program per
+block / row / tile, masked tails) and exercise exactly the lowered constructs the
+backend executes: structured block loads and stores, elementwise bodies,
+reductions and tt.dot.
+"""
+import triton
+import triton.language as tl
+
+
+@triton.jit
+def add_kernel(x_ptr, y_ptr, out_ptr, n_elements, BLOCK_SIZE: tl.constexpr):
+    pid = tl.program_id(axis=0)
+    offsets = pid * BLOCK_SIZE + tl.arange(0, BLOCK_SIZE)
+    mask = offsets < n_elements
+    x = tl.load(x_ptr + offsets, mask=mask)
+    y = tl.load(y_ptr + offsets, mask=mask)
+    tl.store(out_ptr + offsets, x + y, mask=mask)
+
+
+@triton.jit
+def softmax_kernel(out_ptr, in_ptr, in_row_stride, out_row_stride, n_cols, BLOCK_SIZE: tl.constexpr):
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK_SIZE)
+    x = tl.load(in_ptr + row * in_row_stride + cols, mask=cols < n_cols, other=-float('inf'))
+    z = x - tl.max(x, axis=0)
+    num = tl.exp(z)
+    den = tl.sum(num, axis=0)
+    tl.store(out_ptr + row * out_row_stride + cols, num / den, mask=cols < n_cols)
+
+
+@triton.jit
+def layernorm_fwd_kernel(X, Y, W, B, Mean, Rstd, stride, N, eps, BLOCK_SIZE: tl.constexpr):
+    row = tl.program_id(0)
+    Y += row * stride
+    X += row * stride
+    acc = tl.zeros([BLOCK_SIZE], dtype=tl.float32)
+    for off in range(0, N, BLOCK_SIZE):
+        cols = off + tl.arange(0, BLOCK_SIZE)
+        acc += tl.load(X + cols, mask=cols < N, other=0.).to(tl.float32)
+    mean = tl.sum(acc, axis=0) / N
+    acc2 = tl.zeros([BLOCK_SIZE], dtype=tl.float32)
+    for off in range(0, N, BLOCK_SIZE):
+        cols = off + tl.arange(0, BLOCK_SIZE)
+        x = tl.load(X + cols, mask=cols < N, other=0.).to(tl.float32)
+        x = tl.where(cols < N, x - mean, 0.)
+        acc2 += x * x
+    var = tl.sum(acc2, axis=0) / N
+    rstd = 1 / tl.sqrt(var + eps)
+    tl.store(Mean + row, mean)
+    tl.store(Rstd + row, rstd)
+    for off in range(0, N, BLOCK_SIZE):
+        cols = off + tl.arange(0, BLOCK_SIZE)
+        mask = cols < N
+        w = tl.load(W + cols, mask=mask)
+        b = tl.load(B + cols, mask=mask)
+        x = tl.load(X + cols, mask=mask, other=0.).to(tl.float32)
+        y = (x - mean) * rstd * w + b
+        tl.store(Y + cols, y, mask=mask)
+
+
+@triton.jit
+def matmul_kernel(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm,
+                  stride_cn, BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr, BLOCK_K: tl.constexpr,
+                  GROUP_M: tl.constexpr):
+    """C = A @ B with masked M/N/K tails and the grouped program order."""
+    pid = tl.program_id(axis=0)
+    num_pid_m = tl.cdiv(M, BLOCK_M)
+    num_pid_n = tl.cdiv(N, BLOCK_N)
+    num_pid_in_group = GROUP_M * num_pid_n
+    group_id = pid // num_pid_in_group
+    first_pid_m = group_id * GROUP_M
+    group_size_m = min(num_pid_m - first_pid_m, GROUP_M)
+    pid_m = first_pid_m + (pid % group_size_m)
+    pid_n = (pid % num_pid_in_group) // group_size_m
+    offs_m = pid_m * BLOCK_M + tl.arange(0, BLOCK_M)
+    offs_n = pid_n * BLOCK_N + tl.arange(0, BLOCK_N)
+    offs_k = tl.arange(0, BLOCK_K)
+    a_ptrs = a_ptr + (offs_m[:, None] * stride_am + offs_k[None, :] * stride_ak)
+    b_ptrs = b_ptr + (offs_k[:, None] * stride_bk + offs_n[None, :] * stride_bn)
+    acc = tl.zeros((BLOCK_M, BLOCK_N), dtype=tl.float32)
+    for k in range(0, tl.cdiv(K, BLOCK_K)):
+        a = tl.load(a_ptrs, mask=(offs_m[:, None] < M) & (offs_k[None, :] < K - k * BLOCK_K), other=0.0)
+        b = tl.load(b_ptrs, mask=(offs_k[:, None] < K - k * BLOCK_K) & (offs_n[None, :] < N), other=0.0)
+        acc = tl.dot(a, b, acc)
+        a_ptrs += BLOCK_K * stride_ak
+        b_ptrs += BLOCK_K * stride_bk
+    c = acc.to(c_ptr.dtype.element_ty)
+    c_ptrs = c_ptr + stride_cm * offs_m[:, None] + stride_cn * offs_n[None, :]
+    tl.store(c_ptrs, c, mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+
+@triton.jit
+def row_sum_kernel(x_ptr, out_ptr, M, N, stride_m, stride_n, BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr):
+    """out[i] = sum_j x[i*stride_m + j*stride_n] for j < N: ragged 2-D blocks, sum along axis 1."""
+    pid = tl.program_id(0)
+    offs_m = pid * BLOCK_M + tl.arange(0, BLOCK_M)
+    acc = tl.zeros([BLOCK_M], dtype=tl.float32)
+    for n0 in range(0, N, BLOCK_N):
+        offs_n = n0 + tl.arange(0, BLOCK_N)
+        ptrs = x_ptr + offs_m[:, None] * stride_m + offs_n[None, :] * stride_n
+        mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+        x = tl.load(ptrs, mask=mask, other=0.0)
+        acc += tl.sum(x, axis=1)
+    tl.store(out_ptr + offs_m, acc, mask=offs_m < M)
+
+
+@triton.jit
+def total_kernel(x_ptr, out_ptr, n, BLOCK: tl.constexpr):
+    """out[0] = sum of x[0:n]; a single program."""
+    acc = tl.zeros([BLOCK], dtype=tl.float32)
+    for off in range(0, n, BLOCK):
+        offs = off + tl.arange(0, BLOCK)
+        acc += tl.load(x_ptr + offs, mask=offs < n, other=0.0)
+    tl.store(out_ptr, tl.sum(acc, axis=0))
+
+
+# ---- small kernels covering the generic structured-access engine -----------------
+
+@triton.jit
+def affine_2d_kernel(x_ptr, out_ptr, stride_m, stride_n, M, N, BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr):
+    """out = 2*x + 1 on masked 2-D blocks (2-D program grid)."""
+    pm = tl.program_id(0)
+    pn = tl.program_id(1)
+    offs_m = pm * BLOCK_M + tl.arange(0, BLOCK_M)
+    offs_n = pn * BLOCK_N + tl.arange(0, BLOCK_N)
+    mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+    offs = offs_m[:, None] * stride_m + offs_n[None, :] * stride_n
+    x = tl.load(x_ptr + offs, mask=mask, other=0)
+    tl.store(out_ptr + offs, 2 * x + 1, mask=mask)
+
+
+@triton.jit
+def swap_kernel(x_ptr, y_ptr, BLOCK: tl.constexpr):
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    x = tl.load(x_ptr + offs)
+    y = tl.load(y_ptr + offs)
+    tl.store(x_ptr + offs, y)
+    tl.store(y_ptr + offs, x)
+
+
+@triton.jit
+def masked_other_kernel(in_ptr, out_ptr):
+    """Fully masked-off load: every lane takes `other`."""
+    offs = 100 + tl.arange(0, 4)
+    a = tl.load(in_ptr + offs, mask=offs < 4, other=-1)
+    tl.store(out_ptr + tl.arange(0, 4), a)
+
+
+@triton.jit
+def scalar_conj_mask_kernel(in_ptr, out_ptr, bound, value):
+    offs = tl.arange(0, 8)
+    a = tl.load(in_ptr + offs, mask=(value < 5) & (offs < bound), other=-1)
+    tl.store(out_ptr + offs, a)
+
+
+@triton.jit
+def splat_kernel(out_ptr, fill, n, BLOCK: tl.constexpr):
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    v = tl.full([BLOCK], 0, dtype=tl.float32) + fill
+    tl.store(out_ptr + offs, v, mask=offs < n)
+
+
+@triton.jit
+def gelu_bias_kernel(x_ptr, b_ptr, out_ptr, n_cols, BLOCK: tl.constexpr):
+    """Row-broadcast bias + tanh-GELU in fp16 I/O with fp32 math (2-D grid: row, column block)."""
+    row = tl.program_id(0)
+    cols = tl.program_id(1) * BLOCK + tl.arange(0, BLOCK)
+    m = cols < n_cols
+    x = tl.load(x_ptr + row * n_cols + cols, mask=m, other=0.0).to(tl.float32)
+    b = tl.load(b_ptr + cols, mask=m, other=0.0).to(tl.float32)
+    v = x + b
+    inner = 0.7978845608028654 * (v + 0.044715 * v * v * v)
+    e = tl.exp(2.0 * inner)
+    t = 1.0 - 2.0 / (e + 1.0)
+    y = 0.5 * v * (1.0 + t)
+    tl.store(out_ptr + row * n_cols + cols, y.to(tl.float16), mask=m)

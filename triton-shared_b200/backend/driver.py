@@ -1,0 +1,271 @@
+"""Triton driver plugin for the B200 execution library.
+
+Counterpart of the reference's ``backend/driver.py``: ``B200Driver`` has the
+method set of ``CPUDriver`` (lines 420-464 there), ``B200Utils`` that of
+``CPUUtils`` (380-417) and ``B200Launcher`` the call signature of ``CPULauncher``
+(361-376, 262-265).  Where the reference compiles a C++ launcher per kernel and
+runs the grid as a serial host loop (116-133), this launcher evaluates the
+kernel's launch plan for the call's arguments and enqueues CUDA kernels of
+libtsb200.so on the current stream.  Launches are asynchronous.
+
+Activation is the same one-line swap as for the reference
+(``python/examples/conftest.py:7``):
+
+    import triton, triton_shared_b200
+    triton.runtime.driver.set_active(triton_shared_b200.B200Driver())
+
+Multi-GPU: ``B200Driver(program_range=(lo, hi))`` or the context manager
+``driver.partition(rank, world)`` restricts every launch to a contiguous range
+of the linearised grid; num_programs stays the full grid.
+"""
+import contextlib
+import sys
+
+import numpy as np
+
+from triton.backends.compiler import GPUTarget
+from triton.backends.driver import DriverBase
+
+from . import plan as _plan
+from . import runtime as rt
+from .compiler import BACKEND_NAME
+
+
+def _ty_to_cpp(ty):
+    """Same table as the reference (backend/driver.py:41-64)."""
+    if ty[0] == '*':
+        return "void*"
+    if ty == "constexpr":
+        return "PyObject*"
+    return {
+        "i1": "int32_t", "i8": "int8_t", "i16": "int16_t", "i32": "int32_t", "i64": "int64_t",
+        "u1": "uint32_t", "u8": "uint8_t", "u16": "uint16_t", "u32": "uint32_t", "u64": "uint64_t",
+        "fp32": "float", "f32": "float", "fp64": "double",
+    }[ty]
+
+
+def partition_range(n_programs: int, rank: int, world: int):
+    """Contiguous share of the linearised grid owned by `rank` of `world` (balanced to within one program)."""
+    base, rem = divmod(n_programs, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+class _DeviceState:
+    """Per-device scratch owned by the host side (the C library never allocates)."""
+
+    def __init__(self):
+        self.scratch = None
+        self.tables = {}
+        self.status = None
+
+
+class LaunchArgs:
+    """What a plan needs from one launch: scalars, floats, pointers, device scratch."""
+
+    def __init__(self, launcher, values):
+        self.scalars, self.floats, self._ptrs = {}, {}, {}
+        self._dev = launcher._device_state()
+        for k, (ty, v) in enumerate(values):
+            if ty[0] == '*':
+                self._ptrs[k] = v
+            elif ty in ("fp32", "f32", "fp64"):
+                self.floats[k] = float(v)
+            else:
+                self.scalars[k] = int(v)
+
+    def pointer(self, k: int) -> int:
+        """Device address of pointer argument k: int, None (null) or an object with data_ptr()
+        (the reference's getPointer, backend/driver.py:140-171)."""
+        v = self._ptrs[k]
+        if v is None:
+            return 0
+        if isinstance(v, int):
+            return v
+        dp = getattr(v, "data_ptr", None)
+        if dp is None:
+            raise TypeError("Pointer argument must be either uint64 or have data_ptr method")
+        p = dp()
+        if not isinstance(p, int):
+            raise TypeError("data_ptr method of Pointer object must return 64-bit int")
+        return p
+
+    # -- device memory the kernels need beyond inputs and outputs (torch caching allocator)
+    def scratch(self, nbytes: int, stream) -> int:
+        import torch
+        d = self._dev
+        if d.scratch is None or d.scratch.numel() < nbytes:
+            d.scratch = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device="cuda")
+        return d.scratch.data_ptr()
+
+    def device_table(self, key, host: np.ndarray, stream) -> int:
+        import torch
+        d = self._dev
+        t = d.tables.get(key)
+        if t is None:
+            if len(d.tables) > 32:
+                d.tables.clear()
+            t = torch.from_numpy(np.ascontiguousarray(host)).to("cuda", non_blocking=False)
+            d.tables[key] = t
+        return t.data_ptr()
+
+    def status_word(self, stream) -> int:
+        import torch
+        d = self._dev
+        if d.status is None:
+            d.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        return d.status.data_ptr()
+
+
+class B200Launcher(object):
+
+    def __init__(self, src, metadata):
+        constants = src.constants if hasattr(src, "constants") else dict()
+        arg_names = src.fn.arg_names if hasattr(src, "fn") else list(src.signature.keys())
+        cst_key = lambda i: arg_names.index(i) if isinstance(i, str) else i
+        self.constants = {cst_key(key): value for key, value in constants.items()}
+        self.signature = {cst_key(key): value for key, value in src.signature.items()}
+        self.order = sorted(self.signature.keys())
+        self._states = {}
+
+    def _device_state(self):
+        import torch
+        dev = torch.cuda.current_device() if torch.cuda.is_available() else -1
+        st = self._states.get(dev)
+        if st is None:
+            st = self._states[dev] = _DeviceState()
+        return st
+
+    def __call__(self, gridX, gridY, gridZ, stream, function, kernel_metadata, launch_metadata,
+                 launch_enter_hook, launch_exit_hook, *args):
+        plan = function
+        if not isinstance(plan, _plan.Plan):
+            raise rt.TsbError("launch without a launch plan: the kernel was not compiled by the B200 backend")
+        if launch_enter_hook is not None:
+            launch_enter_hook(launch_metadata)
+        values = []
+        for idx in self.order:
+            ty = self.signature[idx]
+            if ty == "constexpr":
+                continue
+            values.append((ty, args[idx]))
+        grid = (int(gridX), int(gridY), int(gridZ))
+        total = grid[0] * grid[1] * grid[2]
+        if total > 0:
+            drv = B200Driver.current
+            lo, hi = (0, total) if drv is None else drv.range_for(total)
+            if hi > lo:
+                plan.launch(LaunchArgs(self, values), grid, lo, hi, stream or 0)
+        if launch_exit_hook is not None:
+            launch_exit_hook(launch_metadata)
+
+
+class B200Utils(object):
+
+    def __new__(cls):
+        if not hasattr(cls, "instance"):
+            cls.instance = super(B200Utils, cls).__new__(cls)
+        return cls.instance
+
+    @staticmethod
+    def get_device_properties(device):
+        import torch
+        if not torch.cuda.is_available():
+            return {"max_shared_mem": 232448, "multiprocessor_count": 148, "sm_clock_rate": None,
+                    "mem_clock_rate": None, "mem_bus_width": None}
+        pr = torch.cuda.get_device_properties(device)
+        return {"max_shared_mem": 232448, "multiprocessor_count": pr.multi_processor_count,
+                "sm_clock_rate": None, "mem_clock_rate": None, "mem_bus_width": None}
+
+    @staticmethod
+    def load_binary(name, kernel_obj, shared, device):
+        # same tuple as the reference (backend/driver.py:410-417); `function` is the parsed plan
+        rt.lib()  # fail now, loudly, if the CUDA library has not been built
+        return (None, _plan.plan_from_bytes(kernel_obj), None, None, sys.maxsize)
+
+
+class B200Driver(DriverBase):
+    current = None  # the driver whose program range launches honour
+
+    def __init__(self, program_range=None):
+        super().__init__()
+        self.utils = B200Utils()
+        self.launcher_cls = B200Launcher
+        self.binary_ext = "plan"
+        self._range = program_range  # None | (lo, hi) | ("part", rank, world)
+        B200Driver.current = self
+
+    # never auto-selected; only through triton.runtime.driver.set_active (reference: driver.py:428-432)
+    @staticmethod
+    def is_active():
+        return False
+
+    def range_for(self, total: int):
+        r = self._range
+        if r is None:
+            return 0, total
+        if r[0] == "part":
+            return partition_range(total, r[1], r[2])
+        return max(0, r[0]), min(total, r[1])
+
+    @contextlib.contextmanager
+    def partition(self, rank: int, world: int):
+        """Launches inside the block run only rank's contiguous share of each grid."""
+        old = self._range
+        self._range = ("part", rank, world)
+        try:
+            yield self
+        finally:
+            self._range = old
+
+    def get_benchmarker(self):
+        from triton.testing import do_bench
+        return do_bench
+
+    def get_device_capability(self, device=None):
+        return (10, 0)
+
+    def get_current_stream(self, device=None):
+        import torch
+        if not torch.cuda.is_available():
+            return 0
+        try:
+            from torch._C import _cuda_getCurrentRawStream
+            return _cuda_getCurrentRawStream(torch.cuda.current_device() if device is None else device)
+        except ImportError:
+            return torch.cuda.current_stream(device).cuda_stream
+
+    def get_current_device(self):
+        import torch
+        return torch.cuda.current_device() if torch.cuda.is_available() else 0
+
+    def set_current_device(self, device):
+        import torch
+        if torch.cuda.is_available():
+            torch.cuda.set_device(device)
+
+    def get_current_target(self):
+        # only B200Backend.supports_target accepts this name: neither Triton's own CUDA
+        # code generator nor any CPU path can be selected for kernels launched through this driver
+        return GPUTarget(BACKEND_NAME, 100, 32)
+
+    def get_active_torch_device(self):
+        import torch
+        return torch.device("cuda", self.get_current_device())
+
+    def get_device_interface(self):
+        import torch
+        return torch.cuda
+
+    def get_empty_cache_for_benchmark(self):
+        import torch
+        return torch.empty(int(256 * 1024 * 1024 // 4), dtype=torch.int, device="cuda")
+
+    def clear_cache(self, cache):
+        cache.zero_()
+
+    def assemble_tensormap_to_arg(self, tensormaps_info, args):
+        return args
+
+    def map_python_to_cpp_type(self, ty: str) -> str:
+        return _ty_to_cpp(ty)

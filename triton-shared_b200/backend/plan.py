@@ -1,0 +1,1096 @@
+"""Launch plans: map an analysed kernel (structured accesses + block dataflow graph)
+onto one of the pre-built CUDA kernel families of libtsb200.so and its parameters.
+
+Families (tried in this order):
+  gemm         scf.for {2 masked block loads, tt.dot} + truncf + masked store      -> tsb_gemm
+  layernorm    the three-loop LayerNorm forward of python/examples/test_layernorm.py -> tsb_layernorm_fwd
+  softmax      masked row load, max, exp, sum, div, masked row store              -> tsb_softmax_rows
+  reduce_rows  loop of masked 2-D block loads + sum(axis) + add, masked 1-D store  -> tsb_reduce_rows
+  reduce_all   loop of masked 1-D loads + add, full sum, scalar store              -> tsb_reduce_all
+  elementwise  any loop-free body of loads, elementwise ops and stores             -> tsb_elementwise
+A kernel that fits none raises UnsupportedTTIR at compile time; nothing falls
+back to another executor.
+
+A plan is JSON-serialisable (it is the "binary" of the Triton compile pipeline)
+and is evaluated against concrete arguments at launch.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import struct
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+
+from . import runtime as rt
+from .structured import (Access, Analyzer, Kernel, Loop, Node, Poly, TData, TMask, float_from_key)
+from .ttir import UnsupportedTTIR
+
+# --------------------------------------------------------------------------
+# small pattern matcher over the hash-consed block graph
+
+_COMMUTATIVE = {"addf", "mulf", "maxnumf", "minnumf", "maximumf", "minimumf", "addi", "muli", "andi", "ori", "xori"}
+
+
+def _is_ext(n: Node):
+    return n.op == "cast" and n.attr("kind") in ("extf", "fp_to_fp") and n.dtype == "f32"
+
+
+def _is_trunc(n: Node):
+    return n.op == "cast" and n.attr("kind") in ("truncf", "fp_to_fp")
+
+
+def const_value(n: Node) -> Optional[float]:
+    """Float value of a constant node, looking through splat/broadcast."""
+    while n.op in ("splat", "broadcast", "expand_dims"):
+        n = n.args[0]
+    if n.op == "const":
+        return float_from_key(n.attr("value"))
+    return None
+
+
+def match(n: Node, pat, b: Dict[str, Node]) -> bool:
+    """pat: ("$", name) | ("op", name, *pats) | ("ext", pat) | ("trunc", pat) | ("splat", pat)
+    | ("const", value) | ("reduce", comb, axis|None, pat) | ("attrs", pat, {k: v})"""
+    kind = pat[0]
+    if kind == "$":
+        if pat[1] in b:
+            return b[pat[1]] is n
+        b[pat[1]] = n
+        return True
+    if kind == "ext":
+        return match(n.args[0], pat[1], b) if _is_ext(n) else match(n, pat[1], b)
+    if kind == "trunc":
+        return match(n.args[0], pat[1], b) if _is_trunc(n) else match(n, pat[1], b)
+    if kind == "splat":
+        if n.op in ("splat", "broadcast"):
+            return match(n.args[0], pat, b) or match(n.args[0], pat[1], b)
+        return False
+    if kind == "const":
+        v = const_value(n)
+        return v is not None and (v == pat[1] or (v != v and pat[1] != pat[1]))
+    if kind == "reduce":
+        if n.op != "reduce" or n.attr("comb") != pat[1]:
+            return False
+        if pat[2] is not None and n.attr("axis") != pat[2]:
+            return False
+        return match(n.args[0], pat[3], b)
+    if kind == "attrs":
+        return all(n.attr(k) == v for k, v in pat[2].items()) and match(n, pat[1], b)
+    if kind == "op":
+        name, subs = pat[1], pat[2:]
+        if n.op != name or len(n.args) != len(subs):
+            return False
+        trial = dict(b)
+        if all(match(a, p, trial) for a, p in zip(n.args, subs)):
+            b.update(trial)
+            return True
+        if name in _COMMUTATIVE and len(subs) == 2:
+            trial = dict(b)
+            if match(n.args[0], subs[1], trial) and match(n.args[1], subs[0], trial):
+                b.update(trial)
+                return True
+        return False
+    raise AssertionError(pat)
+
+
+# --------------------------------------------------------------------------
+# JSON encoding of plan parameters
+
+def enc(o):
+    if isinstance(o, Poly):
+        return {"$poly": o.to_json()}
+    if isinstance(o, dict):
+        return {k: enc(v) for k, v in o.items()}
+    if isinstance(o, (list, tuple)):
+        return [enc(v) for v in o]
+    return o
+
+
+def dec(o):
+    if isinstance(o, dict):
+        if "$poly" in o:
+            return Poly.from_json(o["$poly"])
+        return {k: dec(v) for k, v in o.items()}
+    if isinstance(o, list):
+        return [dec(v) for v in o]
+    return o
+
+
+# --------------------------------------------------------------------------
+# launch-time helpers
+
+_PID = [("pid", 0), ("pid", 1), ("pid", 2)]
+
+
+class LaunchEnv:
+    """Concrete values of the symbols a plan's polynomials mention."""
+
+    def __init__(self, scalars: Dict[int, int], grid):
+        self.base = {("arg", i): int(v) for i, v in scalars.items()}
+        for a in range(3):
+            self.base[("np", a)] = int(grid[a])
+        self.grid = tuple(int(g) for g in grid)
+
+    def at(self, pid=(0, 0, 0), **its):
+        e = dict(self.base)
+        for a in range(3):
+            e[("pid", a)] = pid[a]
+        for k, v in its.items():
+            e[("it", int(k[2:]))] = v
+        return e
+
+    def affine_pid(self, p: Poly, its=None) -> Tuple[int, List[int]]:
+        """(value at pid 0, per-axis increments). The caller has checked affinity symbolically."""
+        its = its or {}
+        v0 = int(p.evaluate(self.at((0, 0, 0), **its)))
+        inc = []
+        for a in range(3):
+            if self.grid[a] <= 1:
+                inc.append(0)
+                continue
+            pid = [0, 0, 0]
+            pid[a] = 1
+            inc.append(int(p.evaluate(self.at(tuple(pid), **its))) - v0)
+        return v0, inc
+
+    def all_pids(self):
+        """Environment with numpy arrays for every program of the grid, linearised x fastest."""
+        gx, gy, gz = self.grid
+        lin = np.arange(gx * gy * gz, dtype=np.int64)
+        e = dict(self.base)
+        e[("pid", 0)] = lin % gx
+        e[("pid", 1)] = (lin // gx) % gy
+        e[("pid", 2)] = lin // (gx * gy)
+        return e
+
+
+def is_affine_in_pid(p: Poly) -> bool:
+    for m in p.terms:
+        deg = 0
+        for a in m:
+            if a[0] == "pid":
+                deg += 1
+            elif a[0] == "fn" and (a[2].depends_on(("pid",)) or a[3].depends_on(("pid",))):
+                return False
+        if deg > 1:
+            return False
+    return True
+
+
+def _float_bits(v: float, elem: str) -> int:
+    if elem == "f32":
+        return struct.unpack("<I", struct.pack("<f", v))[0]
+    if elem == "f16":
+        return int(np.asarray([v], dtype=np.float16).view(np.uint16)[0])
+    if elem == "bf16":
+        u = struct.unpack("<I", struct.pack("<f", v))[0]
+        if (u & 0x7fffffff) > 0x7f800000:
+            return (u >> 16) | 0x40
+        return ((u + 0x7fff + ((u >> 16) & 1)) >> 16) & 0xffff
+    raise UnsupportedTTIR(f"fill value of type {elem}")
+
+
+def other_bits(node: Optional[Node], elem: str) -> Optional[int]:
+    """Bit pattern of a load's `other` when it is a compile-time constant."""
+    if node is None:
+        return None
+    n = node
+    while n.op in ("splat", "broadcast", "expand_dims"):
+        n = n.args[0]
+    if n.op == "const":
+        return _float_bits(float_from_key(n.attr("value")), elem)
+    if n.op == "sint" and n.attr("poly").is_const:
+        return n.attr("poly").as_const & ((1 << (8 * rt.DTYPE_SIZE[elem])) - 1)
+    if n.op == "index" and n.attr("offset").is_const and all(s.is_zero for s in n.attr("strides")):
+        return n.attr("offset").as_const & ((1 << (8 * rt.DTYPE_SIZE[elem])) - 1)
+    if n.op == "cast":
+        # e.g. other=-1 written as an int and converted to the element type
+        inner = other_bits(n.args[0], n.args[0].dtype)
+        if inner is not None and n.args[0].dtype.startswith("i") and elem.startswith("i"):
+            return inner & ((1 << (8 * rt.DTYPE_SIZE[elem])) - 1)
+        if inner is not None and n.args[0].dtype.startswith("i") and elem in ("f32", "f16", "bf16"):
+            bits = 8 * rt.DTYPE_SIZE[n.args[0].dtype]
+            sv = inner - (1 << bits) if inner >= (1 << (bits - 1)) else inner
+            return _float_bits(float(sv), elem)
+    raise UnsupportedTTIR("masked load whose `other` is not a compile-time constant")
+
+
+class Plan:
+    family = "?"
+
+    def __init__(self, name: str, params: dict):
+        self.name = name
+        self.p = params
+
+    def to_bytes(self) -> bytes:
+        return json.dumps({"family": self.family, "name": self.name, "params": enc(self.p)}).encode()
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        raise NotImplementedError
+
+    def describe(self) -> str:
+        return f"{self.family}:{self.name}"
+
+
+def plan_from_bytes(b: bytes) -> Plan:
+    j = json.loads(b.decode())
+    cls = _FAMILIES[j["family"]]
+    return cls(j["name"], dec(j["params"]))
+
+
+# --------------------------------------------------------------------------
+# elementwise family
+
+def _mask_json(mask: Optional[TMask], shape):
+    if mask is None:
+        return None
+    return {"dims": [[[s, bnd] for (s, bnd) in d] for d in mask.dims], "conds": list(mask.scalar_conds)}
+
+
+class _EwLowering:
+    """Linearises the value graphs of all stores into VM ops over one iteration space."""
+
+    def __init__(self, kernel: Kernel, an: Analyzer, space: Tuple[int, ...]):
+        self.k, self.an, self.space = kernel, an, space
+        self.accs: List[dict] = []
+        self.ops: List[list] = []  # [opcode, dtype, dst, a, b, c, imm, imm2] with virtual registers
+        self.memo: Dict[tuple, int] = {}
+        self.nv = 0
+
+    def new(self):
+        self.nv += 1
+        return self.nv - 1
+
+    def acc_for(self, kind: str, elem: str, shape, dimmap, offset: Poly, strides, mask, other, arg=None):
+        """Access descriptor promoted to the iteration space; returns its index."""
+        r = len(self.space)
+        st = [Poly.const(0)] * r
+        mdims = [[] for _ in range(r)]
+        conds = list(mask["conds"]) if mask else []
+        for d, it_d in enumerate(dimmap):
+            if shape[d] > 1:
+                st[it_d] = strides[d]
+                if mask and mask["dims"][d]:
+                    mdims[it_d] = mdims[it_d] + list(mask["dims"][d])
+            elif mask and mask["dims"][d]:
+                # a masked unit dim gates the whole block: lane 0 valid iff start < bound
+                for s, bnd in mask["dims"][d]:
+                    conds.append(Poly.fn("cmp_slt", s, bnd))
+        for p in [offset] + st + [x for dd in mdims for sb in dd for x in sb] + conds:
+            if p.depends_on(("it", "carry")):
+                raise UnsupportedTTIR("elementwise body with a loop-dependent access")
+            if not is_affine_in_pid(p):
+                raise UnsupportedTTIR("access offset is not affine in program_id")
+        for p in st + [sb[1] for dd in mdims for sb in dd] + conds:
+            if p.depends_on(("pid",)):
+                raise UnsupportedTTIR("stride, mask bound or scalar mask condition depends on program_id")
+        if any(len(dd) > 1 for dd in mdims):
+            # several upper bounds on one dim: all must share the start; the bound is their minimum
+            for i, dd in enumerate(mdims):
+                if len(dd) > 1:
+                    if any(s != dd[0][0] for s, _ in dd):
+                        raise UnsupportedTTIR("conjunction of masks with different starts on one dim")
+                    bnd = dd[0][1]
+                    for _, b2 in dd[1:]:
+                        bnd = Poly.fn("minsi", bnd, b2)
+                    mdims[i] = [(dd[0][0], bnd)]
+        desc = {"kind": kind, "elem": elem, "arg": arg, "offset": offset, "strides": st,
+                "mask": [dd[0] if dd else None for dd in mdims], "conds": conds, "other": other}
+        self.accs.append(desc)
+        return len(self.accs) - 1
+
+    def emit(self, opcode, dtype, a=0, b=0, c=0, imm=0, imm2=0):
+        dst = self.new()
+        self.ops.append([opcode, dtype, dst, a, b, c, imm, imm2])
+        return dst
+
+    def value(self, n: Node, dimmap: Tuple[int, ...]) -> int:
+        key = (n.id, dimmap)
+        if key in self.memo:
+            return self.memo[key]
+        v = self._value(n, dimmap)
+        self.memo[key] = v
+        return v
+
+    def _value(self, n: Node, dimmap):
+        op = n.op
+        if op == "load":
+            acc: Access = self.an.access_of(n)
+            if acc.wrapped:
+                raise UnsupportedTTIR("wrap-around (modulo) block load in an elementwise body")
+            ob = other_bits(acc.other, acc.elem)
+            ai = self.acc_for("load", acc.elem, acc.shape, dimmap, acc.offset, acc.strides,
+                              _mask_json(acc.mask, acc.shape), ob, acc.arg)
+            return self.emit("load", acc.elem, a=ai)
+        if op in ("splat",):
+            return self.value(n.args[0], ())
+        if op == "broadcast":
+            return self.value(n.args[0], dimmap)
+        if op == "expand_dims":
+            ax = n.attr("axis")
+            return self.value(n.args[0], dimmap[:ax] + dimmap[ax + 1:])
+        if op == "const":
+            v = float_from_key(n.attr("value"))
+            bits = struct.unpack("<I", struct.pack("<f", v))[0]
+            return self.emit("const", n.dtype, imm=bits)
+        if op == "sint":
+            p = n.attr("poly")
+            if p.depends_on(("pid", "it", "carry")):
+                ai = self.acc_for("index", n.dtype, (), (), p, (), None, None)
+                return self.emit("load", n.dtype, a=ai)
+            return self.emit("const", n.dtype, imm=("poly", p))
+        if op == "farg":
+            return self.emit("const", n.dtype, imm=("farg", n.attr("arg")))
+        if op == "index":
+            ai = self.acc_for("index", n.dtype, n.shape, dimmap, n.attr("offset"), n.attr("strides"), None, None)
+            return self.emit("load", n.dtype, a=ai)
+        if op == "maskval":
+            m = {"dims": [[list(sb) for sb in d] for d in n.attr("dims")], "conds": list(n.attr("conds"))}
+            ai = self.acc_for("maskprobe", "i1", n.shape, dimmap, Poly.const(0), [Poly.const(0)] * len(n.shape), m, None)
+            return self.emit("load", "i1", a=ai)
+        if op in ("addf", "subf", "mulf", "divf", "maxnumf", "minnumf", "maximumf", "minimumf", "remf",
+                  "addi", "subi", "muli", "divsi", "remsi", "divui", "remui", "minsi", "maxsi", "minui",
+                  "maxui", "andi", "ori", "xori", "shli", "shrsi", "shrui"):
+            a = self.value(n.args[0], dimmap)
+            b = self.value(n.args[1], dimmap)
+            return self.emit(op, n.dtype, a=a, b=b)
+        if op in ("exp", "exp2", "log", "log2", "sqrt", "rsqrt", "sin", "cos", "tanh", "erf", "absf",
+                  "negf", "floor", "ceil", "absi"):
+            return self.emit(op, n.dtype, a=self.value(n.args[0], dimmap))
+        if op == "fma":
+            a, b, c = (self.value(x, dimmap) for x in n.args)
+            return self.emit("fma", n.dtype, a=a, b=b, c=c)
+        if op == "cmpf":
+            a, b = self.value(n.args[0], dimmap), self.value(n.args[1], dimmap)
+            return self.emit("cmpf", n.args[0].dtype, a=a, b=b, imm=rt.CMPF[n.attr("pred")])
+        if op == "cmpi":
+            a, b = self.value(n.args[0], dimmap), self.value(n.args[1], dimmap)
+            return self.emit("cmpi", n.args[0].dtype, a=a, b=b, imm=rt.CMPI[n.attr("pred")])
+        if op == "select":
+            c, a, b = (self.value(x, dimmap) for x in n.args)
+            return self.emit("select", n.dtype, a=c, b=a, c=b)
+        if op == "cast":
+            kind = n.attr("kind")
+            src = n.args[0]
+            a = self.value(src, dimmap)
+            if kind == "bitcast":
+                if rt.DTYPE_SIZE.get(src.dtype) != 4 or rt.DTYPE_SIZE.get(n.dtype) != 4:
+                    raise UnsupportedTTIR("bitcast between types that are not 32 bits wide")
+                return self.emit("bitcast", n.dtype, a=a)
+            mode = 1 if kind in ("uitofp", "fptoui", "extui") else 0
+            return self.emit("cast", n.dtype, a=a, imm=rt.DTYPES[src.dtype], imm2=mode)
+        raise UnsupportedTTIR(f"operation {op} has no elementwise lowering")
+
+    def lower(self, stores: List[Access]):
+        for acc in stores:
+            shape = acc.shape
+            dimmap = tuple(range(len(self.space) - len(shape), len(self.space)))
+            v = self.value(acc.value, dimmap)
+            ai = self.acc_for("store", acc.elem, shape, dimmap, acc.offset, acc.strides,
+                              _mask_json(acc.mask, shape), None, acc.arg)
+            self.ops.append(["store", acc.elem, -1, ai, v, 0, 0, 0])
+        return self.allocate()
+
+    def allocate(self):
+        """Hoist loads, then map virtual registers onto TSB_NUM_REGS physical ones."""
+        loads = [o for o in self.ops if o[0] == "load"]
+        rest = [o for o in self.ops if o[0] != "load"]
+        ops = loads + rest
+        last_use: Dict[int, int] = {}
+        for i, o in enumerate(ops):
+            for r in _reads(o):
+                last_use[r] = i
+        free = list(range(rt.TSB_NUM_REGS - 1, -1, -1))
+        phys: Dict[int, int] = {}
+        out = []
+        for i, o in enumerate(ops):
+            o = list(o)
+            reads = _reads(o)
+            mapped = {r: phys[r] for r in reads}
+            for r in set(reads):
+                if last_use[r] == i:
+                    free.append(phys.pop(r))
+            if o[0] != "store":
+                if not free:
+                    raise UnsupportedTTIR(f"elementwise body needs more than {rt.TSB_NUM_REGS} live block values")
+                if o[2] not in last_use:
+                    dst_phys = free[-1]  # dead value: still needs a slot for this op
+                else:
+                    dst_phys = free.pop()
+                    phys[o[2]] = dst_phys
+                o[2] = dst_phys
+            _remap(o, mapped)
+            out.append(o)
+        if len(out) > rt.TSB_MAX_OPS:
+            raise UnsupportedTTIR(f"elementwise body of {len(out)} ops exceeds {rt.TSB_MAX_OPS}")
+        if len(self.accs) > rt.TSB_MAX_ACCESSES:
+            raise UnsupportedTTIR(f"{len(self.accs)} block accesses exceed {rt.TSB_MAX_ACCESSES}")
+        return out
+
+
+def _reads(o):
+    opc = o[0]
+    if opc in ("load", "const", "iota"):
+        return []
+    if opc == "store":
+        return [o[4]]
+    if opc in ("select", "fma"):
+        return [o[3], o[4], o[5]]
+    if opc in ("exp", "exp2", "log", "log2", "sqrt", "rsqrt", "sin", "cos", "tanh", "erf", "absf", "negf",
+               "floor", "ceil", "absi", "cast", "bitcast", "mov"):
+        return [o[3]]
+    return [o[3], o[4]]
+
+
+def _remap(o, mapped):
+    opc = o[0]
+    if opc == "store":
+        o[4] = mapped[o[4]]
+        return
+    rs = _reads(o)
+    if len(rs) >= 1:
+        o[3] = mapped[o[3]]
+    if len(rs) >= 2:
+        o[4] = mapped[o[4]]
+    if len(rs) >= 3:
+        o[5] = mapped[o[5]]
+
+
+class ElementwisePlan(Plan):
+    family = "elementwise"
+
+    @staticmethod
+    def build(kernel: Kernel, an: Analyzer) -> "ElementwisePlan":
+        stores = []
+        for kind, e in kernel.effects:
+            if kind != "store":
+                raise UnsupportedTTIR("elementwise family: kernel contains a loop")
+            stores.append(e)
+        if not stores:
+            raise UnsupportedTTIR("kernel stores nothing")
+        shapes = {s.shape for s in stores}
+        full = max(shapes, key=lambda s: (len(s), int(np.prod(s)) if s else 1))
+        rank = max(len(full), 1)
+        space = tuple([1] * (rank - len(full)) + list(full))
+        for s in shapes:
+            pad = tuple([1] * (rank - len(s)) + list(s))
+            if any(a != b and a != 1 for a, b in zip(pad, space)):
+                raise UnsupportedTTIR("stores of different block shapes in one kernel")
+        if rank > rt.TSB_MAX_RANK:
+            raise UnsupportedTTIR(f"blocks of rank {rank} (max {rt.TSB_MAX_RANK})")
+        for s in stores:
+            if s.wrapped:
+                raise UnsupportedTTIR("wrap-around (modulo) block store")
+        low = _EwLowering(kernel, an, space)
+        ops = low.lower(stores)
+        return ElementwisePlan(kernel.name, {"space": list(space), "accs": low.accs, "ops": ops,
+                                             "ptr_args": sorted({s.arg for s in stores})})
+
+    def __init__(self, name, params):
+        super().__init__(name, params)
+        self._cache = {}
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        scal_key = tuple((i, v) for i, v in sorted(args.scalars.items())) + tuple(grid) + \
+            tuple(sorted(args.floats.items()))
+        ent = self._cache.get(scal_key)
+        if ent is None:
+            ent = self._evaluate(args, grid)
+            if len(self._cache) > 64:
+                self._cache.clear()
+            self._cache[scal_key] = ent
+        accs, ops, arg_of = ent
+        for a, i in zip(accs, arg_of):
+            if i is not None:
+                a.base = args.pointer(i)
+        g = (ctypes.c_int32 * 3)(*grid)
+        rt.check(rt.lib().tsb_elementwise(accs, len(accs), ops, len(ops), g, pid_lo, pid_hi, stream),
+                 f"tsb_elementwise[{self.name}]")
+
+    def _evaluate(self, args, grid):
+        p = self.p
+        env = LaunchEnv(args.scalars, grid)
+        space = p["space"]
+        rank = len(space)
+        n = len(p["accs"])
+        accs = (rt.Access * n)()
+        arg_of = []
+        for ai, d in enumerate(p["accs"]):
+            a = accs[ai]
+            kind = d["kind"]
+            a.dtype = rt.DTYPES[d["elem"]]
+            a.rank = rank
+            a.is_store = {"load": 0, "store": 1, "maskprobe": 2, "index": 3}[kind]
+            off0, inc = env.affine_pid(d["offset"])
+            a.offset0 = off0
+            for k in range(3):
+                a.offset_pid[k] = inc[k]
+            gate = all(int(c.evaluate(env.at())) != 0 for c in d["conds"])
+            for k in range(rank):
+                a.sizes[k] = space[k]
+                a.strides[k] = int(d["strides"][k].evaluate(env.at()))
+                m = d["mask"][k]
+                if m is not None:
+                    a.masked[k] = 1
+                    s0, sinc = env.affine_pid(m[0])
+                    a.mask_start0[k] = s0
+                    for j in range(3):
+                        a.mask_start_pid[k][j] = sinc[j]
+                    a.mask_bound[k] = int(m[1].evaluate(env.at()))
+            if not gate:
+                # a false scalar conjunct empties the block (MaskAnalysis.cpp:224-267)
+                a.masked[0] = 1
+                a.mask_bound[0] = -(1 << 62)
+            if d["other"] is not None:
+                a.has_other = 1
+                a.other_bits = d["other"]
+            arg_of.append(None)
+        ops = (rt.Op * len(p["ops"]))()
+        for k, o in enumerate(p["ops"]):
+            opc, dt, dst, ra, rb, rc, imm, imm2 = o
+            x = ops[k]
+            x.opcode = rt.OPCODES[opc]
+            x.type = rt.DTYPES[dt]
+            x.dst, x.a, x.b, x.c = max(dst, 0), ra, rb, rc
+            if isinstance(imm, (list, tuple)):
+                if imm[0] == "poly":
+                    v = int(imm[1].evaluate(env.at()))
+                    x.imm = v & 0xffffffff
+                else:  # farg
+                    x.imm = struct.unpack("<I", struct.pack("<f", float(args.floats[imm[1]])))[0]
+            else:
+                x.imm = imm
+            x.imm2 = imm2
+        # which kernel pointer argument backs each access
+        for ai, d in enumerate(p["accs"]):
+            arg_of[ai] = d.get("arg")
+        return accs, ops, arg_of
+
+
+# --------------------------------------------------------------------------
+# row softmax
+
+def _row_access(acc: Access, what: str):
+    """Checks a 1-D unit-stride row access whose offset is row*stride + const; returns (stride Poly per pid0, mask)."""
+    if len(acc.shape) != 1 or acc.wrapped:
+        raise UnsupportedTTIR(f"{what}: not a 1-D block")
+    if acc.strides[0] != Poly.const(1):
+        raise UnsupportedTTIR(f"{what}: row is not unit-stride")
+    if not is_affine_in_pid(acc.offset):
+        raise UnsupportedTTIR(f"{what}: offset not affine in program_id")
+
+
+def _single_bound(mask: Optional[TMask], d: int):
+    if mask is None or not mask.dims[d]:
+        return None
+    if len(mask.dims[d]) != 1 or mask.scalar_conds:
+        raise UnsupportedTTIR("compound mask on a row access")
+    return mask.dims[d][0]
+
+
+class SoftmaxPlan(Plan):
+    family = "softmax"
+
+    @staticmethod
+    def build(kernel: Kernel, an: Analyzer) -> "SoftmaxPlan":
+        if len(kernel.effects) != 1 or kernel.effects[0][0] != "store":
+            raise UnsupportedTTIR("softmax family: expects exactly one store")
+        st: Access = kernel.effects[0][1]
+        b: Dict[str, Node] = {}
+        num = ("op", "exp", ("op", "subf", ("$", "x"), ("splat", ("reduce", "maxnumf", 0, ("$", "x")))))
+        num_alt = ("op", "exp", ("op", "subf", ("$", "x"), ("splat", ("reduce", "maximumf", 0, ("$", "x")))))
+        ok = False
+        for nm in (num, num_alt):
+            b = {}
+            if match(st.value, ("op", "divf", nm, ("splat", ("reduce", "addf", 0, nm))), b):
+                ok = True
+                break
+        if not ok or b["x"].op != "load":
+            raise UnsupportedTTIR("softmax family: body is not exp(x-max(x))/sum(exp(x-max(x)))")
+        ld = an.access_of(b["x"])
+        _row_access(ld, "softmax load")
+        _row_access(st, "softmax store")
+        if ld.elem != "f32" or st.elem != "f32":
+            raise UnsupportedTTIR("softmax family: only fp32 rows")
+        lb, sb = _single_bound(ld.mask, 0), _single_bound(st.mask, 0)
+        block = ld.shape[0]
+        if lb is not None:
+            if not lb[0].is_zero:
+                raise UnsupportedTTIR("softmax family: column mask does not start at 0")
+            ob = other_bits(ld.other, "f32") if ld.other is not None else None
+            if ob != 0xff800000:
+                raise UnsupportedTTIR("softmax family: masked row load needs other=-inf")
+        if (lb is None) != (sb is None) or (lb is not None and (lb[1] != sb[1] or not sb[0].is_zero)):
+            raise UnsupportedTTIR("softmax family: load and store masks differ")
+        n_cols = lb[1] if lb is not None else Poly.const(block)
+        if n_cols.depends_on(("pid",)):
+            raise UnsupportedTTIR("softmax family: n_cols depends on program_id")
+        return SoftmaxPlan(kernel.name, {"in_arg": ld.arg, "out_arg": st.arg, "in_off": ld.offset,
+                                         "out_off": st.offset, "n_cols": n_cols, "block": block})
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        env = LaunchEnv(args.scalars, grid)
+        i0, iinc = env.affine_pid(p["in_off"])
+        o0, oinc = env.affine_pid(p["out_off"])
+        if any(iinc[1:]) or any(oinc[1:]) or grid[1] * grid[2] != 1:
+            raise UnsupportedTTIR("softmax family: rows must be indexed by program_id(0) only")
+        n_cols = int(p["n_cols"].evaluate(env.at()))
+        rc = rt.lib().tsb_softmax_rows(args.pointer(p["in_arg"]) + 4 * i0, args.pointer(p["out_arg"]) + 4 * o0,
+                                       rt.DTYPES["f32"], iinc[0], oinc[0], n_cols, p["block"], pid_lo, pid_hi, stream)
+        rt.check(rc, f"tsb_softmax_rows[{self.name}]")
+
+
+# --------------------------------------------------------------------------
+# LayerNorm forward
+
+class LayerNormPlan(Plan):
+    family = "layernorm"
+
+    @staticmethod
+    def build(kernel: Kernel, an: Analyzer) -> "LayerNormPlan":
+        eff = kernel.effects
+        loops = [e for k, e in eff if k == "loop"]
+        stores = [e for k, e in eff if k == "store"]
+        if len(loops) != 3 or len(stores) > 2:
+            raise UnsupportedTTIR("layernorm family: expects three loops and at most two scalar stores")
+        l1, l2, l3 = loops
+        if l1.effects or l2.effects or len(l3.effects) != 1 or l3.effects[0][0] != "store":
+            raise UnsupportedTTIR("layernorm family: loop structure differs")
+        for l in loops:
+            if not l.lb.is_zero or l.ub != l1.ub or l.step != l1.step or not l.step.is_const:
+                raise UnsupportedTTIR("layernorm family: loops must all run 0..N step BLOCK")
+        if len(l1.yields) != 1 or len(l2.yields) != 1 or l3.yields:
+            raise UnsupportedTTIR("layernorm family: unexpected loop-carried values")
+        ysto: Access = l3.effects[0][1]
+        b: Dict[str, Node] = {}
+        it1 = ("attrs", ("$", "acc1"), {"loop": l1.id, "k": 0})
+        if not match(l1.yields[0].node, ("op", "addf", it1, ("ext", ("$", "x1"))), b) or b["acc1"].op != "iter_arg":
+            raise UnsupportedTTIR("layernorm family: first loop is not a lane-accumulated sum of x")
+        sum1 = ("reduce", "addf", 0, ("attrs", ("$", "r1"), {"loop": l1.id, "k": 0}))
+        mean = ("op", "divf", sum1, ("$", "nf"))
+        d = ("op", "select", ("$", "mask2"), ("op", "subf", ("ext", ("$", "x2")), ("splat", mean)), ("const", 0.0))
+        it2 = ("attrs", ("$", "acc2"), {"loop": l2.id, "k": 0})
+        if not match(l2.yields[0].node, ("op", "addf", it2, ("op", "mulf", d, d)), b):
+            raise UnsupportedTTIR("layernorm family: second loop is not a lane-accumulated sum of (x-mean)^2")
+        var = ("op", "divf", ("reduce", "addf", 0, ("attrs", ("$", "r2"), {"loop": l2.id, "k": 0})), ("$", "nf"))
+        rstd = ("op", "divf", ("const", 1.0), ("op", "sqrt", ("op", "addf", var, ("$", "eps"))))
+        yv = ("trunc", ("op", "addf", ("op", "mulf", ("op", "mulf", ("op", "subf", ("ext", ("$", "x3")), ("splat", mean)),
+                                                      ("splat", rstd)), ("ext", ("$", "w"))), ("ext", ("$", "bias"))))
+        if not match(ysto.value, yv, b):
+            raise UnsupportedTTIR("layernorm family: third loop is not ((x-mean)*rstd)*w+b")
+        for k in ("r1", "r2"):
+            if b[k].op != "loop_result":
+                raise UnsupportedTTIR("layernorm family: reductions do not consume the loop results")
+        if b["mask2"].op != "maskval" or b["eps"].op != "farg":
+            raise UnsupportedTTIR("layernorm family: unexpected select mask or eps")
+        nf = b["nf"]
+        if not (nf.op == "cast" and nf.args[0].op == "sint"):
+            raise UnsupportedTTIR("layernorm family: divisor is not float(N)")
+        n_poly = nf.args[0].attr("poly")
+        if n_poly != l1.ub:
+            raise UnsupportedTTIR("layernorm family: divisor differs from the loop bound")
+        for k in ("x1", "x2", "x3", "w", "bias"):
+            if b[k].op != "load":
+                raise UnsupportedTTIR("layernorm family: operand is not a block load")
+        x1, x2, x3, w, bias = (an.access_of(b[k]) for k in ("x1", "x2", "x3", "w", "bias"))
+        block = l1.step.as_const
+        it_atoms = {l.id: Poly.atom(("it", l.id)) for l in loops}
+        # every x load reads row*stride + iv + lane with mask iv + lane < N and other = 0
+        base_off = None
+        for acc, l in ((x1, l1), (x2, l2), (x3, l3)):
+            _row_access(acc, "layernorm x")
+            off = acc.offset - l.step * it_atoms[l.id]
+            if off.depends_on(("it", "carry")) or acc.shape != (block,):
+                raise UnsupportedTTIR("layernorm family: x offset is not row base + loop offset")
+            if base_off is None:
+                base_off = off
+            if off != base_off or acc.arg != x1.arg or acc.elem != x1.elem:
+                raise UnsupportedTTIR("layernorm family: the three x loads differ")
+            mb = _single_bound(acc.mask, 0)
+            if mb is None or mb[0] != l.step * it_atoms[l.id] or mb[1] != n_poly:
+                raise UnsupportedTTIR("layernorm family: x mask is not offs < N")
+            if other_bits(acc.other, acc.elem) != 0:
+                raise UnsupportedTTIR("layernorm family: x loads need other=0")
+        for acc in (w, bias):
+            _row_access(acc, "layernorm weight/bias")
+            if acc.offset != l3.step * it_atoms[l3.id] or acc.elem != x1.elem:
+                raise UnsupportedTTIR("layernorm family: weight/bias are not indexed by column only")
+        _row_access(ysto, "layernorm y")
+        yoff = ysto.offset - l3.step * it_atoms[l3.id]
+        if yoff.depends_on(("it", "carry")) or ysto.elem != x1.elem:
+            raise UnsupportedTTIR("layernorm family: y offset is not row base + loop offset")
+        mean_arg = rstd_arg = None
+        mean_off = rstd_off = None
+        for s in stores:
+            bb = dict(b)
+            if s.shape != () or s.elem != "f32":
+                raise UnsupportedTTIR("layernorm family: unexpected extra store")
+            if match(s.value, mean, bb):
+                mean_arg, mean_off = s.arg, s.offset
+            elif match(s.value, rstd, bb):
+                rstd_arg, rstd_off = s.arg, s.offset
+            else:
+                raise UnsupportedTTIR("layernorm family: extra store is neither mean nor rstd")
+        return LayerNormPlan(kernel.name, {
+            "x": x1.arg, "y": ysto.arg, "w": w.arg, "b": bias.arg, "mean": mean_arg, "rstd": rstd_arg,
+            "x_off": base_off, "y_off": yoff, "mean_off": mean_off, "rstd_off": rstd_off, "n": n_poly,
+            "eps_arg": b["eps"].attr("arg"), "elem": x1.elem})
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        env = LaunchEnv(args.scalars, grid)
+        x0, xinc = env.affine_pid(p["x_off"])
+        y0, yinc = env.affine_pid(p["y_off"])
+        if any(xinc[1:]) or any(yinc[1:]) or grid[1] * grid[2] != 1:
+            raise UnsupportedTTIR("layernorm family: rows must be indexed by program_id(0) only")
+        es = rt.DTYPE_SIZE[p["elem"]]
+        mean_p = rstd_p = None
+        for key in ("mean", "rstd"):
+            if p[key] is not None:
+                o0, oinc = env.affine_pid(p[key + "_off"])
+                if oinc[0] != 1:
+                    raise UnsupportedTTIR("layernorm family: mean/rstd must be stored at index row")
+                ptr = args.pointer(p[key]) + 4 * o0
+                if key == "mean":
+                    mean_p = ptr
+                else:
+                    rstd_p = ptr
+        n = int(p["n"].evaluate(env.at()))
+        rc = rt.lib().tsb_layernorm_fwd(args.pointer(p["x"]) + es * x0, args.pointer(p["y"]) + es * y0,
+                                        args.pointer(p["w"]), args.pointer(p["b"]), mean_p, rstd_p,
+                                        rt.DTYPES[p["elem"]], xinc[0], yinc[0], n,
+                                        float(args.floats[p["eps_arg"]]), pid_lo, pid_hi, stream)
+        rt.check(rc, f"tsb_layernorm_fwd[{self.name}]")
+
+
+# --------------------------------------------------------------------------
+# strided 2-D reduction along one axis, and the full sum
+
+class ReduceRowsPlan(Plan):
+    family = "reduce_rows"
+
+    @staticmethod
+    def build(kernel: Kernel, an: Analyzer) -> "ReduceRowsPlan":
+        eff = kernel.effects
+        if len(eff) != 2 or eff[0][0] != "loop" or eff[1][0] != "store":
+            raise UnsupportedTTIR("reduce_rows family: expects one loop followed by one store")
+        loop: Loop = eff[0][1]
+        st: Access = eff[1][1]
+        if loop.effects or len(loop.yields) != 1 or not loop.lb.is_zero or not loop.step.is_const:
+            raise UnsupportedTTIR("reduce_rows family: loop shape differs")
+        b: Dict[str, Node] = {}
+        it = ("attrs", ("$", "acc"), {"loop": loop.id, "k": 0})
+        if not match(loop.yields[0].node, ("op", "addf", it, ("reduce", "addf", None, ("$", "x"))), b):
+            raise UnsupportedTTIR("reduce_rows family: loop body is not acc += sum(block, axis)")
+        if b["acc"].op != "iter_arg" or b["x"].op != "load" or const_value(loop.inits[0].node) != 0.0:
+            raise UnsupportedTTIR("reduce_rows family: accumulator is not a zero-initialised loop-carried block")
+        rb: Dict[str, Node] = {}
+        if not match(st.value, ("attrs", ("$", "r"), {"loop": loop.id, "k": 0}), rb) or rb["r"].op != "loop_result":
+            raise UnsupportedTTIR("reduce_rows family: store does not write the accumulated sums")
+        red = loop.yields[0].node.args[1] if loop.yields[0].node.args[1].op == "reduce" else loop.yields[0].node.args[0]
+        axis = red.attr("axis")
+        ld = an.access_of(b["x"])
+        if len(ld.shape) != 2 or ld.wrapped or ld.elem != "f32" or st.elem != "f32":
+            raise UnsupportedTTIR("reduce_rows family: expects a 2-D fp32 block load")
+        keep = 1 - axis
+        itp = Poly.atom(("it", loop.id))
+        # offset = rows0(pid)*stride_keep + (step*it)*stride_red
+        off = ld.offset - loop.step * itp * ld.strides[axis]
+        if off.depends_on(("it", "carry")) or not is_affine_in_pid(off):
+            raise UnsupportedTTIR("reduce_rows family: block offset is not row block + loop offset")
+        mk, mr = _single_bound(ld.mask, keep), _single_bound(ld.mask, axis)
+        if mr is None or mr[0] != loop.step * itp:
+            raise UnsupportedTTIR("reduce_rows family: the reduced dim needs a mask col < N starting at the loop offset")
+        if other_bits(ld.other, "f32") != 0:
+            raise UnsupportedTTIR("reduce_rows family: masked load needs other=0")
+        if len(st.shape) != 1 or st.strides[0] != Poly.const(1) or st.shape[0] != ld.shape[keep]:
+            raise UnsupportedTTIR("reduce_rows family: store is not a unit-stride 1-D block of row sums")
+        sm = _single_bound(st.mask, 0)
+        if (mk is None) != (sm is None) or (mk is not None and (mk[0] != sm[0] or mk[1] != sm[1])):
+            raise UnsupportedTTIR("reduce_rows family: row masks of load and store differ")
+        if mk is not None and st.offset - mk[0] != Poly.const(0) and (st.offset - mk[0]).depends_on(("pid",)):
+            raise UnsupportedTTIR("reduce_rows family: store offset does not follow the row index")
+        return ReduceRowsPlan(kernel.name, {
+            "x": ld.arg, "out": st.arg, "block_rows": ld.shape[keep], "stride_keep": ld.strides[keep],
+            "stride_red": ld.strides[axis], "x_off": off, "out_off": st.offset,
+            "n_valid": Poly.fn("minsi", mr[1], loop.ub), "row_start": mk[0] if mk is not None else None,
+            "row_bound": mk[1] if mk is not None else None})
+
+    def __init__(self, name, params):
+        super().__init__(name, params)
+        self._scratch = None
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        env = LaunchEnv(args.scalars, grid)
+        if grid[1] * grid[2] != 1:
+            raise UnsupportedTTIR("reduce_rows family: expects a 1-D grid")
+        bm = p["block_rows"]
+        sk = int(p["stride_keep"].evaluate(env.at()))
+        sr = int(p["stride_red"].evaluate(env.at()))
+        x0, xinc = env.affine_pid(p["x_off"])
+        o0, oinc = env.affine_pid(p["out_off"])
+        if xinc[0] != bm * sk or oinc[0] != bm:
+            raise UnsupportedTTIR("reduce_rows family: programs do not tile the rows contiguously")
+        n_valid = max(int(p["n_valid"].evaluate(env.at())), 0)
+        total_rows = grid[0] * bm
+        if p["row_bound"] is not None:
+            s0, sinc = env.affine_pid(p["row_start"])
+            if s0 != 0 or sinc[0] != bm:
+                raise UnsupportedTTIR("reduce_rows family: row mask does not start at pid*BLOCK")
+            total_rows = min(total_rows, int(p["row_bound"].evaluate(env.at())))
+        row_lo, row_hi = min(pid_lo * bm, total_rows), min(pid_hi * bm, total_rows)
+        if row_hi <= row_lo:
+            return
+        need = rt.lib().tsb_reduce_rows_scratch_bytes(row_hi - row_lo, n_valid, sk, sr)
+        scratch = args.scratch(need, stream) if need > 0 else None
+        rc = rt.lib().tsb_reduce_rows(args.pointer(p["x"]) + 4 * x0, args.pointer(p["out"]) + 4 * o0, sk, sr, 1,
+                                      n_valid, row_lo, row_hi, scratch, stream)
+        rt.check(rc, f"tsb_reduce_rows[{self.name}]")
+
+
+class ReduceAllPlan(Plan):
+    family = "reduce_all"
+
+    @staticmethod
+    def build(kernel: Kernel, an: Analyzer) -> "ReduceAllPlan":
+        eff = kernel.effects
+        if len(eff) != 2 or eff[0][0] != "loop" or eff[1][0] != "store":
+            raise UnsupportedTTIR("reduce_all family: expects one loop followed by one store")
+        loop: Loop = eff[0][1]
+        st: Access = eff[1][1]
+        if st.shape != () or st.elem != "f32" or loop.effects or len(loop.yields) != 1 or not loop.lb.is_zero:
+            raise UnsupportedTTIR("reduce_all family: shape differs")
+        b: Dict[str, Node] = {}
+        it = ("attrs", ("$", "acc"), {"loop": loop.id, "k": 0})
+        if not match(loop.yields[0].node, ("op", "addf", it, ("$", "x")), b) or b["x"].op != "load" \
+                or b["acc"].op != "iter_arg" or const_value(loop.inits[0].node) != 0.0:
+            raise UnsupportedTTIR("reduce_all family: loop body is not acc += block")
+        rb: Dict[str, Node] = {}
+        if not match(st.value, ("reduce", "addf", 0, ("attrs", ("$", "r"), {"loop": loop.id, "k": 0})), rb):
+            raise UnsupportedTTIR("reduce_all family: store is not sum(acc)")
+        ld = an.access_of(b["x"])
+        itp = Poly.atom(("it", loop.id))
+        if len(ld.shape) != 1 or ld.elem != "f32" or ld.wrapped:
+            raise UnsupportedTTIR("reduce_all family: expects a 1-D fp32 block load")
+        off = ld.offset - loop.step * itp * ld.strides[0]
+        m = _single_bound(ld.mask, 0)
+        if off.depends_on(("it", "carry", "pid")) or st.offset.depends_on(("pid",)):
+            raise UnsupportedTTIR("reduce_all family: offsets depend on the loop or the program")
+        if m is None or m[0] != loop.step * itp or other_bits(ld.other, "f32") != 0:
+            raise UnsupportedTTIR("reduce_all family: load needs mask offs < n and other=0")
+        return ReduceAllPlan(kernel.name, {"x": ld.arg, "out": st.arg, "x_off": off, "out_off": st.offset,
+                                           "stride": ld.strides[0], "n": Poly.fn("minsi", m[1], loop.ub)})
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        if pid_hi <= pid_lo:
+            return
+        env = LaunchEnv(args.scalars, grid).at()
+        n = max(int(p["n"].evaluate(env)), 0)
+        rc = rt.lib().tsb_reduce_all(args.pointer(p["x"]) + 4 * int(p["x_off"].evaluate(env)),
+                                     args.pointer(p["out"]) + 4 * int(p["out_off"].evaluate(env)), n,
+                                     int(p["stride"].evaluate(env)), stream)
+        rt.check(rc, f"tsb_reduce_all[{self.name}]")
+
+
+# --------------------------------------------------------------------------
+# tt.dot
+
+class GemmPlan(Plan):
+    family = "gemm"
+
+    @staticmethod
+    def build(kernel: Kernel, an: Analyzer) -> "GemmPlan":
+        eff = kernel.effects
+        if len(eff) != 2 or eff[0][0] != "loop" or eff[1][0] != "store":
+            raise UnsupportedTTIR("gemm family: expects one K loop followed by one store")
+        loop: Loop = eff[0][1]
+        st: Access = eff[1][1]
+        if loop.effects:
+            raise UnsupportedTTIR("gemm family: stores inside the K loop")
+        acc_k = None
+        b: Dict[str, Node] = {}
+        for k, y in enumerate(loop.yields):
+            if isinstance(y, TData) and y.node.op == "dot":
+                bb: Dict[str, Node] = {}
+                if match(y.node, ("op", "dot", ("$", "a"), ("$", "b"), ("attrs", ("$", "acc"), {"loop": loop.id, "k": k})), bb) \
+                        and bb["acc"].op == "iter_arg":
+                    acc_k, b = k, bb
+        if acc_k is None or b["a"].op != "load" or b["b"].op != "load":
+            raise UnsupportedTTIR("gemm family: loop body is not acc = dot(load, load, acc)")
+        if const_value(loop.inits[acc_k].node) != 0.0:
+            raise UnsupportedTTIR("gemm family: accumulator does not start at zero")
+        rb: Dict[str, Node] = {}
+        if not match(st.value, ("trunc", ("attrs", ("$", "r"), {"loop": loop.id, "k": acc_k})), rb) or rb["r"].op != "loop_result":
+            raise UnsupportedTTIR("gemm family: store does not write the (truncated) accumulator")
+        A, B = an.access_of(b["a"]), an.access_of(b["b"])
+        if A.elem not in ("f16", "bf16") or B.elem != A.elem or st.elem != A.elem:
+            raise UnsupportedTTIR("gemm family: operands and result must all be f16 or all bf16")
+        if len(A.shape) != 2 or len(B.shape) != 2 or len(st.shape) != 2 or A.shape[1] != B.shape[0] \
+                or st.shape != (A.shape[0], B.shape[1]):
+            raise UnsupportedTTIR("gemm family: block shapes do not form a matmul")
+        BM, BK = A.shape
+        BN = B.shape[1]
+        itp = Poly.atom(("it", loop.id))
+
+        def split(acc: Access, kdim: int, what: str):
+            """-> (tile offset Poly (it = 0), k advance per iteration Poly, wrapped on the non-K dim or None)"""
+            if len(acc.wrapped) > 1 or (acc.wrapped and acc.wrapped[0].dim == kdim):
+                raise UnsupportedTTIR(f"gemm family: {what} wraps along K or along both dims")
+            # offset is linear in `it`: offset = base + it * adv
+            terms_it = {m: c for m, c in acc.offset.terms.items() if ("it", loop.id) in m}
+            adv = Poly({tuple(a for a in m if a != ("it", loop.id)): c for m, c in terms_it.items()
+                        if m.count(("it", loop.id)) == 1})
+            base = acc.offset - adv * itp
+            if base.depends_on(("it", "carry")) or adv.depends_on(("it", "carry", "pid")):
+                raise UnsupportedTTIR(f"gemm family: {what} offset is not tile base + it * step")
+            return base, adv, (acc.wrapped[0] if acc.wrapped else None)
+
+        a_base, a_adv, a_wrap = split(A, 1, "A")
+        b_base, b_adv, b_wrap = split(B, 0, "B")
+        mka = _single_bound(A.mask, 1)
+        mkb = _single_bound(B.mask, 0)
+        for m, what in ((mka, "A"), (mkb, "B")):
+            if m is not None and other_bits((A if what == "A" else B).other, A.elem) != 0:
+                raise UnsupportedTTIR(f"gemm family: masked {what} load needs other=0")
+        params = {
+            "a": A.arg, "b": B.arg, "c": st.arg, "elem": A.elem, "BM": BM, "BN": BN, "BK": BK,
+            "a_base": a_base, "a_adv": a_adv, "b_base": b_base, "b_adv": b_adv,
+            "sam": a_wrap.scale * a_wrap.inner_stride if a_wrap else A.strides[0], "sak": A.strides[1],
+            "sbk": B.strides[0], "sbn": b_wrap.scale * b_wrap.inner_stride if b_wrap else B.strides[1],
+            "scm": st.strides[0], "scn": st.strides[1], "c_off": st.offset,
+            "trip": loop.trip,
+            # K mask: lanes k with start + k < bound (evaluated at it = 0 gives K itself)
+            "ka": list(mka) if mka else None, "kb": list(mkb) if mkb else None,
+            "am": list(_single_bound(A.mask, 0)) if _single_bound(A.mask, 0) else None,
+            "bn": list(_single_bound(B.mask, 1)) if _single_bound(B.mask, 1) else None,
+            "cm": list(_single_bound(st.mask, 0)) if _single_bound(st.mask, 0) else None,
+            "cn": list(_single_bound(st.mask, 1)) if _single_bound(st.mask, 1) else None,
+            "a_wrap": [a_wrap.inner_offset, a_wrap.inner_stride, a_wrap.modulus, a_wrap.scale] if a_wrap else None,
+            "b_wrap": [b_wrap.inner_offset, b_wrap.inner_stride, b_wrap.modulus, b_wrap.scale] if b_wrap else None,
+        }
+        if st.wrapped:
+            raise UnsupportedTTIR("gemm family: wrap-around store")
+        return GemmPlan(kernel.name, params)
+
+    def __init__(self, name, params):
+        super().__init__(name, params)
+        self._cache = {}
+
+    def resolve(self, args, grid):
+        """Evaluate the plan for concrete scalars: problem sizes, strides and the pid -> tile table."""
+        p = self.p
+        env = LaunchEnv(args.scalars, grid)
+        e0 = env.at()
+        ev = lambda q: int(q.evaluate(e0))
+        BM, BN, BK = p["BM"], p["BN"], p["BK"]
+        sam, sak, sbk, sbn, scm, scn = (ev(p[k]) for k in ("sam", "sak", "sbk", "sbn", "scm", "scn"))
+        trip = ev(p["trip"])
+        # K
+        K = None
+        for key in ("ka", "kb"):
+            if p[key] is not None:
+                k_here = ev(p[key][1]) - ev(p[key][0])
+                if K is not None and K != k_here:
+                    raise UnsupportedTTIR("gemm family: A and B K-masks disagree")
+                K = k_here
+        if K is None:
+            K = trip * BK
+        if trip != -(-K // BK) and not (K <= 0 and trip == 0):
+            raise UnsupportedTTIR(f"gemm family: loop runs {trip} steps but K={K}, BLOCK_K={BK}")
+        if ev(p["a_adv"]) != BK * sak or ev(p["b_adv"]) != BK * sbk:
+            raise UnsupportedTTIR("gemm family: pointers do not advance by BLOCK_K per iteration")
+        # tiles per program, from every program's offsets
+        ea = env.all_pids()
+        n_prog = grid[0] * grid[1] * grid[2]
+        full = lambda q: np.broadcast_to(np.asarray(q.evaluate(ea), dtype=np.int64), (n_prog,))
+        c_off = full(p["c_off"])
+        if p["cm"] is not None:
+            row0 = full(p["cm"][0])
+            M = ev(p["cm"][1])
+        elif p["a_wrap"] is not None:
+            row0 = full(p["a_wrap"][0])
+            M = None
+        else:
+            if sam == 0:
+                raise UnsupportedTTIR("gemm family: cannot derive tile rows (stride_am == 0)")
+            row0 = full(p["a_base"]) // sam
+            M = None
+        if p["cn"] is not None:
+            col0 = full(p["cn"][0])
+            N = ev(p["cn"][1])
+        elif p["b_wrap"] is not None:
+            col0 = full(p["b_wrap"][0])
+            N = None
+        else:
+            if sbn == 0:
+                raise UnsupportedTTIR("gemm family: cannot derive tile columns (stride_bn == 0)")
+            col0 = full(p["b_base"]) // sbn
+            N = None
+        if np.any(row0 % BM) or np.any(col0 % BN) or np.any(row0 < 0) or np.any(col0 < 0):
+            raise UnsupportedTTIR("gemm family: tiles are not aligned to the block shape")
+        if M is None:
+            M = int(row0.max()) + BM if n_prog else 0
+        if N is None:
+            N = int(col0.max()) + BN if n_prog else 0
+        if np.any(c_off != row0 * scm + col0 * scn):
+            raise UnsupportedTTIR("gemm family: store offsets do not match the tile indices")
+        # operand offsets must address the same tiles (a wrap modulo M/N only changes rows the
+        # store mask discards, which requires the modulus to equal the store bound)
+        if p["a_wrap"] is not None:
+            w = p["a_wrap"]
+            if ev(w[2]) != M or ev(w[1]) != 1 or ev(w[3]) != sam or np.any(full(w[0]) != row0) or np.any(full(p["a_base"]) != 0):
+                raise UnsupportedTTIR("gemm family: A row wrap-around is not `% M` of the tile rows")
+        elif np.any(full(p["a_base"]) != row0 * sam):
+            raise UnsupportedTTIR("gemm family: A offsets do not match the tile rows")
+        if p["b_wrap"] is not None:
+            w = p["b_wrap"]
+            if ev(w[2]) != N or ev(w[1]) != 1 or ev(w[3]) != sbn or np.any(full(w[0]) != col0) or np.any(full(p["b_base"]) != 0):
+                raise UnsupportedTTIR("gemm family: B column wrap-around is not `% N` of the tile columns")
+        elif np.any(full(p["b_base"]) != col0 * sbn):
+            raise UnsupportedTTIR("gemm family: B offsets do not match the tile columns")
+        for key, lim, what in (("am", M, "A rows"), ("bn", N, "B columns")):
+            if p[key] is not None and ev(p[key][1]) != lim:
+                raise UnsupportedTTIR(f"gemm family: mask bound of {what} differs from the store bound")
+        unmasked_rows = p["am"] is None and p["a_wrap"] is None and p["cm"] is None
+        tiles = np.stack([row0 // BM, col0 // BN], axis=1).astype(np.int32)
+        return dict(M=M, N=N, K=K, sam=sam, sak=sak, sbk=sbk, sbn=sbn, scm=scm, scn=scn, tiles=tiles,
+                    n_prog=n_prog, unmasked_rows=unmasked_rows)
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        key = tuple(sorted(args.scalars.items())) + tuple(grid)
+        r = self._cache.get(key)
+        if r is None:
+            r = self.resolve(args, grid)
+            if len(self._cache) > 16:
+                self._cache.clear()
+            self._cache[key] = r
+        tiles_dev = args.device_table(("gemm_tiles", self.name) + key, r["tiles"], stream)
+        status = args.status_word(stream)
+        rc = rt.lib().tsb_gemm(args.pointer(p["a"]), args.pointer(p["b"]), args.pointer(p["c"]),
+                               rt.DTYPES[p["elem"]], r["M"], r["N"], r["K"], r["sam"], r["sak"], r["sbk"],
+                               r["sbn"], r["scm"], r["scn"], p["BM"], p["BN"], p["BK"], tiles_dev,
+                               r["n_prog"], pid_lo, pid_hi, status, stream)
+        rt.check(rc, f"tsb_gemm[{self.name}]")
+
+
+_FAMILIES = {c.family: c for c in (GemmPlan, LayerNormPlan, SoftmaxPlan, ReduceRowsPlan, ReduceAllPlan,
+                                   ElementwisePlan)}
+_ORDER = [GemmPlan, LayerNormPlan, SoftmaxPlan, ReduceRowsPlan, ReduceAllPlan, ElementwisePlan]
+
+
+def make_plan(kernel: Kernel, an: Analyzer) -> Plan:
+    """Pick the kernel family for an analysed kernel or raise UnsupportedTTIR with every reason."""
+    reasons = []
+    for cls in _ORDER:
+        try:
+            return cls.build(kernel, an)
+        except UnsupportedTTIR as e:
+            reasons.append(f"{cls.family}: {e}")
+    raise UnsupportedTTIR(f"kernel {kernel.name} fits no pre-built kernel family:\n  " + "\n  ".join(reasons))

@@ -1,0 +1,227 @@
+// Strided masked 2-D sums along axis 1, and the full 1-D sum.
+//
+// Reference lowered form this replaces (paths inside microsoft/triton-shared):
+//   masked 2-D block load   test/Conversion/StructuredToMemref/masked_ldst_2d.mlir:76-99
+//   sum over axis 1         test/Conversion/StructuredToMemref/reducesum_512_256_f32_axis1.mlir
+//                           (transpose + linalg.reduce dims=[0], ConversionPatterns.hpp:1343-1407)
+//   scalar sum              test/Conversion/StructuredToMemref/reducesum_scalar.mlir:21-31
+// The CPU backend copies each ragged block element by element
+// (CRunnerUtils.cpp:58-113) and folds left to right on one thread.
+#include "tsb_common.cuh"
+
+namespace tsb {
+
+// ---- kept dim contiguous (stride_m == 1): "column sums of a row-major matrix" ----
+// CTA = 8 warps and a tile of 128 consecutive rows i. With VEC4 a lane owns rows
+// 4*lane..4*lane+3 of the tile and issues one 16-byte load per j; otherwise it
+// owns rows lane, lane+32, lane+64, lane+96 (scalar loads, still coalesced).
+// The 8 warps take interleaved j. blockIdx.y selects a slice of j (a "split");
+// partial sums of split s go to dst[s*dst_stride_split + i] (straight to the
+// output when there is one split).
+constexpr int RC_WARPS = 8;
+constexpr int RC_UNROLL = 8;
+constexpr int RC_TILE = 128;
+
+template <bool VEC4>
+__global__ void __launch_bounds__(RC_WARPS * 32)
+reduce_rows_contig_m_kernel(const float *__restrict__ x, float *__restrict__ dst,
+                            long long dst_stride_i, long long dst_stride_split, long long stride_n,
+                            long long n_valid, long long row_lo, long long row_hi, int j_per_split) {
+  __shared__ float red[RC_WARPS][RC_TILE];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long tile0 = row_lo + (long long)blockIdx.x * RC_TILE;
+  const long long j_lo = (long long)blockIdx.y * j_per_split;
+  long long j_hi = j_lo + j_per_split;
+  if (j_hi > n_valid) j_hi = n_valid;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (VEC4 && tile0 + RC_TILE <= row_hi) {
+    const float *p = x + tile0 + lane * 4;
+    long long j = j_lo + warp;
+    // RC_UNROLL independent 16-byte loads in flight per thread
+    for (; j + (RC_UNROLL - 1) * RC_WARPS < j_hi; j += RC_UNROLL * RC_WARPS) {
+      float4 q[RC_UNROLL];
+#pragma unroll
+      for (int u = 0; u < RC_UNROLL; ++u)
+        q[u] = __ldg(reinterpret_cast<const float4 *>(p + (j + u * RC_WARPS) * stride_n));
+#pragma unroll
+      for (int u = 0; u < RC_UNROLL; ++u) {
+        acc[0] += q[u].x; acc[1] += q[u].y; acc[2] += q[u].z; acc[3] += q[u].w;
+      }
+    }
+    for (; j < j_hi; j += RC_WARPS) {
+      float4 q = __ldg(reinterpret_cast<const float4 *>(p + j * stride_n));
+      acc[0] += q.x; acc[1] += q.y; acc[2] += q.z; acc[3] += q.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) red[warp][lane * 4 + k] = acc[k];
+  } else {
+    for (long long j = j_lo + warp; j < j_hi; j += RC_WARPS)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const long long i = tile0 + lane + 32 * k;
+        if (i < row_hi) acc[k] += __ldg(x + i + j * stride_n);
+      }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) red[warp][lane + 32 * k] = acc[k];
+  }
+  __syncthreads();
+  // 128 row sums per CTA, combined over the 8 warps in a fixed order
+  if (threadIdx.x < RC_TILE) {
+    const int r = threadIdx.x;
+    float s = red[0][r];
+#pragma unroll
+    for (int w = 1; w < RC_WARPS; ++w) s += red[w][r];
+    const long long i = tile0 + r;
+    if (i < row_hi) dst[(i - row_lo) * dst_stride_i + (long long)blockIdx.y * dst_stride_split] = s;
+  }
+}
+
+// Sum the per-split partials: out[i] = sum_s part[s*n_rows + i], s ascending.
+__global__ void reduce_rows_finalize_kernel(const float *__restrict__ part, float *__restrict__ out,
+                                            long long out_stride, long long n_rows, int splits,
+                                            long long row_lo) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_rows) return;
+  float s = 0.f;
+  for (int k = 0; k < splits; ++k) s += part[(long long)k * n_rows + i];
+  out[(row_lo + i) * out_stride] = s;
+}
+
+// ---- reduced dim contiguous (stride_n == 1): one warp per row -----------------
+__global__ void __launch_bounds__(256)
+reduce_rows_contig_n_kernel(const float *__restrict__ x, float *__restrict__ out, long long stride_m,
+                            long long out_stride, long long n_valid, long long row_lo,
+                            long long row_hi, int vec_ok) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long i = row_lo + (long long)blockIdx.x * 8 + warp;
+  if (i >= row_hi) return;
+  const float *p = x + i * stride_m;
+  float s = 0.f;
+  if (vec_ok) {
+    const long long nv = n_valid / 4;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (long long v = lane; v < nv; v += 32) {
+      float4 q = __ldg(reinterpret_cast<const float4 *>(p) + v);
+      a0 += q.x; a1 += q.y; a2 += q.z; a3 += q.w;
+    }
+    s = (a0 + a1) + (a2 + a3);
+    for (long long j = nv * 4 + lane; j < n_valid; j += 32) s += __ldg(p + j);
+  } else {
+    for (long long j = lane; j < n_valid; j += 32) s += __ldg(p + j);
+  }
+  s = warp_sum(s);
+  if (lane == 0) out[i * out_stride] = s;
+}
+
+// ---- arbitrary strides: one thread per row ------------------------------------
+__global__ void reduce_rows_generic_kernel(const float *__restrict__ x, float *__restrict__ out,
+                                           long long stride_m, long long stride_n,
+                                           long long out_stride, long long n_valid,
+                                           long long row_lo, long long row_hi) {
+  const long long i = row_lo + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= row_hi) return;
+  float s = 0.f;
+  for (long long j = 0; j < n_valid; ++j) s += __ldg(x + i * stride_m + j * stride_n);
+  out[i * out_stride] = s;
+}
+
+// ---- full sum: one CTA, fixed order --------------------------------------------
+__global__ void __launch_bounds__(1024)
+reduce_all_kernel(const float *__restrict__ x, float *__restrict__ out, long long n, long long stride) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < n; i += 1024) s += __ldg(x + i * stride);
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = red[threadIdx.x];
+    v = warp_sum(v);
+    if (threadIdx.x == 0) out[0] = v;
+  }
+}
+
+struct ContigMPlan {
+  long long i_tiles;
+  int splits;
+  int j_per_split;
+};
+
+// Depends on the problem shape only, so that the scratch size a caller asked
+// for earlier always matches the launch.
+static ContigMPlan plan_contig_m(long long n_rows, long long n_valid) {
+  ContigMPlan p;
+  p.i_tiles = (n_rows + RC_TILE - 1) / RC_TILE;
+  // enough CTAs for two full waves of 8 CTAs per SM; each split keeps >= 64 j
+  long long want = (2ll * 8 * sm_count() + p.i_tiles - 1) / p.i_tiles;
+  const long long max_splits = (n_valid + 63) / 64;
+  if (want > max_splits) want = max_splits;
+  if (want > 1024) want = 1024;
+  if (want < 1) want = 1;
+  p.j_per_split = (int)((n_valid + want - 1) / want);
+  if (p.j_per_split < 1) p.j_per_split = 1;
+  p.splits = (int)((n_valid + p.j_per_split - 1) / p.j_per_split);
+  if (p.splits < 1) p.splits = 1;
+  return p;
+}
+
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" int64_t tsb_reduce_rows_scratch_bytes(int64_t n_rows, int64_t n_valid, int64_t stride_m,
+                                                 int64_t stride_n) {
+  (void)stride_n;
+  if (n_rows <= 0 || n_valid <= 0 || stride_m != 1) return 0;
+  ContigMPlan p = plan_contig_m(n_rows, n_valid);
+  return p.splits > 1 ? (int64_t)p.splits * n_rows * (int64_t)sizeof(float) : 0;
+}
+
+extern "C" int tsb_reduce_rows(const float *x, float *out, int64_t stride_m, int64_t stride_n,
+                               int64_t out_stride, int64_t n_valid, int64_t row_lo, int64_t row_hi,
+                               void *scratch, void *stream) {
+  if (!x || !out) return fail(TSB_ERR_INVALID, "tsb_reduce_rows: null pointer");
+  if (row_lo < 0 || row_hi < row_lo || n_valid < 0) return fail(TSB_ERR_INVALID, "tsb_reduce_rows: bad range");
+  const long long n_rows = row_hi - row_lo;
+  if (n_rows == 0) return TSB_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (stride_m == 1 && n_valid > 0) {
+    const ContigMPlan p = plan_contig_m(n_rows, n_valid);
+    if (p.splits > 1 && !scratch)
+      return fail(TSB_ERR_INVALID, "tsb_reduce_rows: %lld bytes of scratch required, got NULL",
+                  (long long)p.splits * n_rows * (long long)sizeof(float));
+    const bool vec4 = ((uintptr_t)(x + row_lo) % 16) == 0 && stride_n % 4 == 0;
+    dim3 grid((unsigned)p.i_tiles, (unsigned)p.splits);
+    float *dst = p.splits > 1 ? (float *)scratch : out + row_lo * out_stride;
+    const long long dsi = p.splits > 1 ? 1 : out_stride;
+    const long long dss = p.splits > 1 ? n_rows : 0;
+    if (vec4)
+      reduce_rows_contig_m_kernel<true><<<grid, RC_WARPS * 32, 0, s>>>(x, dst, dsi, dss, stride_n, n_valid, row_lo, row_hi, p.j_per_split);
+    else
+      reduce_rows_contig_m_kernel<false><<<grid, RC_WARPS * 32, 0, s>>>(x, dst, dsi, dss, stride_n, n_valid, row_lo, row_hi, p.j_per_split);
+    TSB_LAUNCH_OK("reduce_rows_contig_m_kernel");
+    if (p.splits > 1) {
+      reduce_rows_finalize_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, s>>>(
+          (const float *)scratch, out, out_stride, n_rows, p.splits, row_lo);
+      TSB_LAUNCH_OK("reduce_rows_finalize_kernel");
+    }
+    return TSB_OK;
+  }
+  if (stride_n == 1 || n_valid == 0) {
+    const int vec_ok = ((uintptr_t)x % 16) == 0 && stride_m % 4 == 0;
+    reduce_rows_contig_n_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, s>>>(x, out, stride_m, out_stride, n_valid, row_lo, row_hi, vec_ok);
+    TSB_LAUNCH_OK("reduce_rows_contig_n_kernel");
+    return TSB_OK;
+  }
+  reduce_rows_generic_kernel<<<(unsigned)((n_rows + 127) / 128), 128, 0, s>>>(x, out, stride_m, stride_n, out_stride, n_valid, row_lo, row_hi);
+  TSB_LAUNCH_OK("reduce_rows_generic_kernel");
+  return TSB_OK;
+}
+
+extern "C" int tsb_reduce_all(const float *x, float *out, int64_t n, int64_t stride, void *stream) {
+  if (!x || !out) return fail(TSB_ERR_INVALID, "tsb_reduce_all: null pointer");
+  if (n < 0) return fail(TSB_ERR_INVALID, "tsb_reduce_all: negative length");
+  reduce_all_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(x, out, n, stride);
+  TSB_LAUNCH_OK("reduce_all_kernel");
+  return TSB_OK;
+}

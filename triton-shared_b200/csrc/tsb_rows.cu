@@ -1,0 +1,368 @@
+// One-program-per-row kernels: fused softmax and LayerNorm forward.
+//
+// Reference lowered forms these replace (paths inside microsoft/triton-shared):
+//   softmax    test/Conversion/StructuredToMemref/kernel-02-fused-softmax.mlir:50-90
+//              (python/examples/test_softmax.py:8-29)
+//   layernorm  test/Conversion/StructuredToMemref/kernel-05-layer-norm-fwd.mlir
+//              (python/examples/test_layernorm.py:29-76)
+// In the reference every op is a separate scalar loop over a malloc'ed 1024-lane
+// buffer and reductions are left-to-right folds (ConversionPatterns.hpp:1203-1440).
+// Here a row is read from HBM once, held in registers, reduced with warp
+// shuffles plus a shared-memory step across warps, and written once.
+#include "tsb_common.cuh"
+#include <math.h>
+
+namespace tsb {
+
+// Sum / max over the TPR threads that share a row. TPR is a multiple of 32 and
+// rows never share a warp, so warp w of the CTA belongs to row w / (TPR/32).
+template <int TPR, bool IS_MAX>
+__device__ __forceinline__ float row_reduce(float v, float *smem /* [THREADS/32] */) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  if (TPR == 32) return v;
+  constexpr int WPR = TPR / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // smem may still be read by the previous reduction
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  const int w0 = (warp / WPR) * WPR;
+  float r = smem[w0];
+#pragma unroll
+  for (int k = 1; k < WPR; ++k) r = IS_MAX ? fmaxf(r, smem[w0 + k]) : r + smem[w0 + k];
+  return r;
+}
+
+// ---------------------------------------------------------------------------
+// softmax, fp32
+// A row is covered by TPR threads x VPT vectors x 4 lanes >= n_cols.
+// ALIGNED: 16-byte vector path (row bases and strides multiples of 4 floats).
+template <int TPR, int VPT, int THREADS, bool ALIGNED>
+__global__ void __launch_bounds__(THREADS)
+softmax_rows_f32_kernel(const float *__restrict__ in, float *__restrict__ out, long long in_stride,
+                        long long out_stride, int n_cols, long long row_lo, long long row_hi) {
+  constexpr int RPC = THREADS / TPR;  // rows per CTA
+  __shared__ float red[THREADS / 32];
+  const int t = threadIdx.x % TPR;
+  const long long row = row_lo + (long long)blockIdx.x * RPC + threadIdx.x / TPR;
+  const bool live = row < row_hi;
+  const float *src = in + (live ? row : row_lo) * in_stride;
+  float x[VPT][4];
+  const float NEG_INF = __uint_as_float(0xff800000u);
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    if (ALIGNED) {
+      const int c = (v * TPR + t) * 4;
+      if (live && c + 4 <= n_cols) {
+        float4 q = __ldg(reinterpret_cast<const float4 *>(src + c));
+        x[v][0] = q.x; x[v][1] = q.y; x[v][2] = q.z; x[v][3] = q.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) x[v][k] = (live && c + k < n_cols) ? __ldg(src + c + k) : NEG_INF;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = (v * 4 + k) * TPR + t;
+        x[v][k] = (live && c < n_cols) ? __ldg(src + c) : NEG_INF;
+      }
+    }
+  }
+  float m = NEG_INF;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) m = fmaxf(m, x[v][k]);
+  m = row_reduce<TPR, true>(m, red);
+  float s = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x[v][k] = expf(x[v][k] - m);
+      s += x[v][k];
+    }
+  s = row_reduce<TPR, false>(s, red);
+  if (!live) return;
+  float *dst = out + row * out_stride;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    if (ALIGNED) {
+      const int c = (v * TPR + t) * 4;
+      if (c + 4 <= n_cols) {
+        *reinterpret_cast<float4 *>(dst + c) =
+            make_float4(x[v][0] / s, x[v][1] / s, x[v][2] / s, x[v][3] / s);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (c + k < n_cols) dst[c + k] = x[v][k] / s;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = (v * 4 + k) * TPR + t;
+        if (c < n_cols) dst[c] = x[v][k] / s;
+      }
+    }
+  }
+}
+
+template <int TPR, int VPT, int THREADS>
+static int launch_softmax(const float *in, float *out, long long is, long long os, int n_cols,
+                          long long row_lo, long long row_hi, bool aligned, cudaStream_t s) {
+  constexpr int RPC = THREADS / TPR;
+  const long long rows = row_hi - row_lo;
+  const long long ctas = (rows + RPC - 1) / RPC;
+  if (ctas > 0x7fffffffll) return fail(TSB_ERR_UNSUPPORTED, "tsb_softmax_rows: too many rows");
+  if (aligned)
+    softmax_rows_f32_kernel<TPR, VPT, THREADS, true><<<(unsigned)ctas, THREADS, 0, s>>>(in, out, is, os, n_cols, row_lo, row_hi);
+  else
+    softmax_rows_f32_kernel<TPR, VPT, THREADS, false><<<(unsigned)ctas, THREADS, 0, s>>>(in, out, is, os, n_cols, row_lo, row_hi);
+  TSB_LAUNCH_OK("softmax_rows_f32_kernel");
+  return TSB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm forward. T = __half / __nv_bfloat16 / float in memory, fp32 math.
+template <typename T> struct Io;
+template <> struct Io<__half> {
+  static constexpr int EPV = 8;
+  __device__ static float ld(const __half *p) { return __half2float(*p); }
+  __device__ static void st(__half *p, float v) { *p = __float2half_rn(v); }
+  __device__ static void unpack(const uint4 &q, float f[8]) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&q);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { float2 a = __half22float2(h[k]); f[2 * k] = a.x; f[2 * k + 1] = a.y; }
+  }
+  __device__ static uint4 pack(const float f[8]) {
+    uint4 q; __half2 *h = reinterpret_cast<__half2 *>(&q);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __halves2half2(__float2half_rn(f[2 * k]), __float2half_rn(f[2 * k + 1]));
+    return q;
+  }
+};
+template <> struct Io<__nv_bfloat16> {
+  static constexpr int EPV = 8;
+  __device__ static float ld(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+  __device__ static void st(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+  __device__ static void unpack(const uint4 &q, float f[8]) {
+    const unsigned *u = reinterpret_cast<const unsigned *>(&q);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { f[2 * k] = __uint_as_float(u[k] << 16); f[2 * k + 1] = __uint_as_float(u[k] & 0xffff0000u); }
+  }
+  __device__ static uint4 pack(const float f[8]) {
+    uint4 q; __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&q);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __halves2bfloat162(__float2bfloat16_rn(f[2 * k]), __float2bfloat16_rn(f[2 * k + 1]));
+    return q;
+  }
+};
+template <> struct Io<float> {
+  static constexpr int EPV = 4;
+  __device__ static float ld(const float *p) { return *p; }
+  __device__ static void st(float *p, float v) { *p = v; }
+  __device__ static void unpack(const uint4 &q, float f[4]) {
+    f[0] = __uint_as_float(q.x); f[1] = __uint_as_float(q.y); f[2] = __uint_as_float(q.z); f[3] = __uint_as_float(q.w);
+  }
+  __device__ static uint4 pack(const float f[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+
+// Persistent CTAs: weight and bias are loaded once per CTA and kept (packed, in
+// their memory type) in registers while the CTA walks rows blockIdx.x,
+// blockIdx.x + gridDim.x, ...  A row is covered by THREADS x VPT 16-byte vectors.
+// Element k of vector v of thread t is column
+//   ALIGNED : (v*THREADS + t)*EPV + k   (one 16-byte load per vector)
+//   otherwise: (v*EPV + k)*THREADS + t   (scalar loads, still coalesced)
+template <typename T, int THREADS, int VPT, bool ALIGNED>
+struct RowTile {
+  static constexpr int EPV = Io<T>::EPV;
+  __device__ static __forceinline__ int col(int v, int k, int t) {
+    return ALIGNED ? (v * THREADS + t) * EPV + k : (v * EPV + k) * THREADS + t;
+  }
+  __device__ static __forceinline__ void load(const T *src, int n_cols, int t, uint4 q[VPT]) {
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      if (ALIGNED && col(v, EPV - 1, t) < n_cols) {
+        q[v] = __ldg(reinterpret_cast<const uint4 *>(src + col(v, 0, t)));
+      } else {
+        float f[EPV];
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) f[k] = col(v, k, t) < n_cols ? Io<T>::ld(src + col(v, k, t)) : 0.f;
+        q[v] = Io<T>::pack(f);  // exact: values are already of type T
+      }
+    }
+  }
+};
+
+template <typename T, int THREADS, int VPT, bool ALIGNED>
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 768 / THREADS : 1))
+layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__restrict__ W,
+                     const T *__restrict__ B, float *__restrict__ Mean, float *__restrict__ Rstd,
+                     long long xs, long long ys, int n_cols, float eps, long long row_lo,
+                     long long row_hi) {
+  using Tile = RowTile<T, THREADS, VPT, ALIGNED>;
+  constexpr int EPV = Io<T>::EPV;
+  __shared__ float red[THREADS / 32];
+  const int t = threadIdx.x;
+  uint4 wq[VPT], bq[VPT];
+  Tile::load(W, n_cols, t, wq);
+  Tile::load(B, n_cols, t, bq);
+  const float fn = (float)n_cols;
+  for (long long row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
+    // Keep weight and bias packed: without this the compiler hoists their
+    // fp32 expansion out of the row loop and triples their register cost.
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      asm volatile("" : "+r"(wq[v].x), "+r"(wq[v].y), "+r"(wq[v].z), "+r"(wq[v].w));
+      asm volatile("" : "+r"(bq[v].x), "+r"(bq[v].y), "+r"(bq[v].z), "+r"(bq[v].w));
+    }
+    uint4 xq[VPT];
+    Tile::load(X + row * xs, n_cols, t, xq);
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float x[EPV];
+      Io<T>::unpack(xq[v], x);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) s += x[k];  // lanes >= n_cols hold 0
+    }
+    s = row_reduce<THREADS, false>(s, red);
+    const float mean = s / fn;
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float x[EPV];
+      Io<T>::unpack(xq[v], x);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) {
+        const float d = (Tile::col(v, k, t) < n_cols) ? x[k] - mean : 0.f;
+        q += d * d;
+      }
+    }
+    q = row_reduce<THREADS, false>(q, red);
+    const float var = q / fn;
+    const float rstd = 1.0f / sqrtf(var + eps);
+    if (t == 0) {
+      if (Mean) Mean[row] = mean;
+      if (Rstd) Rstd[row] = rstd;
+    }
+    T *dst = Y + row * ys;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float x[EPV], w[EPV], b[EPV], y[EPV];
+      Io<T>::unpack(xq[v], x);
+      Io<T>::unpack(wq[v], w);
+      Io<T>::unpack(bq[v], b);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) y[k] = ((x[k] - mean) * rstd) * w[k] + b[k];
+      if (ALIGNED && Tile::col(v, EPV - 1, t) < n_cols) {
+        *reinterpret_cast<uint4 *>(dst + Tile::col(v, 0, t)) = Io<T>::pack(y);
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPV; ++k)
+          if (Tile::col(v, k, t) < n_cols) Io<T>::st(dst + Tile::col(v, k, t), y[k]);
+      }
+    }
+  }
+}
+
+template <typename T, int THREADS, int VPT>
+static int launch_ln(const void *x, void *y, const void *w, const void *b, float *mean, float *rstd,
+                     long long xs, long long ys, int n_cols, float eps, long long row_lo,
+                     long long row_hi, bool aligned, cudaStream_t s) {
+  const long long rows = row_hi - row_lo;
+  int per_sm = 0;
+  if (aligned) {
+    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, layernorm_fwd_kernel<T, THREADS, VPT, true>, THREADS, 0));
+  } else {
+    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, layernorm_fwd_kernel<T, THREADS, VPT, false>, THREADS, 0));
+  }
+  if (per_sm < 1) per_sm = 1;
+  long long ctas = (long long)sm_count() * per_sm;
+  if (ctas > rows) ctas = rows;
+  if (aligned)
+    layernorm_fwd_kernel<T, THREADS, VPT, true><<<(unsigned)ctas, THREADS, 0, s>>>(
+        (const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys, n_cols, eps, row_lo, row_hi);
+  else
+    layernorm_fwd_kernel<T, THREADS, VPT, false><<<(unsigned)ctas, THREADS, 0, s>>>(
+        (const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys, n_cols, eps, row_lo, row_hi);
+  TSB_LAUNCH_OK("layernorm_fwd_kernel");
+  return TSB_OK;
+}
+
+template <typename T>
+static int dispatch_ln(const void *x, void *y, const void *w, const void *b, float *mean, float *rstd,
+                       long long xs, long long ys, long long n_cols, float eps, long long row_lo,
+                       long long row_hi, cudaStream_t s) {
+  constexpr int EPV = Io<T>::EPV;
+  const long long vb = 16;
+  const bool aligned = ((uintptr_t)x % vb) == 0 && ((uintptr_t)y % vb) == 0 && ((uintptr_t)w % vb) == 0 &&
+                       ((uintptr_t)b % vb) == 0 && xs % EPV == 0 && ys % EPV == 0;
+  const long long vecs = (n_cols + EPV - 1) / EPV;  // 16-byte vectors per row
+  const int n = (int)n_cols;
+#define TSB_LN(THREADS, VPT) \
+  return launch_ln<T, THREADS, VPT>(x, y, w, b, mean, rstd, xs, ys, n, eps, row_lo, row_hi, aligned, s)
+  if (vecs <= 32) TSB_LN(32, 1);
+  if (vecs <= 64) TSB_LN(64, 1);
+  if (vecs <= 128) TSB_LN(128, 1);
+  if (vecs <= 256) TSB_LN(256, 1);
+  if (vecs <= 512) TSB_LN(256, 2);
+  if (vecs <= 1024) TSB_LN(256, 4);
+  if (vecs <= 2048) TSB_LN(512, 4);
+  if (vecs <= 4096) TSB_LN(1024, 4);
+#undef TSB_LN
+  return fail(TSB_ERR_UNSUPPORTED, "tsb_layernorm_fwd: rows of %lld elements exceed the register-resident limit (%d)",
+              n_cols, 4096 * EPV);
+}
+
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" int tsb_softmax_rows(const void *in, void *out, int32_t dtype, int64_t in_row_stride,
+                                int64_t out_row_stride, int64_t n_cols, int64_t block,
+                                int64_t row_lo, int64_t row_hi, void *stream) {
+  if (!in || !out) return fail(TSB_ERR_INVALID, "tsb_softmax_rows: null pointer");
+  if (dtype != TSB_F32) return fail(TSB_ERR_UNSUPPORTED, "tsb_softmax_rows: only fp32 rows are implemented (dtype %d)", dtype);
+  if (row_lo < 0 || row_hi < row_lo) return fail(TSB_ERR_INVALID, "tsb_softmax_rows: bad row range");
+  if (n_cols < 0 || block <= 0) return fail(TSB_ERR_INVALID, "tsb_softmax_rows: bad n_cols/block");
+  if (row_hi == row_lo) return TSB_OK;
+  // Lanes >= min(n_cols, block) hold -inf and contribute exp(-inf) = 0.
+  const long long n = n_cols < block ? n_cols : block;
+  if (n == 0) return TSB_OK;
+  const bool aligned = ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+                       in_row_stride % 4 == 0 && out_row_stride % 4 == 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const float *i = (const float *)in;
+  float *o = (float *)out;
+#define TSB_SM(TPR, VPT, THREADS) \
+  return launch_softmax<TPR, VPT, THREADS>(i, o, in_row_stride, out_row_stride, (int)n, row_lo, row_hi, aligned, s)
+  if (n <= 128) TSB_SM(32, 1, 256);
+  if (n <= 256) TSB_SM(32, 2, 256);
+  if (n <= 512) TSB_SM(32, 4, 256);
+  if (n <= 1024) TSB_SM(32, 8, 256);
+  if (n <= 2048) TSB_SM(128, 4, 256);
+  if (n <= 4096) TSB_SM(256, 4, 256);
+  if (n <= 8192) TSB_SM(256, 8, 256);
+  if (n <= 16384) TSB_SM(512, 8, 512);
+  if (n <= 32768) TSB_SM(1024, 8, 1024);
+#undef TSB_SM
+  return fail(TSB_ERR_UNSUPPORTED, "tsb_softmax_rows: rows of %lld columns exceed the register-resident limit (32768)", n);
+}
+
+extern "C" int tsb_layernorm_fwd(const void *x, void *y, const void *w, const void *b, float *mean,
+                                 float *rstd, int32_t io_dtype, int64_t x_row_stride,
+                                 int64_t y_row_stride, int64_t n_cols, float eps, int64_t row_lo,
+                                 int64_t row_hi, void *stream) {
+  if (!x || !y || !w || !b) return fail(TSB_ERR_INVALID, "tsb_layernorm_fwd: null pointer");
+  if (row_lo < 0 || row_hi < row_lo || n_cols <= 0) return fail(TSB_ERR_INVALID, "tsb_layernorm_fwd: bad range");
+  if (row_hi == row_lo) return TSB_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (io_dtype) {
+    case TSB_F16: return dispatch_ln<__half>(x, y, w, b, mean, rstd, x_row_stride, y_row_stride, n_cols, eps, row_lo, row_hi, s);
+    case TSB_BF16: return dispatch_ln<__nv_bfloat16>(x, y, w, b, mean, rstd, x_row_stride, y_row_stride, n_cols, eps, row_lo, row_hi, s);
+    case TSB_F32: return dispatch_ln<float>(x, y, w, b, mean, rstd, x_row_stride, y_row_stride, n_cols, eps, row_lo, row_hi, s);
+  }
+  return fail(TSB_ERR_UNSUPPORTED, "tsb_layernorm_fwd: dtype %d", io_dtype);
+}
