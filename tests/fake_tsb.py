@@ -1,0 +1,331 @@
+"""Host-memory stand-in for libtsb200.so, for CPU-only tests of the host logic.
+
+TEST INFRASTRUCTURE.  It lets the plan compiler, the descriptor evaluation and
+the program-range partitioning be exercised end to end without a GPU: the
+Triton driver plugin runs unchanged, but the ctypes library object is replaced
+by ``FakeLib`` whose entry points take the same arguments and execute on host
+pointers.  ``tsb_elementwise`` is emulated in numpy from the descriptors (the
+same definition as include/tsb200.h); the family entry points call the CPU
+oracle with the arguments they were given.  Nothing here is reachable from the
+product package.
+"""
+import ctypes
+import struct
+
+import numpy as np
+
+import oracle
+from triton_shared_b200.backend import runtime as rt
+
+_NP = {0: np.float32, 1: np.float16, 2: np.uint16, 3: np.int32, 4: np.int16, 5: np.int8, 6: np.uint8,
+       9: np.uint32, 10: np.uint16, 11: np.uint8}
+_SIZE = {0: 4, 1: 2, 2: 2, 3: 4, 4: 2, 5: 1, 6: 1, 9: 4, 10: 2, 11: 1}
+_OPNAME = {v: k for k, v in rt.OPCODES.items()}
+_CMPF = {v: k for k, v in rt.CMPF.items()}
+_CMPI = {v: k for k, v in rt.CMPI.items()}
+
+
+def _host_array(addr, nbytes):
+    return np.ctypeslib.as_array((ctypes.c_uint8 * nbytes).from_address(addr))
+
+
+def _bf16_to_f32(u16):
+    return (u16.astype(np.uint32) << 16).view(np.float32)
+
+
+def _f32_to_bf16(f):
+    u = f.astype(np.float32).view(np.uint32)
+    lsb = (u >> 16) & 1
+    return ((u + 0x7fff + lsb) >> 16).astype(np.uint16)
+
+
+def _round_to(f, dt):
+    if dt == 1:
+        return f.astype(np.float16).astype(np.float32)
+    if dt == 2:
+        return _bf16_to_f32(_f32_to_bf16(f))
+    return f.astype(np.float32)
+
+
+def _is_float(dt):
+    return dt in (0, 1, 2)
+
+
+class HostMemory:
+    """Replacement for the driver's device-memory provider: plain host arrays."""
+
+    def __init__(self):
+        self._scratch = None
+        self._tables = {}
+        self._status = np.zeros(4, dtype=np.int32)
+
+    def scratch(self, nbytes):
+        if self._scratch is None or self._scratch.size < nbytes:
+            self._scratch = np.zeros(max(nbytes, 1024), dtype=np.uint8)
+        return self._scratch.ctypes.data
+
+    def table(self, key, host):
+        t = self._tables.get(key)
+        if t is None:
+            t = self._tables[key] = np.ascontiguousarray(host)
+        return t.ctypes.data
+
+    def status(self):
+        return self._status.ctypes.data
+
+    def read_status(self):
+        return self._status.tolist()
+
+
+class FakeLib:
+    """Same entry points as libtsb200.so, executing on host memory."""
+
+    def __init__(self):
+        self.calls = []
+        self._err = b""
+
+    def tsb_last_error(self):
+        return self._err
+
+    def tsb_version(self):
+        return 1000
+
+    def tsb_sm_count(self):
+        return 148
+
+    # ---------------------------------------------------------------- generic engine
+    def tsb_elementwise(self, accs, n_acc, ops, n_ops, grid, pid_lo, pid_hi, stream):
+        self.calls.append(("tsb_elementwise", pid_lo, pid_hi))
+        g = [max(int(grid[i]), 1) for i in range(3)]
+        rank = accs[0].rank
+        sizes = [int(accs[0].sizes[d]) for d in range(rank)]
+        lanes = int(np.prod(sizes))
+        idx = np.unravel_index(np.arange(lanes), sizes)
+        for prog in range(pid_lo, pid_hi):
+            p = (prog % g[0], (prog // g[0]) % g[1], prog // (g[0] * g[1]))
+            state = []
+            for a in range(n_acc):
+                A = accs[a]
+                off = A.offset0 + sum(A.offset_pid[k] * p[k] for k in range(3))
+                valid = np.ones(lanes, dtype=bool)
+                elem = np.full(lanes, off, dtype=np.int64)
+                for d in range(rank):
+                    elem = elem + idx[d] * A.strides[d]
+                    if A.masked[d]:
+                        st = A.mask_start0[d] + sum(A.mask_start_pid[d][k] * p[k] for k in range(3))
+                        dim = max(min(st + sizes[d], A.mask_bound[d]), st) - st
+                        valid &= idx[d] < dim
+                state.append((elem, valid))
+            regs = {}
+            for k in range(n_ops):
+                o = ops[k]
+                name = _OPNAME[o.opcode]
+                if name == "load":
+                    A = accs[o.a]
+                    elem, valid = state[o.a]
+                    if A.is_store == 2:
+                        regs[o.dst] = valid.astype(np.uint32)
+                    elif A.is_store == 3:
+                        regs[o.dst] = elem.astype(np.int64).astype(np.uint32)
+                    else:
+                        regs[o.dst] = self._load(A, elem, valid)
+                elif name == "store":
+                    A = accs[o.a]
+                    elem, valid = state[o.a]
+                    self._store(A, elem, valid, regs[o.b])
+                else:
+                    regs[o.dst] = self._alu(name, o, regs, lanes)
+        return 0
+
+    @staticmethod
+    def _mem(A, elem):
+        es = _SIZE[A.dtype]
+        return es
+
+    def _load(self, A, elem, valid):
+        es = _SIZE[A.dtype]
+        out = np.zeros(elem.shape, dtype=np.uint32)
+        fill = np.uint64(A.other_bits) if A.has_other else np.uint64(0)
+        raw = np.zeros(elem.shape, dtype=np.uint64)
+        for i in np.nonzero(valid)[0]:
+            b = _host_array(A.base + int(elem[i]) * es, es)
+            raw[i] = int.from_bytes(b.tobytes(), "little")
+        raw[~valid] = fill
+        return self._to_reg(raw, A.dtype)
+
+    @staticmethod
+    def _to_reg(raw, dt):
+        if dt in (0, 3, 9):
+            return raw.astype(np.uint32)
+        if dt == 1:
+            return raw.astype(np.uint16).view(np.float16).astype(np.float32).view(np.uint32)
+        if dt == 2:
+            return _bf16_to_f32(raw.astype(np.uint16)).view(np.uint32)
+        if dt == 4:
+            return raw.astype(np.uint16).view(np.int16).astype(np.int32).view(np.uint32)
+        if dt == 5:
+            return raw.astype(np.uint8).view(np.int8).astype(np.int32).view(np.uint32)
+        return raw.astype(np.uint32)
+
+    def _store(self, A, elem, valid, reg):
+        es = _SIZE[A.dtype]
+        dt = A.dtype
+        if dt in (0, 3, 9):
+            bits = reg.astype(np.uint32)
+        elif dt == 1:
+            bits = reg.view(np.float32).astype(np.float16).view(np.uint16)
+        elif dt == 2:
+            bits = _f32_to_bf16(reg.view(np.float32))
+        elif dt == 6:
+            bits = (reg & 1).astype(np.uint8)
+        else:
+            bits = reg.astype(np.uint32)
+        for i in np.nonzero(valid)[0]:
+            dst = _host_array(A.base + int(elem[i]) * es, es)
+            dst[:] = np.frombuffer(int(bits[i]).to_bytes(8, "little")[:es], dtype=np.uint8)
+
+    def _alu(self, name, o, R, lanes):
+        dt = o.type
+        f = lambda r: R[r].view(np.float32)
+        i = lambda r: R[r].view(np.int32)
+        u = lambda r: R[r]
+        with np.errstate(all="ignore"):
+            if name == "const":
+                return np.full(lanes, o.imm, dtype=np.uint32)
+            if name == "mov":
+                return R[o.a].copy()
+            fb = {"addf": np.add, "subf": np.subtract, "mulf": np.multiply, "divf": np.divide,
+                  "maxnumf": np.fmax, "minnumf": np.fmin, "maximumf": np.maximum, "minimumf": np.minimum,
+                  "remf": np.fmod}
+            if name in fb:
+                return _round_to(fb[name](f(o.a), f(o.b)).astype(np.float32), dt).view(np.uint32)
+            fu = {"exp": np.exp, "exp2": np.exp2, "log": np.log, "log2": np.log2, "sqrt": np.sqrt,
+                  "sin": np.sin, "cos": np.cos, "tanh": np.tanh, "absf": np.abs, "negf": np.negative,
+                  "floor": np.floor, "ceil": np.ceil}
+            if name in fu:
+                return _round_to(fu[name](f(o.a)).astype(np.float32), dt).view(np.uint32)
+            if name == "rsqrt":
+                return _round_to((np.float32(1) / np.sqrt(f(o.a))).astype(np.float32), dt).view(np.uint32)
+            if name == "erf":
+                import math
+                return _round_to(np.array([math.erf(x) for x in f(o.a)], dtype=np.float32), dt).view(np.uint32)
+            if name == "fma":
+                r = (f(o.a).astype(np.float64) * f(o.b).astype(np.float64) + f(o.c).astype(np.float64))
+                return _round_to(r.astype(np.float32), dt).view(np.uint32)
+            ib = {"addi": lambda a, b: a + b, "subi": lambda a, b: a - b, "muli": lambda a, b: a * b,
+                  "andi": lambda a, b: a & b, "ori": lambda a, b: a | b, "xori": lambda a, b: a ^ b}
+            if name in ib:
+                return self._wrap(ib[name](u(o.a).astype(np.uint64), u(o.b).astype(np.uint64)).astype(np.uint32), dt)
+            if name in ("divsi", "remsi", "minsi", "maxsi"):
+                a, b = i(o.a).astype(np.int64), i(o.b).astype(np.int64)
+                bz = np.where(b == 0, 1, b)
+                q = np.abs(a) // np.abs(bz) * np.sign(a) * np.sign(bz)
+                r = {"divsi": q, "remsi": a - q * bz, "minsi": np.minimum(a, b), "maxsi": np.maximum(a, b)}[name]
+                return self._wrap(r.astype(np.int32).view(np.uint32), dt)
+            if name == "absi":
+                return self._wrap(np.abs(i(o.a)).view(np.uint32), dt)
+            if name == "cmpf":
+                a, b = f(o.a), f(o.b)
+                un = np.isnan(a) | np.isnan(b)
+                pred = _CMPF[o.imm]
+                base = {"eq": a == b, "gt": a > b, "ge": a >= b, "lt": a < b, "le": a <= b, "ne": a != b,
+                        "rd": np.ones_like(un), "no": np.zeros_like(un)}[pred[1:]]
+                r = (~un & base) if pred[0] == "o" else (un | base)
+                if pred == "ord":
+                    r = ~un
+                if pred == "uno":
+                    r = un
+                return r.astype(np.uint32)
+            if name == "cmpi":
+                pred = _CMPI[o.imm]
+                a, b = (i(o.a), i(o.b)) if pred[0] == "s" or pred in ("eq", "ne") else (u(o.a), u(o.b))
+                r = {"eq": a == b, "ne": a != b, "lt": a < b, "le": a <= b, "gt": a > b, "ge": a >= b}[pred[-2:]]
+                return r.astype(np.uint32)
+            if name == "select":
+                return np.where((R[o.a] & 1) != 0, R[o.b], R[o.c])
+            if name == "bitcast":
+                return R[o.a].copy()
+            if name == "cast":
+                src, mode = int(o.imm), int(o.imm2)
+                if _is_float(src) and _is_float(dt):
+                    return _round_to(f(o.a), dt).view(np.uint32)
+                if not _is_float(src) and _is_float(dt):
+                    v = u(o.a).astype(np.float64) if (mode == 1 or src in (9, 10, 11, 6)) else i(o.a).astype(np.float64)
+                    return _round_to(v.astype(np.float32), dt).view(np.uint32)
+                if _is_float(src) and not _is_float(dt):
+                    return self._wrap(np.trunc(f(o.a)).astype(np.int64).astype(np.uint32), dt)
+                v = u(o.a)
+                if mode == 1:
+                    v = v & {1: 0xff, 2: 0xffff, 4: 0xffffffff}[_SIZE[src]]
+                    if src == 6:
+                        v = v & 1
+                return self._wrap(v.astype(np.uint32), dt)
+        raise NotImplementedError(name)
+
+    @staticmethod
+    def _wrap(x, dt):
+        x = x.astype(np.uint32)
+        if dt == 4:
+            return x.astype(np.uint16).view(np.int16).astype(np.int32).view(np.uint32)
+        if dt == 10:
+            return x & 0xffff
+        if dt == 5:
+            return x.astype(np.uint8).view(np.int8).astype(np.int32).view(np.uint32)
+        if dt == 11:
+            return x & 0xff
+        if dt == 6:
+            return x & 1
+        return x
+
+    def tsb_block_copy(self, src, dst, grid, pid_lo, pid_hi, stream):
+        raise NotImplementedError
+
+    # ---------------------------------------------------------------- families -> oracle
+    def tsb_softmax_rows(self, inp, out, dtype, is_, os_, n_cols, block, row_lo, row_hi, stream):
+        self.calls.append(("tsb_softmax_rows", row_lo, row_hi))
+        oracle.lib().orc_softmax(out, inp, is_, os_, n_cols, block, row_lo, row_hi, 1)
+        return 0
+
+    def tsb_layernorm_fwd(self, x, y, w, b, mean, rstd, dt, xs, ys, n, eps, row_lo, row_hi, stream):
+        self.calls.append(("tsb_layernorm_fwd", row_lo, row_hi))
+        assert xs == ys
+        oracle.lib().orc_layernorm_fwd(x, y, w, b, mean, rstd, xs, n, eps, 1024, {0: 0, 1: 1, 2: 2}[dt], row_lo, row_hi, 1)
+        return 0
+
+    def tsb_reduce_rows_scratch_bytes(self, n_rows, n_valid, sm, sn):
+        return 4 * n_rows if sm == 1 else 0
+
+    def tsb_reduce_rows(self, x, out, sm, sn, out_stride, n_valid, row_lo, row_hi, scratch, stream):
+        self.calls.append(("tsb_reduce_rows", row_lo, row_hi))
+        assert out_stride == 1
+        oracle.lib().orc_reduce_rows(x, out, row_hi, n_valid, sm, sn, 1, 64, row_lo, row_hi, 1)
+        return 0
+
+    def tsb_reduce_all(self, x, out, n, stride, stream):
+        self.calls.append(("tsb_reduce_all", 0, 1))
+        assert stride == 1
+        oracle.lib().orc_reduce_all(x, out, n, 1024)
+        return 0
+
+    def tsb_gemm(self, a, b, c, dt, M, N, K, sam, sak, sbk, sbn, scm, scn, bm, bn, bk, tiles, n_prog, lo, hi,
+                 status, stream):
+        self.calls.append(("tsb_gemm", lo, hi))
+        oracle.lib().orc_matmul(a, b, c, {1: 1, 2: 2}[dt], M, N, K, sam, sak, sbk, sbn, scm, scn, bm, bn, bk,
+                                tiles, lo, hi, 1)
+        return 0
+
+
+class fake_device:
+    """Context manager: route the driver plugin to FakeLib + host memory."""
+
+    def __enter__(self):
+        from triton_shared_b200.backend.driver import B200Launcher
+        self._old_lib, self._old_mem = rt._lib, B200Launcher.memory
+        self.lib = rt._lib = FakeLib()
+        B200Launcher.memory = HostMemory()
+        return self.lib
+
+    def __exit__(self, *exc):
+        from triton_shared_b200.backend.driver import B200Launcher
+        rt._lib, B200Launcher.memory = self._old_lib, self._old_mem
+        return False

@@ -1,0 +1,128 @@
+"""GPU parity of the tt.dot path against the CPU oracle (rel 1e-2 on 16-bit outputs, fp32 accumulation)."""
+import numpy as np
+import pytest
+import torch
+
+import kernels as K
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def drv(tsb_driver):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return tsb_driver
+
+
+def _bits(t):
+    return t.view(torch.int16).numpy().view(np.uint16)
+
+
+def _to_f32(bits_u16, dtype):
+    t = torch.from_numpy(bits_u16.view(np.int16).copy())
+    return t.view(dtype).float().numpy()
+
+
+def _run(kernel, a, b, BM, BN, BK, GM=8):
+    M, Kd = a.shape
+    N = b.shape[1]
+    c = torch.full((M, N), float("nan"), dtype=a.dtype, device="cuda")
+    grid = (((M + BM - 1) // BM) * ((N + BN - 1) // BN),)
+    kernel[grid](a, b, c, M, N, Kd, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
+                 BLOCK_M=BM, BLOCK_N=BN, BLOCK_K=BK, GROUP_M=GM)
+    torch.cuda.synchronize()
+    return c
+
+
+def _check(c, a, b, oracle_lib, BM, BN, BK, GM=8):
+    dt = oracle_lib.F16 if a.dtype == torch.float16 else oracle_lib.BF16
+    ref = oracle_lib.matmul(_bits(a.cpu().contiguous()), _bits(b.cpu().contiguous()), dt, BM, BN, BK, GM,
+                            threads=oracle_lib.max_threads())
+    ref = _to_f32(ref, a.dtype)
+    got = c.float().cpu().numpy()
+    assert np.isfinite(got).all(), "part of the output was never written"
+    scale = np.abs(ref).max()
+    np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-2 * scale)
+    from triton_shared_b200.backend.driver import B200Launcher
+    st = B200Launcher.memory.read_status()
+    assert st is None or st[0] == 0, f"kernel reported a bounded-wait expiry: {st}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_matmul_512_vs_oracle(drv, oracle_lib, dtype):
+    """BASELINE config 4, CPU-check size: M=N=K=512, blocks 128/256/64."""
+    torch.manual_seed(3)
+    a = (2 * torch.rand(512, 512) - 1).to(dtype).cuda()
+    b = (2 * torch.rand(512, 512) - 1).to(dtype).cuda()
+    c = _run(K.matmul_kernel, a, b, 128, 256, 64)
+    _check(c, a, b, oracle_lib, 128, 256, 64)
+
+
+@pytest.mark.parametrize("M,N,Kd", [(500, 520, 304), (129, 257, 72), (128, 256, 64), (1, 8, 8), (300, 1000, 2048)])
+def test_matmul_ragged_tensor_path(drv, oracle_lib, M, N, Kd):
+    """Masked M/N/K tails on the TMA path (row pitches are multiples of 16 bytes)."""
+    torch.manual_seed(3)
+    a = (2 * torch.rand(M, Kd) - 1).half().cuda()
+    b = (2 * torch.rand(Kd, N) - 1).half().cuda()
+    c = _run(K.matmul_kernel, a, b, 128, 256, 64)
+    _check(c, a, b, oracle_lib, 128, 256, 64)
+
+
+def test_matmul_b_transposed(drv, oracle_lib):
+    """B given K-major (a transposed view): the other shared-memory descriptor form."""
+    torch.manual_seed(3)
+    a = (2 * torch.rand(384, 320) - 1).bfloat16().cuda()
+    bt = (2 * torch.rand(512, 320) - 1).bfloat16().cuda()  # [N, K]
+    b = bt.t()  # [K, N] with strides (1, K)
+    c = _run(K.matmul_kernel, a, b, 128, 128, 64)
+    _check(c, a, b.contiguous(), oracle_lib, 128, 128, 64)
+
+
+def test_matmul_wraparound_kernel(drv, oracle_lib):
+    """The reference's own kernel form: A rows and B columns wrap modulo M and N."""
+    torch.manual_seed(3)
+    a = (2 * torch.rand(200, 128) - 1).half().cuda()
+    b = (2 * torch.rand(128, 264) - 1).half().cuda()
+    c = _run(K.matmul_wrap_kernel, a, b, 128, 256, 64)
+    _check(c, a, b, oracle_lib, 128, 256, 64)
+
+
+@pytest.mark.parametrize("M,N,Kd,BM,BN,BK", [(179, 167, 321, 32, 64, 16), (64, 96, 300, 64, 32, 32)])
+def test_matmul_simt_fallback(drv, oracle_lib, M, N, Kd, BM, BN, BK):
+    """Block shapes and pitches the tensor path cannot take (sizes of python/examples/test_matmul.py:145-157)."""
+    torch.manual_seed(3)
+    a = (2 * torch.rand(M, Kd) - 1).half().cuda()
+    b = (2 * torch.rand(Kd, N) - 1).half().cuda()
+    c = _run(K.matmul_kernel, a, b, BM, BN, BK)
+    _check(c, a, b, oracle_lib, BM, BN, BK)
+
+
+def test_matmul_full_size_property(drv):
+    """8192^3 bf16: sampled rows against an fp32 torch product, and linearity C(2A) == 2 C(A) exactly."""
+    n = 8192
+    torch.manual_seed(3)
+    a = (2 * torch.rand(n, n, device="cuda") - 1).bfloat16()
+    b = (2 * torch.rand(n, n, device="cuda") - 1).bfloat16()
+    c = _run(K.matmul_kernel, a, b, 128, 256, 64)
+    rows = torch.randint(0, n, (64,), device="cuda")
+    ref = a[rows].float() @ b.float()
+    err = (c[rows].float() - ref).abs().max() / ref.abs().max()
+    assert err < 1e-2, err.item()
+    c2 = _run(K.matmul_kernel, a * 2, b, 128, 256, 64)
+    assert torch.equal(c2.float(), c.float() * 2)  # scaling by 2 is exact in bf16 and fp32
+
+
+def test_partitioned_matmul(drv):
+    """Two contiguous program ranges write disjoint tiles and together equal the single launch."""
+    torch.manual_seed(3)
+    a = (2 * torch.rand(1024, 512, device="cuda") - 1).bfloat16()
+    b = (2 * torch.rand(512, 1024, device="cuda") - 1).bfloat16()
+    full = _run(K.matmul_kernel, a, b, 128, 256, 64)
+    parts = torch.zeros_like(full)
+    grid = (8 * 4,)
+    for r in range(2):
+        with drv.partition(r, 2):
+            K.matmul_kernel[grid](a, b, parts, 1024, 1024, 512, 512, 1, 1024, 1, 1024, 1,
+                                  BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
+    assert torch.equal(full, parts)

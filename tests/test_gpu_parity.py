@@ -174,8 +174,17 @@ def test_strided_reduce_vs_oracle(drv, oracle_lib, M, N_total, N_valid, BM, BN):
     tot = torch.zeros(1, dtype=torch.float32, device="cuda")
     K.total_kernel[(1,)](out, tot, M, BLOCK=1024)
     got = out.cpu().numpy()
-    np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-5)
-    np.testing.assert_allclose(tot.cpu().numpy()[0], ref_total, rtol=1e-5, atol=1e-4)
+    _assert_sum_close(got, ref, flat.numpy().reshape(N_total, M)[:N_valid].T)
+    assert abs(tot.cpu().numpy()[0] - ref_total) <= 1e-5 * np.abs(ref).sum()
+
+
+def _assert_sum_close(got, ref, terms, rel=1e-5):
+    """Sums that cancel cannot be compared relative to their own value: both the oracle's
+    left-to-right fold and the GPU's tree differ from the exact sum by O(eps * sum|x|).
+    The stated tolerance (rel 1e-5) is therefore applied to the sum of magnitudes."""
+    scale = np.abs(terms).sum(axis=1)
+    bad = np.abs(got - ref) > rel * scale
+    assert not bad.any(), f"{bad.sum()} row sums off by more than {rel} * sum|x|"
 
 
 def test_row_major_reduce_vs_oracle(drv, oracle_lib):
@@ -186,7 +195,7 @@ def test_row_major_reduce_vs_oracle(drv, oracle_lib):
     ref = oracle_lib.reduce_rows(x.numpy().reshape(-1), M, N - 7, N, 1, 32, 128)
     out = torch.empty(M, dtype=torch.float32, device="cuda")
     K.row_sum_kernel[(triton_cdiv(M, 32),)](x.cuda(), out, M, N - 7, N, 1, BLOCK_M=32, BLOCK_N=128)
-    np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=1e-5, atol=1e-5)
+    _assert_sum_close(out.cpu().numpy(), ref, x.numpy()[:, :N - 7])
 
 
 def test_strided_reduce_full_size_property(drv):
@@ -196,7 +205,8 @@ def test_strided_reduce_full_size_property(drv):
     out = torch.empty(M, device="cuda")
     K.row_sum_kernel[(M // 64,)](flat, out, M, NV, 1, M, BLOCK_M=64, BLOCK_N=64)
     ref = flat.view(N, M)[:NV].double().sum(dim=0)
-    assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-3)
+    scale = flat.view(N, M)[:NV].abs().double().sum(dim=0)
+    assert torch.all((out.double() - ref).abs() <= 1e-5 * scale)
     tot = torch.zeros(1, device="cuda")
     K.total_kernel[(1,)](out, tot, M, BLOCK=1024)
     assert abs(tot.item() - ref.sum().item()) <= 1e-5 * ref.abs().sum().item()

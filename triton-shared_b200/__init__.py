@@ -9,7 +9,7 @@ run on hand-written sm_100a CUDA kernels through the C-ABI library libtsb200.so.
 from triton.backends import Backend, backends
 
 from .backend.compiler import BACKEND_NAME, B200Backend, B200Options, compile_ttir_text
-from .backend.driver import B200Driver, B200Launcher, B200Utils, partition_range
+from .backend.driver import B200Driver, B200Launcher, B200Utils, DevicePtr, partition_range
 from .backend.ttir import UnsupportedTTIR
 from .backend import runtime
 
@@ -27,4 +27,4 @@ def activate(**kwargs) -> B200Driver:
 
 
 __all__ = ["B200Driver", "B200Backend", "B200Options", "B200Launcher", "B200Utils", "UnsupportedTTIR",
-           "activate", "compile_ttir_text", "partition_range", "runtime", "BACKEND_NAME"]
+           "activate", "DevicePtr", "compile_ttir_text", "partition_range", "runtime", "BACKEND_NAME"]

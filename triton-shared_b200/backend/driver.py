@@ -51,21 +51,70 @@ def partition_range(n_programs: int, rank: int, world: int):
     return lo, lo + base + (1 if rank < rem else 0)
 
 
-class _DeviceState:
-    """Per-device scratch owned by the host side (the C library never allocates)."""
+class DevicePtr:
+    """A raw device address that Triton treats as a pointer argument of element type `dtype`
+    (a torch dtype).  Lets a caller hand a kernel a pointer to *virtual* element 0 of an
+    array of which only a shard is resident on this GPU (multi-GPU program ranges)."""
+
+    def __init__(self, address: int, dtype):
+        self.address = int(address)
+        self.dtype = dtype
+
+    def data_ptr(self) -> int:
+        return self.address
+
+
+class TorchDeviceMemory:
+    """Device memory the kernels need beyond inputs and outputs, owned by the host side
+    (the C library never allocates).  One instance per process; state is kept per device."""
 
     def __init__(self):
-        self.scratch = None
-        self.tables = {}
-        self.status = None
+        self._state = {}
+
+    def _dev(self):
+        import torch
+        d = torch.cuda.current_device()
+        st = self._state.get(d)
+        if st is None:
+            st = self._state[d] = {"scratch": None, "tables": {}, "status": None}
+        return st
+
+    def scratch(self, nbytes: int) -> int:
+        import torch
+        st = self._dev()
+        if st["scratch"] is None or st["scratch"].numel() < nbytes:
+            st["scratch"] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device="cuda")
+        return st["scratch"].data_ptr()
+
+    def table(self, key, host: np.ndarray) -> int:
+        import torch
+        st = self._dev()
+        t = st["tables"].get(key)
+        if t is None:
+            if len(st["tables"]) > 32:
+                st["tables"].clear()
+            t = torch.from_numpy(np.ascontiguousarray(host)).to("cuda")
+            st["tables"][key] = t
+        return t.data_ptr()
+
+    def status(self) -> int:
+        import torch
+        st = self._dev()
+        if st["status"] is None:
+            st["status"] = torch.zeros(4, dtype=torch.int32, device="cuda")
+        return st["status"].data_ptr()
+
+    def read_status(self):
+        st = self._dev()
+        return None if st["status"] is None else st["status"].cpu().tolist()
 
 
 class LaunchArgs:
     """What a plan needs from one launch: scalars, floats, pointers, device scratch."""
 
-    def __init__(self, launcher, values):
+    def __init__(self, memory, values):
         self.scalars, self.floats, self._ptrs = {}, {}, {}
-        self._dev = launcher._device_state()
+        self._mem = memory
         for k, (ty, v) in enumerate(values):
             if ty[0] == '*':
                 self._ptrs[k] = v
@@ -90,34 +139,18 @@ class LaunchArgs:
             raise TypeError("data_ptr method of Pointer object must return 64-bit int")
         return p
 
-    # -- device memory the kernels need beyond inputs and outputs (torch caching allocator)
     def scratch(self, nbytes: int, stream) -> int:
-        import torch
-        d = self._dev
-        if d.scratch is None or d.scratch.numel() < nbytes:
-            d.scratch = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device="cuda")
-        return d.scratch.data_ptr()
+        return self._mem.scratch(nbytes)
 
     def device_table(self, key, host: np.ndarray, stream) -> int:
-        import torch
-        d = self._dev
-        t = d.tables.get(key)
-        if t is None:
-            if len(d.tables) > 32:
-                d.tables.clear()
-            t = torch.from_numpy(np.ascontiguousarray(host)).to("cuda", non_blocking=False)
-            d.tables[key] = t
-        return t.data_ptr()
+        return self._mem.table(key, host)
 
     def status_word(self, stream) -> int:
-        import torch
-        d = self._dev
-        if d.status is None:
-            d.status = torch.zeros(4, dtype=torch.int32, device="cuda")
-        return d.status.data_ptr()
+        return self._mem.status()
 
 
 class B200Launcher(object):
+    memory = TorchDeviceMemory()  # provider of scratch/tables/status words (replaceable in tests)
 
     def __init__(self, src, metadata):
         constants = src.constants if hasattr(src, "constants") else dict()
@@ -126,15 +159,6 @@ class B200Launcher(object):
         self.constants = {cst_key(key): value for key, value in constants.items()}
         self.signature = {cst_key(key): value for key, value in src.signature.items()}
         self.order = sorted(self.signature.keys())
-        self._states = {}
-
-    def _device_state(self):
-        import torch
-        dev = torch.cuda.current_device() if torch.cuda.is_available() else -1
-        st = self._states.get(dev)
-        if st is None:
-            st = self._states[dev] = _DeviceState()
-        return st
 
     def __call__(self, gridX, gridY, gridZ, stream, function, kernel_metadata, launch_metadata,
                  launch_enter_hook, launch_exit_hook, *args):
@@ -155,7 +179,7 @@ class B200Launcher(object):
             drv = B200Driver.current
             lo, hi = (0, total) if drv is None else drv.range_for(total)
             if hi > lo:
-                plan.launch(LaunchArgs(self, values), grid, lo, hi, stream or 0)
+                plan.launch(LaunchArgs(B200Launcher.memory, values), grid, lo, hi, stream or 0)
         if launch_exit_hook is not None:
             launch_exit_hook(launch_metadata)
 

@@ -964,7 +964,7 @@ class GemmPlan(Plan):
             "sam": a_wrap.scale * a_wrap.inner_stride if a_wrap else A.strides[0], "sak": A.strides[1],
             "sbk": B.strides[0], "sbn": b_wrap.scale * b_wrap.inner_stride if b_wrap else B.strides[1],
             "scm": st.strides[0], "scn": st.strides[1], "c_off": st.offset,
-            "trip": loop.trip,
+            "trip": loop.trip, "loop": loop.id,
             # K mask: lanes k with start + k < bound (evaluated at it = 0 gives K itself)
             "ka": list(mka) if mka else None, "kb": list(mkb) if mkb else None,
             "am": list(_single_bound(A.mask, 0)) if _single_bound(A.mask, 0) else None,
@@ -986,6 +986,7 @@ class GemmPlan(Plan):
         """Evaluate the plan for concrete scalars: problem sizes, strides and the pid -> tile table."""
         p = self.p
         env = LaunchEnv(args.scalars, grid)
+        env.base[("it", p["loop"])] = 0  # masks and offsets are read at the first K step
         e0 = env.at()
         ev = lambda q: int(q.evaluate(e0))
         BM, BN, BK = p["BM"], p["BN"], p["BK"]
