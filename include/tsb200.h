@@ -109,7 +109,6 @@ enum tsb_opcode {
   TSB_OP_LOAD = 0,   /* dst <- access[a]                               */
   TSB_OP_STORE = 1,  /* access[a] <- reg b                             */
   TSB_OP_CONST = 2,  /* dst <- imm (bit pattern, type)                 */
-  TSB_OP_IOTA = 3,   /* dst <- imm + sum_d i_d * iota_strides (see a)  */
   TSB_OP_MOV = 4,
   /* float binary */
   TSB_OP_ADDF = 10, TSB_OP_SUBF, TSB_OP_MULF, TSB_OP_DIVF,

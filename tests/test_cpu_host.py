@@ -1,0 +1,262 @@
+"""CPU tests of the host side: TTIR -> launch plan, descriptor evaluation at launch, the
+driver plugin surface and program-range partitioning.  Launches run through the real
+Triton JIT and the real driver plugin; only the ctypes library object is replaced by a
+host-memory stand-in (tests/fake_tsb.py), so no GPU is needed."""
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+import triton
+from triton.backends.compiler import GPUTarget
+from triton.compiler import ASTSource
+
+import kernels as K
+import triton_shared_b200 as tsb
+from fake_tsb import fake_device
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TARGET = GPUTarget(tsb.BACKEND_NAME, 100, 32)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _driver():
+    tsb.activate()
+    yield
+
+
+def _family(fn, sig, ce):
+    k = triton.compile(ASTSource(fn, sig, ce), target=TARGET)
+    return json.loads(k.asm["plan"])["family"], k
+
+
+PTR3 = {"a_ptr": "*bf16", "b_ptr": "*bf16", "c_ptr": "*bf16"}
+MM_SIG = dict(PTR3, **{k: "i32" for k in ["M", "N", "K", "stride_am", "stride_bk", "stride_cm"]},
+              **{k: "constexpr" for k in ["stride_ak", "stride_bn", "stride_cn", "BLOCK_M", "BLOCK_N", "BLOCK_K", "GROUP_M"]})
+MM_CE = {"stride_ak": 1, "stride_bn": 1, "stride_cn": 1, "BLOCK_M": 128, "BLOCK_N": 256, "BLOCK_K": 64, "GROUP_M": 8}
+
+
+@pytest.mark.parametrize("fn,sig,ce,family", [
+    (K.add_kernel, {"x_ptr": "*fp32", "y_ptr": "*fp32", "out_ptr": "*fp32", "n_elements": "i32", "BLOCK_SIZE": "constexpr"},
+     {"BLOCK_SIZE": 1024}, "elementwise"),
+    (K.softmax_kernel, {"out_ptr": "*fp32", "in_ptr": "*fp32", "in_row_stride": "i32", "out_row_stride": "i32",
+                        "n_cols": "i32", "BLOCK_SIZE": "constexpr"}, {"BLOCK_SIZE": 1024}, "softmax"),
+    (K.layernorm_fwd_kernel, {"X": "*fp16", "Y": "*fp16", "W": "*fp16", "B": "*fp16", "Mean": "*fp32", "Rstd": "*fp32",
+                              "stride": "i32", "N": "i32", "eps": "fp32", "BLOCK_SIZE": "constexpr"}, {"BLOCK_SIZE": 1024},
+     "layernorm"),
+    (K.matmul_kernel, MM_SIG, MM_CE, "gemm"),
+    (K.matmul_wrap_kernel, MM_SIG, MM_CE, "gemm"),
+    (K.row_sum_kernel, {"x_ptr": "*fp32", "out_ptr": "*fp32", "M": "i32", "N": "i32", "stride_m": "constexpr",
+                        "stride_n": "i32", "BLOCK_M": "constexpr", "BLOCK_N": "constexpr"},
+     {"stride_m": 1, "BLOCK_M": 64, "BLOCK_N": 64}, "reduce_rows"),
+    (K.total_kernel, {"x_ptr": "*fp32", "out_ptr": "*fp32", "n": "i32", "BLOCK": "constexpr"}, {"BLOCK": 1024}, "reduce_all"),
+    (K.gelu_bias_kernel, {"x_ptr": "*fp16", "b_ptr": "*fp16", "out_ptr": "*fp16", "n_cols": "i32", "BLOCK": "constexpr"},
+     {"BLOCK": 256}, "elementwise"),
+])
+def test_kernel_maps_to_family(fn, sig, ce, family):
+    fam, k = _family(fn, sig, ce)
+    assert fam == family
+    assert k.metadata.name == fn.fn.__name__ if hasattr(fn, "fn") else True
+
+
+def test_vec_add_descriptor_matches_reference_lowering():
+    """offsets [pid*1024], sizes [1024], strides [1], mask dim from n: the tts.make_tptr / tts.load of
+    test/Conversion/StructuredToMemref/kernel-01-vector-add.mlir:29-52."""
+    _, k = _family(K.add_kernel, {"x_ptr": "*fp32", "y_ptr": "*fp32", "out_ptr": "*fp32", "n_elements": "i32",
+                                  "BLOCK_SIZE": "constexpr"}, {"BLOCK_SIZE": 1024})
+    p = json.loads(k.asm["plan"])["params"]
+    assert p["space"] == [1024] and len(p["accs"]) == 3
+    for acc, arg in zip(p["accs"], (0, 1, 2)):
+        assert acc["arg"] == arg
+        assert acc["offset"]["$poly"] == [[[["pid", 0]], 1024]]
+        assert acc["strides"][0]["$poly"] == [[[], 1]]
+        start, bound = acc["mask"][0]
+        assert start["$poly"] == [[[["pid", 0]], 1024]] and bound["$poly"] == [[[["arg", 3]], 1]]
+        assert acc["other"] is None
+    assert [o[0] for o in p["ops"]] == ["load", "load", "addf", "store"]
+
+
+def test_unsupported_kernel_is_rejected_at_compile_time():
+    @triton.jit
+    def gather_kernel(x_ptr, idx_ptr, out_ptr, BLOCK: tl_constexpr):
+        offs = tl.arange(0, BLOCK)
+        idx = tl.load(idx_ptr + offs)
+        tl.store(out_ptr + offs, tl.load(x_ptr + idx))
+
+    with pytest.raises(Exception) as e:
+        triton.compile(ASTSource(gather_kernel, {"x_ptr": "*fp32", "idx_ptr": "*i32", "out_ptr": "*fp32", "BLOCK": "constexpr"},
+                                 {"BLOCK": 64}), target=TARGET)
+    assert "structured" in str(e.value) or "fits no" in str(e.value)
+
+
+import triton.language as tl  # noqa: E402  (used by the jit kernel above at compile time)
+tl_constexpr = tl.constexpr
+
+
+# ------------------------------------------------------------------ launches on the host stand-in
+def test_vec_add_end_to_end(oracle_lib):
+    n = 98_432
+    torch.manual_seed(0)
+    x, y = torch.rand(n), torch.rand(n)
+    out = torch.full((n + 32,), -7.0)
+    with fake_device() as lib:
+        K.add_kernel[(97,)](x, y, out, n, BLOCK_SIZE=1024)
+    ref = oracle_lib.vec_add(x.numpy(), y.numpy(), n, 1024)
+    assert np.array_equal(out.numpy()[:n].view(np.uint32), ref.view(np.uint32))
+    assert torch.all(out[n:] == -7.0)
+    assert lib.calls == [("tsb_elementwise", 0, 97)]
+
+
+def test_partitioned_ranges_cover_grid_exactly(oracle_lib):
+    n = 20_000
+    torch.manual_seed(0)
+    x, y = torch.rand(n), torch.rand(n)
+    full = torch.zeros(n)
+    parts = torch.zeros(n)
+    drv = tsb.B200Driver.current
+    with fake_device() as lib:
+        K.add_kernel[(20,)](x, y, full, n, BLOCK_SIZE=1024)
+        for r in range(3):
+            with drv.partition(r, 3):
+                K.add_kernel[(20,)](x, y, parts, n, BLOCK_SIZE=1024)
+    assert torch.equal(full, parts)
+    ranges = [(lo, hi) for name, lo, hi in lib.calls[1:]]
+    assert ranges == [(0, 7), (7, 14), (14, 20)]
+
+
+@pytest.mark.parametrize("total,world", [(97, 2), (97, 8), (5, 8), (2048, 8), (0, 4), (1 << 20, 8)])
+def test_partition_range_properties(total, world):
+    spans = [tsb.partition_range(total, r, world) for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == total
+    for (a, b), (c, d) in zip(spans, spans[1:]):
+        assert b == c and a <= b
+    sizes = [b - a for a, b in spans]
+    assert max(sizes) - min(sizes) <= 1
+
+
+def test_known_answers_through_the_plugin():
+    """Exact vectors of python/examples/test_mask.py:39,58,64 and the 2x+1 answer of
+    test_load_2d_tensor_block.py:76-78, produced by plan + descriptors (host stand-in)."""
+    inp = torch.arange(0, 8, dtype=torch.int32)
+    with fake_device():
+        out = torch.full((8,), -2, dtype=torch.int32)
+        K.masked_other_kernel[(1,)](inp, out)
+        assert out.tolist() == [-1, -1, -1, -1, -2, -2, -2, -2]
+        out = torch.full((8,), -2, dtype=torch.int32)
+        K.scalar_conj_mask_kernel[(1,)](inp, out, 4, 3)
+        assert out.tolist() == [0, 1, 2, 3, -1, -1, -1, -1]
+        out = torch.full((8,), -2, dtype=torch.int32)
+        K.scalar_conj_mask_kernel[(1,)](inp, out, 4, 8)
+        assert out.tolist() == [-1] * 8
+        M, N = 13, 21
+        x = torch.arange(M * N, dtype=torch.int32).reshape(M, N)
+        o2 = torch.full((M, N), -3, dtype=torch.int32)
+        K.affine_2d_kernel[(4, 3)](x, o2, N, 1, M, N, BLOCK_M=4, BLOCK_N=8)
+        assert torch.equal(o2, 2 * x + 1)
+        a = torch.arange(0, 256, dtype=torch.float32)
+        b = torch.arange(1000, 1256, dtype=torch.float32)
+        ae, be = b.clone(), a.clone()
+        K.swap_kernel[(2,)](a, b, BLOCK=128)
+        assert torch.equal(a, ae) and torch.equal(b, be)
+        s = torch.zeros(1000)
+        K.splat_kernel[(4,)](s, 2.5, 1000, BLOCK=256)
+        assert torch.all(s == 2.5)
+
+
+def test_gelu_chain_register_allocation():
+    torch.manual_seed(5)
+    x = torch.randn(5, 300).half()
+    b = torch.randn(300).half()
+    out = torch.zeros_like(x)
+    with fake_device():
+        K.gelu_bias_kernel[(5, 2)](x, b, out, 300, BLOCK=256)
+    ref = torch.nn.functional.gelu(x.float() + b.float(), approximate="tanh")
+    assert torch.allclose(out.float(), ref, rtol=2e-3, atol=2e-3)
+
+
+def test_family_parameters_reach_the_c_abi(oracle_lib):
+    """softmax / layernorm / reductions / matmul: the arguments the plans compute at launch are the
+    ones the oracle needs to reproduce the kernels' results."""
+    with fake_device() as lib:
+        torch.manual_seed(1)
+        base = torch.randn(40, 800)
+        out = torch.full((40, 800), 5.0)
+        K.softmax_kernel[(40,)](out, base, 800, 800, 781, BLOCK_SIZE=1024)
+        np.testing.assert_allclose(out.numpy()[:, :781], oracle_lib.softmax(base.numpy()[:, :781], 1024), rtol=1e-6)
+        assert torch.all(out[:, 781:] == 5.0)
+
+        torch.manual_seed(2)
+        x = torch.randn(6, 2500).half()
+        w = (torch.rand(2500) + 0.5).half()
+        b = (0.1 * torch.randn(2500)).half()
+        y = torch.zeros_like(x)
+        mean, rstd = torch.zeros(6), torch.zeros(6)
+        K.layernorm_fwd_kernel[(6,)](x, y, w, b, mean, rstd, 2500, 2500, 1e-5, BLOCK_SIZE=1024)
+        yr, mr, rr = oracle_lib.layernorm_fwd(x.numpy(), w.numpy(), b.numpy(), 1e-5, 1024)
+        assert np.array_equal(y.numpy(), yr) and np.array_equal(mean.numpy(), mr) and np.array_equal(rstd.numpy(), rr)
+
+        torch.manual_seed(4)
+        flat = torch.randn(512 * 768)
+        rs = torch.zeros(512)
+        K.row_sum_kernel[(8,)](flat, rs, 512, 740, 1, 512, BLOCK_M=64, BLOCK_N=64)
+        tot = torch.zeros(1)
+        K.total_kernel[(1,)](rs, tot, 512, BLOCK=1024)
+        ref = flat.numpy().reshape(768, 512)[:740].astype(np.float64).sum(axis=0)
+        np.testing.assert_allclose(rs.numpy(), ref, rtol=1e-4, atol=1e-4)
+        assert abs(tot.item() - ref.sum()) < 1e-2
+
+        torch.manual_seed(3)
+        a = (2 * torch.rand(200, 128) - 1).half()
+        bm = (2 * torch.rand(128, 264) - 1).half()
+        for kern in (K.matmul_kernel, K.matmul_wrap_kernel):
+            c = torch.zeros(200, 264, dtype=torch.float16)
+            kern[(2 * 2,)](a, bm, c, 200, 264, 128, 128, 1, 264, 1, 264, 1, BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
+            ref = a.float() @ bm.float()
+            assert torch.allclose(c.float(), ref, rtol=1e-2, atol=1e-2)
+    names = [c[0] for c in lib.calls]
+    assert names == ["tsb_softmax_rows", "tsb_layernorm_fwd", "tsb_reduce_rows", "tsb_reduce_all", "tsb_gemm", "tsb_gemm"]
+
+
+# ------------------------------------------------------------------ plugin surface
+def test_driver_surface_matches_reference():
+    """Method set of CPUDriver (backend/driver.py:420-464 in the reference) and launcher call shape."""
+    d = tsb.B200Driver()
+    for name in ["get_benchmarker", "get_device_capability", "get_current_stream", "get_current_device",
+                 "set_current_device", "get_current_target", "get_active_torch_device", "assemble_tensormap_to_arg",
+                 "map_python_to_cpp_type", "is_active"]:
+        assert callable(getattr(d, name))
+    assert d.is_active() is False
+    assert d.binary_ext == "plan" and d.launcher_cls is tsb.B200Launcher
+    assert d.map_python_to_cpp_type("*fp32") == "void*" and d.map_python_to_cpp_type("i32") == "int32_t"
+    t = d.get_current_target()
+    assert tsb.B200Backend.supports_target(t)
+    from triton.backends import backends
+    assert not backends["nvidia"].compiler.supports_target(t)
+    props = d.utils.get_device_properties(0)
+    assert "max_shared_mem" in props
+    with pytest.raises(TypeError):
+        from triton_shared_b200.backend.driver import LaunchArgs
+        LaunchArgs(None, [("*fp32", object())]).pointer(0)
+
+
+def test_c_abi_library_exports_every_declared_symbol():
+    """The shared object loads without a GPU and exports exactly what include/tsb200.h declares."""
+    hdr = open(os.path.join(ROOT, "include", "tsb200.h")).read()
+    declared = set(re.findall(r"\b(tsb_[a-z_0-9]+)\s*\(", hdr))
+    from triton_shared_b200.backend import runtime as rt
+    import ctypes
+    L = ctypes.CDLL(rt.LIB_PATH)
+    for sym in declared:
+        assert hasattr(L, sym), f"{sym} declared in tsb200.h but not exported"
+    assert declared == set(rt.SYMBOLS)
+    assert L.tsb_version() == 1000
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from triton_shared_b200.backend import runtime as rt
+    monkeypatch.setattr(rt, "_lib", None)
+    monkeypatch.setattr(rt, "LIB_PATH", "/nonexistent/libtsb200.so")
+    with pytest.raises(rt.TsbError, match="no fallback"):
+        rt.lib()

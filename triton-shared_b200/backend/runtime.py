@@ -21,7 +21,7 @@ DTYPE_SIZE = {"f32": 4, "f16": 2, "bf16": 2, "i32": 4, "i16": 2, "i8": 1, "i1": 
               "u32": 4, "u16": 2, "u8": 1}
 
 OPCODES = {
-    "load": 0, "store": 1, "const": 2, "iota": 3, "mov": 4,
+    "load": 0, "store": 1, "const": 2, "mov": 4,
     "addf": 10, "subf": 11, "mulf": 12, "divf": 13, "maxnumf": 14, "minnumf": 15, "maximumf": 16,
     "minimumf": 17, "remf": 18,
     "exp": 30, "exp2": 31, "log": 32, "log2": 33, "sqrt": 34, "rsqrt": 35, "sin": 36, "cos": 37,

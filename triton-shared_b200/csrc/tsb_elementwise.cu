@@ -318,14 +318,87 @@ __device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int
 }
 
 // ---- general body: a small register VM ----------------------------------------
+// One pass over the op list for VEC lanes; `ld(access, regs)` and `st(access, regs)`
+// are supplied by the kernel (blocked or flat addressing).
+template <int VEC, typename LoadFn, typename StoreFn>
+__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, LoadFn ld, StoreFn st) {
+  unsigned R[TSB_NUM_REGS][VEC];
+  for (int k = 0; k < n_ops; ++k) {
+    const tsb_op &op = ops[k];
+    const int opc = op.opcode;
+    if (opc == TSB_OP_LOAD) {
+      ld(op.a, R[op.dst]);
+    } else if (opc == TSB_OP_STORE) {
+      st(op.a, R[op.b]);
+    } else if (opc == TSB_OP_CONST) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = op.imm;
+    } else if (opc == TSB_OP_MOV) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = R[op.a][v];
+    } else if (opc >= TSB_OP_ADDF && opc < TSB_OP_EXP) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        R[op.dst][v] = __float_as_uint(round_to(
+            binf(opc, __uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v])), op.type));
+    } else if (opc >= TSB_OP_EXP && opc < TSB_OP_ADDI) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        R[op.dst][v] = __float_as_uint(round_to(unf(opc, __uint_as_float(R[op.a][v])), op.type));
+    } else if (opc == TSB_OP_ABSI) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = wrap_to((unsigned)abs((int)R[op.a][v]), op.type);
+    } else if (opc >= TSB_OP_ADDI && opc < TSB_OP_CMPF) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = wrap_to(bini(opc, R[op.a][v], R[op.b][v]), op.type);
+    } else if (opc == TSB_OP_CMPF) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        R[op.dst][v] = cmpf_(op.imm, __uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v]));
+    } else if (opc == TSB_OP_CMPI) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = cmpi_(op.imm, R[op.a][v], R[op.b][v]);
+    } else if (opc == TSB_OP_SELECT) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = (R[op.a][v] & 1u) ? R[op.b][v] : R[op.c][v];
+    } else if (opc == TSB_OP_CAST) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = cast_(R[op.a][v], (int)op.imm, op.type, op.imm2);
+    } else if (opc == TSB_OP_BITCAST) {
+      // only 32-bit <-> 32-bit bitcasts keep their bits in this representation
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) R[op.dst][v] = R[op.a][v];
+    } else if (opc == TSB_OP_FMA) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        R[op.dst][v] = __float_as_uint(round_to(
+            fmaf(__uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v]), __uint_as_float(R[op.c][v])),
+            op.type));
+    }
+  }
+}
+
+// Program id of a linearised program index (x fastest). 1-D grids skip the divisions.
+__device__ __forceinline__ void split_pid(const int grid[3], long long prog, long long &px, long long &py,
+                                          long long &pz) {
+  if (grid[1] == 1 && grid[2] == 1) {
+    px = prog; py = 0; pz = 0;
+    return;
+  }
+  const unsigned long long gx = (unsigned long long)grid[0], gy = (unsigned long long)grid[1];
+  const unsigned long long q = (unsigned long long)prog / gx;
+  px = (long long)((unsigned long long)prog - q * gx);
+  py = (long long)(q % gy);
+  pz = (long long)(q / gy);
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwParams P) {
   const int items = P.lanes / VEC;
   const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
-    const long long px = prog % P.grid[0];
-    const long long py = (prog / P.grid[0]) % P.grid[1];
-    const long long pz = prog / ((long long)P.grid[0] * P.grid[1]);
+    long long px, py, pz;
+    split_pid(P.grid, prog, px, py, pz);
     ProgState st[TSB_MAX_ACCESSES];
     for (int a = 0; a < P.n_acc; ++a) program_state(P.acc[a], P.size, px, py, pz, st[a]);
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
@@ -333,67 +406,10 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
       const int i2 = l & (P.size[2] - 1);
       const int i1 = (l >> sh1) & (P.size[1] - 1);
       const int i0 = l >> sh0;
-      unsigned R[TSB_NUM_REGS][VEC];
-      for (int k = 0; k < P.n_ops; ++k) {
-        const tsb_op &op = P.ops[k];
-        const int opc = op.opcode;
-        if (opc == TSB_OP_LOAD) {
-          load_vec<VEC>(P.acc[op.a], st[op.a], i0, i1, i2, R[op.dst]);
-        } else if (opc == TSB_OP_STORE) {
-          store_vec<VEC>(P.acc[op.a], st[op.a], i0, i1, i2, R[op.b]);
-        } else if (opc == TSB_OP_CONST) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) R[op.dst][v] = op.imm;
-        } else if (opc == TSB_OP_IOTA) {
-          // value = imm + i_d * imm2 along dim a of the iteration space (i32)
-          const int id = op.a == 0 ? i0 : (op.a == 1 ? i1 : i2);
-#pragma unroll
-          for (int v = 0; v < VEC; ++v)
-            R[op.dst][v] = op.imm + (unsigned)(id + (op.a == 2 ? v : 0)) * op.imm2;
-        } else if (opc == TSB_OP_MOV) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) R[op.dst][v] = R[op.a][v];
-        } else if (opc >= TSB_OP_ADDF && opc < TSB_OP_EXP) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v)
-            R[op.dst][v] = __float_as_uint(round_to(
-                binf(opc, __uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v])), op.type));
-        } else if (opc >= TSB_OP_EXP && opc < TSB_OP_ADDI) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v)
-            R[op.dst][v] = __float_as_uint(round_to(unf(opc, __uint_as_float(R[op.a][v])), op.type));
-        } else if (opc == TSB_OP_ABSI) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) R[op.dst][v] = wrap_to((unsigned)abs((int)R[op.a][v]), op.type);
-        } else if (opc >= TSB_OP_ADDI && opc < TSB_OP_CMPF) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v)
-            R[op.dst][v] = wrap_to(bini(opc, R[op.a][v], R[op.b][v]), op.type);
-        } else if (opc == TSB_OP_CMPF) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v)
-            R[op.dst][v] = cmpf_(op.imm, __uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v]));
-        } else if (opc == TSB_OP_CMPI) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) R[op.dst][v] = cmpi_(op.imm, R[op.a][v], R[op.b][v]);
-        } else if (opc == TSB_OP_SELECT) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) R[op.dst][v] = (R[op.a][v] & 1u) ? R[op.b][v] : R[op.c][v];
-        } else if (opc == TSB_OP_CAST) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) R[op.dst][v] = cast_(R[op.a][v], (int)op.imm, op.type, op.imm2);
-        } else if (opc == TSB_OP_BITCAST) {
-          // only 32-bit <-> 32-bit bitcasts keep their bits in this representation
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) R[op.dst][v] = R[op.a][v];
-        } else if (opc == TSB_OP_FMA) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v)
-            R[op.dst][v] = __float_as_uint(round_to(
-                fmaf(__uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v]), __uint_as_float(R[op.c][v])),
-                op.type));
-        }
-      }
+      vm_exec<VEC>(
+          P.ops, P.n_ops,
+          [&](int a, unsigned(&r)[VEC]) { load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r); },
+          [&](int a, const unsigned(&r)[VEC]) { store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r); });
     }
   }
 }
@@ -417,9 +433,8 @@ __global__ void __launch_bounds__(256) ew_binary_f32_kernel(const __grid_constan
     for (int u = 0; u < U; ++u) {
       long long prog = prog0 + u;
       if (prog >= P.pid_hi) prog = P.pid_hi - 1;  // duplicate work is skipped below
-      const long long px = prog % P.grid[0];
-      const long long py = (prog / P.grid[0]) % P.grid[1];
-      const long long pz = prog / ((long long)P.grid[0] * P.grid[1]);
+      long long px, py, pz;
+      split_pid(P.grid, prog, px, py, pz);
       program_state(A0, P.size, px, py, pz, s0[u]);
       program_state(A1, P.size, px, py, pz, s1[u]);
       program_state(AS, P.size, px, py, pz, ss[u]);
@@ -445,6 +460,132 @@ __global__ void __launch_bounds__(256) ew_binary_f32_kernel(const __grid_constan
         store_vec<VEC>(AS, ss[u], i0, i1, i2, r);
       }
     }
+  }
+}
+
+// ---- flat addressing ------------------------------------------------------------
+// When every access is a unit-stride 1-D block whose offset and mask start advance
+// by exactly the block size per program (the "pid * BLOCK + arange(BLOCK)" idiom on a
+// 1-D grid), lane l of program p is element g = p*BLOCK + l of one flat range: it
+// lives at base + shift + g and is accessible iff g < limit.  The kernels below walk
+// that range with no per-program bookkeeping; results are identical to the blocked
+// kernels.
+struct FlatAcc {
+  char *base;
+  long long shift;
+  long long limit;
+  int dtype, esize, vec_ok, has_other, kind;
+  unsigned other;
+};
+struct FlatParams {
+  FlatAcc acc[TSB_MAX_ACCESSES];
+  tsb_op ops[TSB_MAX_OPS];
+  int n_acc, n_ops;
+  long long g_lo, g_hi;
+};
+
+__device__ __forceinline__ void flat_load(const FlatAcc &A, long long g, unsigned (&out)[4]) {
+  const long long e = A.shift + g;
+  if (A.kind >= 2) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) out[k] = A.kind == 2 ? ((g + k) < A.limit ? 1u : 0u) : (unsigned)(e + k);
+    return;
+  }
+  const char *p = A.base + e * A.esize;
+  if (A.vec_ok && g + 4 <= A.limit) {
+    if (A.esize == 4) {
+      const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(p));
+      out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    } else if (A.esize == 2) {
+      const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(p));
+      unsigned short h[4] = {(unsigned short)(v.x & 0xffff), (unsigned short)(v.x >> 16),
+                             (unsigned short)(v.y & 0xffff), (unsigned short)(v.y >> 16)};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) out[k] = ld_elem(reinterpret_cast<const char *>(&h[k]), A.dtype);
+    } else {
+      const unsigned v = __ldcs(reinterpret_cast<const unsigned *>(p));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        unsigned char b = (unsigned char)(v >> (8 * k));
+        out[k] = ld_elem(reinterpret_cast<const char *>(&b), A.dtype);
+      }
+    }
+    return;
+  }
+  const unsigned fill = A.has_other ? A.other : 0u;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) out[k] = (g + k) < A.limit ? ld_elem(p + k * A.esize, A.dtype) : fill;
+}
+
+__device__ __forceinline__ void flat_store(const FlatAcc &A, long long g, const unsigned (&in)[4]) {
+  char *p = A.base + (A.shift + g) * A.esize;
+  if (A.vec_ok && g + 4 <= A.limit) {
+    if (A.esize == 4) {
+      __stcs(reinterpret_cast<uint4 *>(p), make_uint4(in[0], in[1], in[2], in[3]));
+    } else if (A.esize == 2) {
+      unsigned short h[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) st_elem(reinterpret_cast<char *>(&h[k]), A.dtype, in[k]);
+      __stcs(reinterpret_cast<uint2 *>(p),
+             make_uint2((unsigned)h[0] | ((unsigned)h[1] << 16), (unsigned)h[2] | ((unsigned)h[3] << 16)));
+    } else {
+      unsigned v = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        unsigned char b;
+        st_elem(reinterpret_cast<char *>(&b), A.dtype, in[k]);
+        v |= (unsigned)b << (8 * k);
+      }
+      __stcs(reinterpret_cast<unsigned *>(p), v);
+    }
+    return;
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (g + k < A.limit) st_elem(p + k * A.esize, A.dtype, in[k]);
+}
+
+constexpr int FLAT_UNROLL = 2;
+
+__global__ void __launch_bounds__(256) ew_flat_binary_f32_kernel(const __grid_constant__ FlatParams P) {
+  const int opc = P.ops[2].opcode;
+  const FlatAcc &A0 = P.acc[P.ops[0].a];
+  const FlatAcc &A1 = P.acc[P.ops[1].a];
+  const FlatAcc &AS = P.acc[P.ops[3].a];
+  const long long n_vec = (P.g_hi - P.g_lo) >> 2;
+  const long long step = (long long)gridDim.x * blockDim.x * FLAT_UNROLL;
+  for (long long v0 = (long long)blockIdx.x * blockDim.x * FLAT_UNROLL + threadIdx.x; v0 < n_vec; v0 += step) {
+    unsigned a[FLAT_UNROLL][4], b[FLAT_UNROLL][4];
+#pragma unroll
+    for (int u = 0; u < FLAT_UNROLL; ++u) {
+      const long long v = v0 + u * blockDim.x;
+      if (v < n_vec) {
+        flat_load(A0, P.g_lo + v * 4, a[u]);
+        flat_load(A1, P.g_lo + v * 4, b[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < FLAT_UNROLL; ++u) {
+      const long long v = v0 + u * blockDim.x;
+      if (v < n_vec) {
+        unsigned r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          r[k] = __float_as_uint(binf(opc, __uint_as_float(a[u][k]), __uint_as_float(b[u][k])));
+        flat_store(AS, P.g_lo + v * 4, r);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__ FlatParams P) {
+  const long long n_vec = (P.g_hi - P.g_lo) >> 2;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += step) {
+    const long long g = P.g_lo + v * 4;
+    vm_exec<4>(
+        P.ops, P.n_ops, [&](int a, unsigned(&r)[4]) { flat_load(P.acc[a], g, r); },
+        [&](int a, const unsigned(&r)[4]) { flat_store(P.acc[a], g, r); });
   }
 }
 
@@ -552,8 +693,8 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d stores to a load access", k);
     if (o.opcode != TSB_OP_STORE && (o.dst < 0 || o.dst >= TSB_NUM_REGS))
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, o.dst);
-    const int regs[3] = {is_mem || o.opcode == TSB_OP_CONST || o.opcode == TSB_OP_IOTA ? 0 : o.a,
-                         o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_CONST || o.opcode == TSB_OP_IOTA ? 0 : o.b,
+    const int regs[3] = {is_mem || o.opcode == TSB_OP_CONST ? 0 : o.a,
+                         o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_CONST ? 0 : o.b,
                          (o.opcode == TSB_OP_SELECT || o.opcode == TSB_OP_FMA) ? o.c : 0};
     for (int r = 0; r < 3; ++r)
       if (regs[r] < 0 || regs[r] >= TSB_NUM_REGS)
@@ -565,6 +706,30 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
   P.pid_lo = pid_lo;
   P.pid_hi = pid_hi;
   return TSB_OK;
+}
+
+// Flat form of a launch, when every access follows the pid*BLOCK + lane idiom on a 1-D grid.
+static bool build_flat(const EwParams &P, int vec, FlatParams &F) {
+  if (vec != 4 || P.size[0] != 1 || P.size[1] != 1 || P.grid[1] != 1 || P.grid[2] != 1) return false;
+  const long long B = P.size[2];
+  for (int a = 0; a < P.n_acc; ++a) {
+    const DAcc &d = P.acc[a];
+    if (d.masked & 3) return false;
+    if (d.kind != 2 && (d.stride[2] != 1 || d.off_pid[0] != B)) return false;
+    if ((d.masked & 4) && d.mstart_pid[2][0] != B) return false;
+    FlatAcc &f = F.acc[a];
+    f.base = d.base;
+    f.shift = d.off0;
+    f.limit = (d.masked & 4) ? d.bound[2] - d.mstart0[2] : 0x7fffffffffffffffll;
+    f.dtype = d.dtype; f.esize = d.esize; f.has_other = d.has_other; f.kind = d.kind; f.other = d.other;
+    f.vec_ok = d.kind < 2 && ((uintptr_t)d.base % (4ull * d.esize)) == 0 && d.off0 % 4 == 0;
+  }
+  memcpy(F.ops, P.ops, sizeof(tsb_op) * P.n_ops);
+  F.n_acc = P.n_acc;
+  F.n_ops = P.n_ops;
+  F.g_lo = P.pid_lo * B;
+  F.g_hi = P.pid_hi * B;
+  return true;
 }
 
 static bool is_fast_binary(const tsb_access *acc, const tsb_op *ops, int n_ops) {
@@ -595,6 +760,19 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
   int threads = items >= 256 ? 256 : (items >= 128 ? 128 : (items >= 64 ? 64 : 32));
   const long long max_ctas = (long long)sm_count() * (2048 / threads) * 4;
   cudaStream_t s = (cudaStream_t)stream;
+  static thread_local FlatParams F;
+  if (build_flat(P, vec, F)) {
+    const long long n_vec = (F.g_hi - F.g_lo) / 4;
+    const bool fast = is_fast_binary(acc, ops, n_ops);
+    const long long per_cta = 256ll * (fast ? FLAT_UNROLL : 1);
+    long long ctas = (n_vec + per_cta - 1) / per_cta;
+    const long long cap = (long long)sm_count() * 8 * 4;
+    if (ctas > cap) ctas = cap;
+    if (fast) ew_flat_binary_f32_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
+    else ew_flat_vm_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
+    TSB_LAUNCH_OK("ew_flat_kernel");
+    return TSB_OK;
+  }
   if (is_fast_binary(acc, ops, n_ops)) {
     long long ctas = (n_prog + 1) / 2;
     if (ctas > max_ctas) ctas = max_ctas;
