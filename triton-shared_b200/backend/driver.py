@@ -205,7 +205,10 @@ class B200Utils(object):
     def load_binary(name, kernel_obj, shared, device):
         # same tuple as the reference (backend/driver.py:410-417); `function` is the parsed plan
         rt.lib()  # fail now, loudly, if the CUDA library has not been built
-        return (None, _plan.plan_from_bytes(kernel_obj), None, None, sys.maxsize)
+        plan = _plan.plan_from_bytes(kernel_obj)
+        # `module` must not be None: Triton re-initialises the kernel handles on every launch
+        # while it is (compiler.py `_init_handles`), which would re-parse the plan each time
+        return (plan, plan, None, None, sys.maxsize)
 
 
 class B200Driver(DriverBase):
@@ -217,6 +220,7 @@ class B200Driver(DriverBase):
         self.launcher_cls = B200Launcher
         self.binary_ext = "plan"
         self._range = program_range  # None | (lo, hi) | ("part", rank, world)
+        self._cuda = None
         B200Driver.current = self
 
     # never auto-selected; only through triton.runtime.driver.set_active (reference: driver.py:428-432)
@@ -249,19 +253,23 @@ class B200Driver(DriverBase):
     def get_device_capability(self, device=None):
         return (10, 0)
 
+    def _has_cuda(self):
+        if self._cuda is None:
+            import torch
+            self._cuda = bool(torch.cuda.is_available())
+            if self._cuda:
+                from torch._C import _cuda_getCurrentRawStream
+                self._raw_stream = _cuda_getCurrentRawStream
+                self._cur_dev = torch.cuda.current_device
+        return self._cuda
+
     def get_current_stream(self, device=None):
-        import torch
-        if not torch.cuda.is_available():
+        if not self._has_cuda():
             return 0
-        try:
-            from torch._C import _cuda_getCurrentRawStream
-            return _cuda_getCurrentRawStream(torch.cuda.current_device() if device is None else device)
-        except ImportError:
-            return torch.cuda.current_stream(device).cuda_stream
+        return self._raw_stream(self._cur_dev() if device is None else device)
 
     def get_current_device(self):
-        import torch
-        return torch.cuda.current_device() if torch.cuda.is_available() else 0
+        return self._cur_dev() if self._has_cuda() else 0
 
     def set_current_device(self, device):
         import torch

@@ -223,6 +223,17 @@ class Plan:
     def __init__(self, name: str, params: dict):
         self.name = name
         self.p = params
+        self._memo = {}
+
+    def memo(self, args, grid, compute):
+        """Launch parameters depend only on the scalar arguments and the grid: evaluate once per value set."""
+        key = (tuple(sorted(args.scalars.items())), tuple(sorted(args.floats.items())), tuple(grid))
+        v = self._memo.get(key)
+        if v is None:
+            if len(self._memo) > 64:
+                self._memo.clear()
+            v = self._memo[key] = compute()
+        return v
 
     def to_bytes(self) -> bytes:
         return json.dumps({"family": self.family, "name": self.name, "params": enc(self.p)}).encode()
@@ -631,17 +642,22 @@ class SoftmaxPlan(Plan):
         return SoftmaxPlan(kernel.name, {"in_arg": ld.arg, "out_arg": st.arg, "in_off": ld.offset,
                                          "out_off": st.offset, "n_cols": n_cols, "block": block})
 
-    def launch(self, args, grid, pid_lo, pid_hi, stream):
+    def _resolve(self, args, grid):
         p = self.p
         env = LaunchEnv(args.scalars, grid)
         i0, iinc = env.affine_pid(p["in_off"])
         o0, oinc = env.affine_pid(p["out_off"])
         if any(iinc[1:]) or any(oinc[1:]) or grid[1] * grid[2] != 1:
             raise UnsupportedTTIR("softmax family: rows must be indexed by program_id(0) only")
-        n_cols = int(p["n_cols"].evaluate(env.at()))
+        return i0, iinc[0], o0, oinc[0], int(p["n_cols"].evaluate(env.at()))
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        i0, istride, o0, ostride, n_cols = self.memo(args, grid, lambda: self._resolve(args, grid))
         rc = rt.lib().tsb_softmax_rows(args.pointer(p["in_arg"]) + 4 * i0, args.pointer(p["out_arg"]) + 4 * o0,
-                                       rt.DTYPES["f32"], iinc[0], oinc[0], n_cols, p["block"], pid_lo, pid_hi, stream)
-        rt.check(rc, f"tsb_softmax_rows[{self.name}]")
+                                       rt.DTYPES["f32"], istride, ostride, n_cols, p["block"], pid_lo, pid_hi, stream)
+        if rc:
+            rt.check(rc, f"tsb_softmax_rows[{self.name}]")
 
 
 # --------------------------------------------------------------------------
@@ -740,31 +756,34 @@ class LayerNormPlan(Plan):
             "x_off": base_off, "y_off": yoff, "mean_off": mean_off, "rstd_off": rstd_off, "n": n_poly,
             "eps_arg": b["eps"].attr("arg"), "elem": x1.elem})
 
-    def launch(self, args, grid, pid_lo, pid_hi, stream):
+    def _resolve(self, args, grid):
         p = self.p
         env = LaunchEnv(args.scalars, grid)
         x0, xinc = env.affine_pid(p["x_off"])
         y0, yinc = env.affine_pid(p["y_off"])
         if any(xinc[1:]) or any(yinc[1:]) or grid[1] * grid[2] != 1:
             raise UnsupportedTTIR("layernorm family: rows must be indexed by program_id(0) only")
-        es = rt.DTYPE_SIZE[p["elem"]]
-        mean_p = rstd_p = None
+        offs = {}
         for key in ("mean", "rstd"):
             if p[key] is not None:
                 o0, oinc = env.affine_pid(p[key + "_off"])
                 if oinc[0] != 1:
                     raise UnsupportedTTIR("layernorm family: mean/rstd must be stored at index row")
-                ptr = args.pointer(p[key]) + 4 * o0
-                if key == "mean":
-                    mean_p = ptr
-                else:
-                    rstd_p = ptr
-        n = int(p["n"].evaluate(env.at()))
+                offs[key] = o0
+        return x0, xinc[0], y0, yinc[0], offs, int(p["n"].evaluate(env.at()))
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        p = self.p
+        x0, xs, y0, ys, offs, n = self.memo(args, grid, lambda: self._resolve(args, grid))
+        es = rt.DTYPE_SIZE[p["elem"]]
+        mean_p = args.pointer(p["mean"]) + 4 * offs["mean"] if "mean" in offs else None
+        rstd_p = args.pointer(p["rstd"]) + 4 * offs["rstd"] if "rstd" in offs else None
         rc = rt.lib().tsb_layernorm_fwd(args.pointer(p["x"]) + es * x0, args.pointer(p["y"]) + es * y0,
                                         args.pointer(p["w"]), args.pointer(p["b"]), mean_p, rstd_p,
-                                        rt.DTYPES[p["elem"]], xinc[0], yinc[0], n,
+                                        rt.DTYPES[p["elem"]], xs, ys, n,
                                         float(args.floats[p["eps_arg"]]), pid_lo, pid_hi, stream)
-        rt.check(rc, f"tsb_layernorm_fwd[{self.name}]")
+        if rc:
+            rt.check(rc, f"tsb_layernorm_fwd[{self.name}]")
 
 
 # --------------------------------------------------------------------------
