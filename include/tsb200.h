@@ -233,6 +233,25 @@ int tsb_reduce_rows(const float *x, float *out, int64_t stride_m, int64_t stride
                     void *scratch, void *stream);
 
 /*
+ * tsb_reduce_rows for hosts that cannot allocate device memory (no counterpart in the
+ * reference, which never allocates on a device).  Meant for launchers without an
+ * allocator of their own (plain C / ctypes), for processes whose device memory is
+ * entirely managed by another framework's arena, and for latency-critical loops that
+ * must avoid the device-wide synchronisation cudaMalloc and cudaFree can cause.
+ * The per-split partial sums go to a fixed array in the library's device image:
+ * TSB_REDUCE_STATIC_SCRATCH_BYTES per GPU, resident from library load to process exit.
+ * A shape whose partials need more (see tsb_reduce_rows_scratch_bytes) is refused
+ * with TSB_ERR_UNSUPPORTED.  Same arguments and results as tsb_reduce_rows.
+ * All calls on one device share the array: calls that overlap on the GPU race, so
+ * keep them on one stream or order them with events.  The first call on a device
+ * looks the array's address up and should precede any stream capture.
+ */
+#define TSB_REDUCE_STATIC_SCRATCH_BYTES (2u << 20)
+int tsb_reduce_rows_static(const float *x, float *out, int64_t stride_m, int64_t stride_n,
+                           int64_t out_stride, int64_t n_valid, int64_t row_lo, int64_t row_hi,
+                           void *stream);
+
+/*
  * Full sum of n fp32 values x[i*stride] into out[0] (one program, 1-D block
  * loads + linalg.reduce addf into a rank-0 tensor, reducesum_scalar.mlir:21-31).
  * Deterministic: fixed tree order for given n.

@@ -81,7 +81,7 @@ _lib = None
 # every symbol include/tsb200.h declares
 SYMBOLS = ["tsb_last_error", "tsb_version", "tsb_sm_count", "tsb_elementwise", "tsb_block_copy",
            "tsb_softmax_rows", "tsb_layernorm_fwd", "tsb_reduce_rows_scratch_bytes", "tsb_reduce_rows",
-           "tsb_reduce_all", "tsb_gemm"]
+           "tsb_reduce_rows_static", "tsb_reduce_all", "tsb_gemm"]
 
 
 def lib():
@@ -111,6 +111,8 @@ def lib():
     L.tsb_reduce_rows_scratch_bytes.argtypes = [i64, i64, i64, i64]
     L.tsb_reduce_rows.restype = ctypes.c_int
     L.tsb_reduce_rows.argtypes = [vp, vp, i64, i64, i64, i64, i64, i64, vp, vp]
+    L.tsb_reduce_rows_static.restype = ctypes.c_int
+    L.tsb_reduce_rows_static.argtypes = [vp, vp, i64, i64, i64, i64, i64, i64, vp]
     L.tsb_reduce_all.restype = ctypes.c_int
     L.tsb_reduce_all.argtypes = [vp, vp, i64, i64, vp]
     L.tsb_gemm.restype = ctypes.c_int

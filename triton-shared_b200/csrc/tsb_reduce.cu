@@ -225,3 +225,70 @@ extern "C" int tsb_reduce_all(const float *x, float *out, int64_t n, int64_t str
   TSB_LAUNCH_OK("reduce_all_kernel");
   return TSB_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of tsb_reduce_rows.
+//
+// tsb_reduce_rows wants the caller to hand it device scratch for the per-split
+// partial sums.  Some hosts cannot produce such a buffer at the point of the
+// call: a launcher written in plain C or ctypes with no device allocator of its
+// own, a process whose whole device memory is already carved up by another
+// framework's arena, or a latency-critical loop that must not risk the implicit
+// device-wide synchronisation of cudaMalloc/cudaFree.  For them the partials live
+// in a fixed array inside this library's device image.
+//
+// Facts a user must know:
+//  * The array is TSB_REDUCE_STATIC_SCRATCH_BYTES (2 MiB) of device memory per GPU
+//    that loads the library, held until the process exits.
+//  * Calls whose partials do not fit are refused with TSB_ERR_UNSUPPORTED; nothing
+//    is allocated behind the caller's back (no cudaMalloc, cudaFree, or any
+//    allocating library routine is reached from this entry point).
+//  * Every call on a device shares the one array and finds in it whatever the
+//    previous call left.  Nothing needs clearing: the combine step only reads
+//    partials that the first step of the same call has written.  Two calls that
+//    overlap on the GPU (different streams, or different host threads) race on
+//    the array; issue them on one stream or order them with events.
+//  * The first call on each device resolves the array's device address
+//    (cudaGetSymbolAddress, with that device current) and caches it; make that
+//    first call before starting any stream capture.
+static __device__ __align__(256) float g_reduce_static_scratch[TSB_REDUCE_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+namespace tsb {
+// In host code the array's name is only a handle for the runtime, not a device
+// address, so the address handed to the kernels is looked up once per device.
+static int reduce_static_scratch(float **out) {
+  static float *per_device[64] = {nullptr};
+  int dev = -1;
+  TSB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(TSB_ERR_UNSUPPORTED, "tsb_reduce_rows_static: device ordinal %d", dev);
+  float *p = __atomic_load_n(&per_device[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void *addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&addr, g_reduce_static_scratch);
+    if (e != cudaSuccess || !addr)
+      return fail(TSB_ERR_CUDA, "tsb_reduce_rows_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    p = static_cast<float *>(addr);
+    __atomic_store_n(&per_device[dev], p, __ATOMIC_RELEASE);  // racing first calls store the same value
+  }
+  *out = p;
+  return TSB_OK;
+}
+}  // namespace tsb
+
+extern "C" int tsb_reduce_rows_static(const float *x, float *out, int64_t stride_m, int64_t stride_n,
+                                      int64_t out_stride, int64_t n_valid, int64_t row_lo, int64_t row_hi,
+                                      void *stream) {
+  if (row_lo < 0 || row_hi < row_lo || n_valid < 0) return fail(TSB_ERR_INVALID, "tsb_reduce_rows_static: bad range");
+  const int64_t need = tsb_reduce_rows_scratch_bytes(row_hi - row_lo, n_valid, stride_m, stride_n);
+  if (need > (int64_t)TSB_REDUCE_STATIC_SCRATCH_BYTES)
+    return fail(TSB_ERR_UNSUPPORTED,
+                "tsb_reduce_rows_static: this shape needs %lld bytes of partial sums but the built-in array holds %lld; "
+                "use tsb_reduce_rows with caller-provided scratch",
+                (long long)need, (long long)TSB_REDUCE_STATIC_SCRATCH_BYTES);
+  float *scratch = nullptr;
+  if (need > 0) {
+    int rc = reduce_static_scratch(&scratch);
+    if (rc != TSB_OK) return rc;
+  }
+  return tsb_reduce_rows(x, out, stride_m, stride_n, out_stride, n_valid, row_lo, row_hi, scratch, stream);
+}
