@@ -119,7 +119,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", help="softmax only, or all (adds the secondary workloads)")
+    ap.add_argument("--workload", default="all",
+                    help="which secondary workloads to time after the softmax headline: all, none, or a "
+                         "comma-separated subset of vec_add,layernorm,strided_reduce,matmul")
+    ap.add_argument("--small", action="store_true",
+                    help="reduced sizes (still larger than L2) and 3 timed steps, for profiler captures")
     ap.add_argument("--rows", type=int, default=SOFTMAX_ROWS, help="softmax rows per GPU (smaller for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager plugin launches instead of a replayed CUDA graph")
@@ -271,9 +275,9 @@ def main():
 
     sampler = ClockSampler(local_rank)
     sampler.start()
+    time.sleep(0.3)  # let the sampler deliver its first lines before the timed region
     total_ms, per_launch_ms = timed(softmax_step, args.steps, max(args.warmup, 3), graph=not args.eager)
     eager_ms, _ = timed(softmax_step, args.steps, 3, graph=False)
-    clocks = sampler.stop()
     alg_bytes = rows * cols * 8  # per rank per launch
     value = alg_bytes * world * args.steps / (total_ms * 1e-3) / 1e9
     achieved = alg_bytes / (per_launch_ms * 1e-3) / 1e9
@@ -291,6 +295,7 @@ def main():
     e2e_steps = max(3, min(args.steps, 10))
     e2e_ms, _ = timed(e2e_step, e2e_steps, 3, graph=False)
     e2e_value = alg_bytes * world * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    clocks = sampler.stop()  # sampled across the headline and end-to-end timed regions
     del hx, hy
 
     line = {
@@ -316,9 +321,11 @@ def main():
     torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ secondary workloads
-    if args.workload == "all":
+    names = {"vec_add", "layernorm", "strided_reduce", "matmul"}
+    chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names}
+    if chosen:
         wl = {}
-        steps2, warm2 = 10, 3
+        steps2, warm2 = (3, 3) if args.small else (10, 3)
 
         def record(name, fn, alg, unit_scale, bound, unit, nbuf=1, launches=1, graph=True):
             """fn runs the workload once per rotating buffer set (nbuf passes of `alg` work)."""
@@ -336,72 +343,85 @@ def main():
                                                          "peak_source": f"of {peaks['src']}"},
                         "gpu_launches": steps2 * launches * nbuf, "rotating_buffers": nbuf}
 
-        # masked vector add, 2^30 fp32 per GPU
-        n = ADD_N
-        a = torch.rand(n, device="cuda")
-        b = torch.rand(n, device="cuda")
-        c = torch.empty(n, device="cuda")
-        off = rank * n * 4
-        grid = ((n * world + 1023) // 1024,)
-        def add_step():
-            with drv.partition(rank, world):
-                K.add_kernel[grid](DP(a.data_ptr() - off, torch.float32), DP(b.data_ptr() - off, torch.float32),
-                                   DP(c.data_ptr() - off, torch.float32), n * world, BLOCK_SIZE=1024)
-        record("vec_add", add_step, n * 12, 1e9, "hbm", "GB/s")
-        if "value" in wl["vec_add"]:
-            wl["vec_add"]["result_check"] = bool(torch.equal(c[:1 << 20], a[:1 << 20] + b[:1 << 20]))
-        del a, b, c
-        torch.cuda.empty_cache()
+        def wl_vec_add():
+            # masked vector add, 2^30 fp32 per GPU
+            n = ADD_N >> 3 if args.small else ADD_N
+            a = torch.rand(n, device="cuda")
+            b = torch.rand(n, device="cuda")
+            c = torch.empty(n, device="cuda")
+            off = rank * n * 4
+            grid = ((n * world + 1023) // 1024,)
 
-        # LayerNorm forward 4096 x 8192 fp16 per GPU; 8 rotating buffer sets (134 MB each ~ L2 size)
-        nb = 8
-        xs = [torch.randn(LN_M, LN_N, device="cuda").half() for _ in range(nb)]
-        ys = [torch.empty_like(xs[0]) for _ in range(nb)]
-        w = (torch.rand(LN_N, device="cuda") + 0.5).half()
-        bb = (0.1 * torch.randn(LN_N, device="cuda")).half()
-        mean = torch.empty(LN_M * world, device="cuda")
-        rstd = torch.empty(LN_M * world, device="cuda")
-        lo_ln = rank * LN_M
-        def ln_step():
-            for i in range(nb):
+            def add_step():
                 with drv.partition(rank, world):
-                    K.layernorm_fwd_kernel[(LN_M * world,)](DP(xs[i].data_ptr() - lo_ln * LN_N * 2, torch.float16),
-                                                           DP(ys[i].data_ptr() - lo_ln * LN_N * 2, torch.float16),
-                                                           w, bb, mean, rstd, LN_N, LN_N, 1e-5, BLOCK_SIZE=1024)
-        record("layernorm", ln_step, 4 * LN_M * LN_N + 4 * LN_N + 8 * LN_M, 1e9, "hbm", "GB/s", nbuf=nb)
-        del xs, ys
-        torch.cuda.empty_cache()
+                    K.add_kernel[grid](DP(a.data_ptr() - off, torch.float32), DP(b.data_ptr() - off, torch.float32),
+                                       DP(c.data_ptr() - off, torch.float32), n * world, BLOCK_SIZE=1024)
+            record("vec_add", add_step, n * 12, 1e9, "hbm", "GB/s")
+            if "value" in wl["vec_add"]:
+                wl["vec_add"]["n"] = n
+                wl["vec_add"]["result_check"] = bool(torch.equal(c[:1 << 20], a[:1 << 20] + b[:1 << 20]))
 
-        # strided masked reduction 8192 x 12288 (strides [1, 8192]) masked to 12000 columns + scalar total
-        nb = 4
-        fl = [torch.randn(RED_M * RED_N, device="cuda") for _ in range(nb)]
-        rs = torch.empty(RED_M, device="cuda")
-        tot = torch.zeros(1, device="cuda")
-        def red_step():
-            # every GPU reduces its own 8192-row matrix (weak scaling); the scalar is combined across GPUs
-            for i in range(nb):
-                K.row_sum_kernel[(RED_M // 64,)](fl[i], rs, RED_M, RED_NV, 1, RED_M, BLOCK_M=64, BLOCK_N=64)
-                K.total_kernel[(1,)](rs, tot, RED_M, BLOCK=1024)
-                if world > 1:
-                    dist.all_reduce(tot)
-        record("strided_reduce", red_step, 4 * RED_M * RED_NV + 4 * RED_M + 4, 1e9, "hbm", "GB/s", nbuf=nb, launches=3,
-               graph=(world == 1))
-        del fl
-        torch.cuda.empty_cache()
+        def wl_layernorm():
+            # LayerNorm forward 4096 x 8192 fp16 per GPU; rotating buffer sets (134 MB each is about the L2 size)
+            nb = 2 if args.small else 8
+            m = LN_M * 4 if args.small else LN_M  # one 537 MB pass exceeds L2 by itself in a capture
+            xs = [torch.randn(m, LN_N, device="cuda").half() for _ in range(nb)]
+            ys = [torch.empty_like(xs[0]) for _ in range(nb)]
+            w = (torch.rand(LN_N, device="cuda") + 0.5).half()
+            bb = (0.1 * torch.randn(LN_N, device="cuda")).half()
+            mean = torch.empty(m * world, device="cuda")
+            rstd = torch.empty(m * world, device="cuda")
+            lo_ln = rank * m
 
-        # bf16 matmul 8192^3, blocks 128/256/64, fp32 accumulation
-        A = (2 * torch.rand(MM, MM, device="cuda") - 1).bfloat16()
-        B = (2 * torch.rand(MM, MM, device="cuda") - 1).bfloat16()
-        C = torch.empty(MM, MM, device="cuda", dtype=torch.bfloat16)
-        mm_grid = ((MM // 128) * (MM // 256),)
-        def mm_step():
-            K.matmul_kernel[mm_grid](A, B, C, MM, MM, MM, A.stride(0), A.stride(1), B.stride(0), B.stride(1),
-                                     C.stride(0), C.stride(1), BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
-        record("matmul", mm_step, 2.0 * MM * MM * MM, 1e12, "tensor", "TFLOP/s")
-        if "value" in wl.get("matmul", {}):
-            ref = (A[:256].float() @ B.float())
-            err = (C[:256].float() - ref).abs().max().item() / ref.abs().max().item()
-            wl["matmul"]["result_check_rel_err"] = err
+            def ln_step():
+                for i in range(nb):
+                    with drv.partition(rank, world):
+                        K.layernorm_fwd_kernel[(m * world,)](DP(xs[i].data_ptr() - lo_ln * LN_N * 2, torch.float16),
+                                                            DP(ys[i].data_ptr() - lo_ln * LN_N * 2, torch.float16),
+                                                            w, bb, mean, rstd, LN_N, LN_N, 1e-5, BLOCK_SIZE=1024)
+            record("layernorm", ln_step, 4 * m * LN_N + 4 * LN_N + 8 * m, 1e9, "hbm", "GB/s", nbuf=nb)
+            if "value" in wl["layernorm"]:
+                wl["layernorm"]["rows"] = m
+
+        def wl_strided_reduce():
+            # strided masked reduction 8192 x 12288 (strides [1, 8192]) masked to 12000 columns + scalar total
+            nb = 2 if args.small else 4
+            fl = [torch.randn(RED_M * RED_N, device="cuda") for _ in range(nb)]
+            rs = torch.empty(RED_M, device="cuda")
+            tot = torch.zeros(1, device="cuda")
+
+            def red_step():
+                # every GPU reduces its own 8192-row matrix (weak scaling); the scalar is combined across GPUs
+                for i in range(nb):
+                    K.row_sum_kernel[(RED_M // 64,)](fl[i], rs, RED_M, RED_NV, 1, RED_M, BLOCK_M=64, BLOCK_N=64)
+                    K.total_kernel[(1,)](rs, tot, RED_M, BLOCK=1024)
+                    if world > 1:
+                        dist.all_reduce(tot)
+            record("strided_reduce", red_step, 4 * RED_M * RED_NV + 4 * RED_M + 4, 1e9, "hbm", "GB/s", nbuf=nb,
+                   launches=3, graph=(world == 1))
+
+        def wl_matmul():
+            # bf16 matmul 8192^3, blocks 128/256/64, fp32 accumulation
+            A = (2 * torch.rand(MM, MM, device="cuda") - 1).bfloat16()
+            B = (2 * torch.rand(MM, MM, device="cuda") - 1).bfloat16()
+            C = torch.empty(MM, MM, device="cuda", dtype=torch.bfloat16)
+            mm_grid = ((MM // 128) * (MM // 256),)
+
+            def mm_step():
+                K.matmul_kernel[mm_grid](A, B, C, MM, MM, MM, A.stride(0), A.stride(1), B.stride(0), B.stride(1),
+                                         C.stride(0), C.stride(1), BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
+            record("matmul", mm_step, 2.0 * MM * MM * MM, 1e12, "tensor", "TFLOP/s")
+            if "value" in wl.get("matmul", {}):
+                ref = (A[:256].float() @ B.float())
+                err = (C[:256].float() - ref).abs().max().item() / ref.abs().max().item()
+                wl["matmul"]["result_check_rel_err"] = err
+                wl["matmul"]["roofline"]["frac_of_sustained"] = wl["matmul"]["roofline"]["achieved"] / peaks["tensor_sustained"]
+
+        for name, fn in (("vec_add", wl_vec_add), ("layernorm", wl_layernorm),
+                         ("strided_reduce", wl_strided_reduce), ("matmul", wl_matmul)):
+            if name in chosen:
+                fn()
+                torch.cuda.empty_cache()
         line["workloads"] = wl
 
     # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1)
