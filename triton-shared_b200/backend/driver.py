@@ -246,6 +246,17 @@ class B200Driver(DriverBase):
         finally:
             self._range = old
 
+    @contextlib.contextmanager
+    def program_range(self, lo: int, hi: int):
+        """Launches inside the block run only programs [lo, hi) of each (linearised) grid, e.g. to
+        pipeline one large launch as chunks behind their host-to-device copies."""
+        old = self._range
+        self._range = (int(lo), int(hi))
+        try:
+            yield self
+        finally:
+            self._range = old
+
     def get_benchmarker(self):
         from triton.testing import do_bench
         return do_bench

@@ -545,36 +545,85 @@ __device__ __forceinline__ void flat_store(const FlatAcc &A, long long g, const 
     if (g + k < A.limit) st_elem(p + k * A.esize, A.dtype, in[k]);
 }
 
-constexpr int FLAT_UNROLL = 2;
+constexpr int FLAT_UNROLL = 4;
 
-__global__ void __launch_bounds__(256) ew_flat_binary_f32_kernel(const __grid_constant__ FlatParams P) {
-  const int opc = P.ops[2].opcode;
+// out = OPC(in0, in1) over the flat range.  The leading `interior` vectors lie below
+// every access's limit and all three accesses are aligned fp32, so they run as a bare
+// 16-byte load/load/op/store stream with FLAT_UNROLL independent vectors per thread;
+// the ragged remainder (and any unaligned or narrow access) takes the checked path.
+template <int OPC>
+__device__ __forceinline__ void flat_binary_body(const FlatParams &P) {
   const FlatAcc &A0 = P.acc[P.ops[0].a];
   const FlatAcc &A1 = P.acc[P.ops[1].a];
   const FlatAcc &AS = P.acc[P.ops[3].a];
   const long long n_vec = (P.g_hi - P.g_lo) >> 2;
+  long long interior = 0;
+  if (A0.vec_ok && A1.vec_ok && AS.vec_ok && A0.esize == 4 && A1.esize == 4 && AS.esize == 4) {
+    long long lim = A0.limit < A1.limit ? A0.limit : A1.limit;
+    lim = lim < AS.limit ? lim : AS.limit;
+    interior = (lim - P.g_lo) >> 2;
+    interior = interior < 0 ? 0 : (interior > n_vec ? n_vec : interior);
+  }
+  const long long tid = (long long)blockIdx.x * blockDim.x * FLAT_UNROLL + threadIdx.x;
   const long long step = (long long)gridDim.x * blockDim.x * FLAT_UNROLL;
-  for (long long v0 = (long long)blockIdx.x * blockDim.x * FLAT_UNROLL + threadIdx.x; v0 < n_vec; v0 += step) {
-    unsigned a[FLAT_UNROLL][4], b[FLAT_UNROLL][4];
+  {
+    const float4 *pa = reinterpret_cast<const float4 *>(A0.base + (A0.shift + P.g_lo) * 4);
+    const float4 *pb = reinterpret_cast<const float4 *>(A1.base + (A1.shift + P.g_lo) * 4);
+    float4 *pc = reinterpret_cast<float4 *>(AS.base + (AS.shift + P.g_lo) * 4);
+    long long v0 = tid;
+    for (; v0 + (FLAT_UNROLL - 1) * (long long)blockDim.x < interior; v0 += step) {
+      float4 a[FLAT_UNROLL], b[FLAT_UNROLL];
 #pragma unroll
-    for (int u = 0; u < FLAT_UNROLL; ++u) {
-      const long long v = v0 + u * blockDim.x;
-      if (v < n_vec) {
-        flat_load(A0, P.g_lo + v * 4, a[u]);
-        flat_load(A1, P.g_lo + v * 4, b[u]);
+      for (int u = 0; u < FLAT_UNROLL; ++u) {
+        a[u] = __ldcs(pa + v0 + u * blockDim.x);
+        b[u] = __ldcs(pb + v0 + u * blockDim.x);
+      }
+#pragma unroll
+      for (int u = 0; u < FLAT_UNROLL; ++u) {
+        float4 r;
+        r.x = binf(OPC, a[u].x, b[u].x);
+        r.y = binf(OPC, a[u].y, b[u].y);
+        r.z = binf(OPC, a[u].z, b[u].z);
+        r.w = binf(OPC, a[u].w, b[u].w);
+        __stcs(pc + v0 + u * blockDim.x, r);
       }
     }
-#pragma unroll
+    // this thread's leftover interior vectors of its last, partial group
     for (int u = 0; u < FLAT_UNROLL; ++u) {
-      const long long v = v0 + u * blockDim.x;
-      if (v < n_vec) {
-        unsigned r[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          r[k] = __float_as_uint(binf(opc, __uint_as_float(a[u][k]), __uint_as_float(b[u][k])));
-        flat_store(AS, P.g_lo + v * 4, r);
+      const long long v = v0 + u * (long long)blockDim.x;
+      if (v < interior) {
+        const float4 x = __ldcs(pa + v), y = __ldcs(pb + v);
+        float4 r;
+        r.x = binf(OPC, x.x, y.x);
+        r.y = binf(OPC, x.y, y.y);
+        r.z = binf(OPC, x.z, y.z);
+        r.w = binf(OPC, x.w, y.w);
+        __stcs(pc + v, r);
       }
     }
+  }
+  // checked path for everything at or beyond `interior`
+  const long long gstep = (long long)gridDim.x * blockDim.x;
+  for (long long v = interior + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gstep) {
+    unsigned a[4], b[4], r[4];
+    flat_load(A0, P.g_lo + v * 4, a);
+    flat_load(A1, P.g_lo + v * 4, b);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) r[k] = __float_as_uint(binf(OPC, __uint_as_float(a[k]), __uint_as_float(b[k])));
+    flat_store(AS, P.g_lo + v * 4, r);
+  }
+}
+
+__global__ void __launch_bounds__(256) ew_flat_binary_f32_kernel(const __grid_constant__ FlatParams P) {
+  switch (P.ops[2].opcode) {
+    case TSB_OP_ADDF: flat_binary_body<TSB_OP_ADDF>(P); break;
+    case TSB_OP_SUBF: flat_binary_body<TSB_OP_SUBF>(P); break;
+    case TSB_OP_MULF: flat_binary_body<TSB_OP_MULF>(P); break;
+    case TSB_OP_DIVF: flat_binary_body<TSB_OP_DIVF>(P); break;
+    case TSB_OP_MAXNUMF: flat_binary_body<TSB_OP_MAXNUMF>(P); break;
+    case TSB_OP_MINNUMF: flat_binary_body<TSB_OP_MINNUMF>(P); break;
+    case TSB_OP_MAXIMUMF: flat_binary_body<TSB_OP_MAXIMUMF>(P); break;
+    case TSB_OP_MINIMUMF: flat_binary_body<TSB_OP_MINIMUMF>(P); break;
   }
 }
 

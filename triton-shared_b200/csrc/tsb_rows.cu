@@ -180,11 +180,18 @@ struct RowTile {
   __device__ static __forceinline__ int col(int v, int k, int t) {
     return ALIGNED ? (v * THREADS + t) * EPV + k : (v * EPV + k) * THREADS + t;
   }
+  // shared-memory slot of vector v of thread t (16 bytes each, conflict-free for a warp)
+  __device__ static __forceinline__ void put(T *base, int v, int t, const uint4 &q) {
+    reinterpret_cast<uint4 *>(base)[v * THREADS + t] = q;
+  }
+  __device__ static __forceinline__ uint4 get(const T *base, int v, int t) {
+    return reinterpret_cast<const uint4 *>(base)[v * THREADS + t];
+  }
   __device__ static __forceinline__ void load(const T *src, int n_cols, int t, uint4 q[VPT]) {
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       if (ALIGNED && col(v, EPV - 1, t) < n_cols) {
-        q[v] = __ldg(reinterpret_cast<const uint4 *>(src + col(v, 0, t)));
+        q[v] = __ldcs(reinterpret_cast<const uint4 *>(src + col(v, 0, t)));
       } else {
         float f[EPV];
 #pragma unroll
@@ -195,6 +202,9 @@ struct RowTile {
   }
 };
 
+// Weight and bias are staged once per CTA in shared memory (indexed by column) and the
+// next row's loads are issued before the current row is reduced, so that a CTA always
+// has a full row of 16-byte loads in flight.
 template <typename T, int THREADS, int VPT, bool ALIGNED>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 768 / THREADS : 1))
 layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__restrict__ W,
@@ -203,22 +213,30 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
                      long long row_hi) {
   using Tile = RowTile<T, THREADS, VPT, ALIGNED>;
   constexpr int EPV = Io<T>::EPV;
+  constexpr int COVER = THREADS * VPT * EPV;
+  extern __shared__ __align__(16) unsigned char ln_smem[];
+  T *sw = reinterpret_cast<T *>(ln_smem);
+  T *sb = sw + COVER;
   __shared__ float red[THREADS / 32];
   const int t = threadIdx.x;
-  uint4 wq[VPT], bq[VPT];
-  Tile::load(W, n_cols, t, wq);
-  Tile::load(B, n_cols, t, bq);
-  const float fn = (float)n_cols;
-  for (long long row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
-    // Keep weight and bias packed: without this the compiler hoists their
-    // fp32 expansion out of the row loop and triples their register cost.
+  {
+    uint4 q[VPT];
+    Tile::load(W, n_cols, t, q);
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      asm volatile("" : "+r"(wq[v].x), "+r"(wq[v].y), "+r"(wq[v].z), "+r"(wq[v].w));
-      asm volatile("" : "+r"(bq[v].x), "+r"(bq[v].y), "+r"(bq[v].z), "+r"(bq[v].w));
-    }
-    uint4 xq[VPT];
-    Tile::load(X + row * xs, n_cols, t, xq);
+    for (int v = 0; v < VPT; ++v) Tile::put(sw, v, t, q[v]);
+    Tile::load(B, n_cols, t, q);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) Tile::put(sb, v, t, q[v]);
+  }
+  // each thread reads back only what it wrote: no barrier needed
+  const float fn = (float)n_cols;
+  long long row = row_lo + blockIdx.x;
+  uint4 xq[VPT];
+  if (row < row_hi) Tile::load(X + row * xs, n_cols, t, xq);
+  for (; row < row_hi; row += gridDim.x) {
+    const long long next = row + gridDim.x;
+    uint4 xn[VPT];
+    if (next < row_hi) Tile::load(X + next * xs, n_cols, t, xn);
     float s = 0.f;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
@@ -252,17 +270,21 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
     for (int v = 0; v < VPT; ++v) {
       float x[EPV], w[EPV], b[EPV], y[EPV];
       Io<T>::unpack(xq[v], x);
-      Io<T>::unpack(wq[v], w);
-      Io<T>::unpack(bq[v], b);
+      Io<T>::unpack(Tile::get(sw, v, t), w);
+      Io<T>::unpack(Tile::get(sb, v, t), b);
 #pragma unroll
       for (int k = 0; k < EPV; ++k) y[k] = ((x[k] - mean) * rstd) * w[k] + b[k];
       if (ALIGNED && Tile::col(v, EPV - 1, t) < n_cols) {
-        *reinterpret_cast<uint4 *>(dst + Tile::col(v, 0, t)) = Io<T>::pack(y);
+        __stcs(reinterpret_cast<uint4 *>(dst + Tile::col(v, 0, t)), Io<T>::pack(y));
       } else {
 #pragma unroll
         for (int k = 0; k < EPV; ++k)
           if (Tile::col(v, k, t) < n_cols) Io<T>::st(dst + Tile::col(v, k, t), y[k]);
       }
+    }
+    if (next < row_hi) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) xq[v] = xn[v];
     }
   }
 }
@@ -272,21 +294,31 @@ static int launch_ln(const void *x, void *y, const void *w, const void *b, float
                      long long xs, long long ys, int n_cols, float eps, long long row_lo,
                      long long row_hi, bool aligned, cudaStream_t s) {
   const long long rows = row_hi - row_lo;
+  constexpr int SMEM = 2 * THREADS * VPT * 16;  // weight + bias, one 16-byte vector per (thread, v)
+  auto kt = layernorm_fwd_kernel<T, THREADS, VPT, true>;
+  auto kf = layernorm_fwd_kernel<T, THREADS, VPT, false>;
+  if (SMEM > 48 * 1024) {
+    TSB_CUDA_OK(cudaFuncSetAttribute(kt, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    TSB_CUDA_OK(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  }
   int per_sm = 0;
   if (aligned) {
-    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, layernorm_fwd_kernel<T, THREADS, VPT, true>, THREADS, 0));
+    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kt, THREADS, SMEM));
   } else {
-    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, layernorm_fwd_kernel<T, THREADS, VPT, false>, THREADS, 0));
+    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kf, THREADS, SMEM));
   }
   if (per_sm < 1) per_sm = 1;
+  // resident CTAs, then shrunk so that every CTA walks the same number of rows (+-0)
   long long ctas = (long long)sm_count() * per_sm;
   if (ctas > rows) ctas = rows;
+  const long long rows_per_cta = (rows + ctas - 1) / ctas;
+  ctas = (rows + rows_per_cta - 1) / rows_per_cta;
   if (aligned)
-    layernorm_fwd_kernel<T, THREADS, VPT, true><<<(unsigned)ctas, THREADS, 0, s>>>(
-        (const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys, n_cols, eps, row_lo, row_hi);
+    kt<<<(unsigned)ctas, THREADS, SMEM, s>>>((const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys,
+                                            n_cols, eps, row_lo, row_hi);
   else
-    layernorm_fwd_kernel<T, THREADS, VPT, false><<<(unsigned)ctas, THREADS, 0, s>>>(
-        (const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys, n_cols, eps, row_lo, row_hi);
+    kf<<<(unsigned)ctas, THREADS, SMEM, s>>>((const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys,
+                                            n_cols, eps, row_lo, row_hi);
   TSB_LAUNCH_OK("layernorm_fwd_kernel");
   return TSB_OK;
 }
