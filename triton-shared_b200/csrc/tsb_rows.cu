@@ -32,6 +32,21 @@ __device__ __forceinline__ float row_reduce(float v, float *smem /* [THREADS/32]
   return r;
 }
 
+// Sum over the whole CTA with a single barrier; the caller alternates between two
+// `smem` buffers so that a buffer is never rewritten while another warp still reads it.
+template <int THREADS>
+__device__ __forceinline__ float row_reduce2(float v, float *smem /* [THREADS/32] */) {
+  v = warp_sum(v);
+  if (THREADS == 32) return v;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = smem[0];
+#pragma unroll
+  for (int k = 1; k < THREADS / 32; ++k) r += smem[k];
+  return r;
+}
+
 // ---------------------------------------------------------------------------
 // softmax, fp32
 // A row is covered by TPR threads x VPT vectors x 4 lanes >= n_cols.
@@ -202,63 +217,87 @@ struct RowTile {
   }
 };
 
-// Weight and bias are staged once per CTA in shared memory (indexed by column) and the
-// next row's loads are issued before the current row is reduced, so that a CTA always
-// has a full row of 16-byte loads in flight.
+// Weight and bias are staged once per CTA in shared memory as fp32 (no per-row
+// conversion), the row is expanded to fp32 registers once, and the next row's 16-byte
+// loads are issued before the current row is reduced, so that a CTA always has a full
+// row in flight.  The kernel is close to issue-bound, so every per-element instruction
+// counts: masks are evaluated per 16-byte vector, not per element.
 template <typename T, int THREADS, int VPT, bool ALIGNED>
-__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 768 / THREADS : 1))
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 768 / THREADS : (THREADS == 512 ? 2 : 1)))
 layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__restrict__ W,
                      const T *__restrict__ B, float *__restrict__ Mean, float *__restrict__ Rstd,
                      long long xs, long long ys, int n_cols, float eps, long long row_lo,
                      long long row_hi) {
   using Tile = RowTile<T, THREADS, VPT, ALIGNED>;
   constexpr int EPV = Io<T>::EPV;
-  constexpr int COVER = THREADS * VPT * EPV;
+  constexpr int SLOTS = THREADS * VPT;  // 16-byte vectors per row
   extern __shared__ __align__(16) unsigned char ln_smem[];
-  T *sw = reinterpret_cast<T *>(ln_smem);
-  T *sb = sw + COVER;
-  __shared__ float red[THREADS / 32];
+  // slot (v, t) holds EPV floats as EPV/4 float4; element group j of the slot sits at
+  // [(j * SLOTS + v * THREADS + t)] so that a warp reads consecutive float4 (no bank conflicts)
+  float4 *sw = reinterpret_cast<float4 *>(ln_smem);
+  float4 *sb = sw + SLOTS * (EPV / 4);
+  // two exchange buffers, used alternately, so that one barrier per reduction suffices:
+  // buffer 0 is next written a full reduction (and its barrier) after its last read
+  __shared__ float red[2][THREADS / 32];
   const int t = threadIdx.x;
   {
     uint4 q[VPT];
     Tile::load(W, n_cols, t, q);
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) Tile::put(sw, v, t, q[v]);
+    for (int v = 0; v < VPT; ++v) {
+      float f[EPV];
+      Io<T>::unpack(q[v], f);
+#pragma unroll
+      for (int j = 0; j < EPV / 4; ++j)
+        sw[j * SLOTS + v * THREADS + t] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+    }
     Tile::load(B, n_cols, t, q);
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) Tile::put(sb, v, t, q[v]);
+    for (int v = 0; v < VPT; ++v) {
+      float f[EPV];
+      Io<T>::unpack(q[v], f);
+#pragma unroll
+      for (int j = 0; j < EPV / 4; ++j)
+        sb[j * SLOTS + v * THREADS + t] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+    }
   }
-  // each thread reads back only what it wrote: no barrier needed
+  // each thread reads back only the slots it wrote: no barrier needed
   const float fn = (float)n_cols;
   long long row = row_lo + blockIdx.x;
   uint4 xq[VPT];
   if (row < row_hi) Tile::load(X + row * xs, n_cols, t, xq);
   for (; row < row_hi; row += gridDim.x) {
+    float x[VPT][EPV];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) Io<T>::unpack(xq[v], x[v]);
     const long long next = row + gridDim.x;
-    uint4 xn[VPT];
-    if (next < row_hi) Tile::load(X + next * xs, n_cols, t, xn);
-    float s = 0.f;
+    if (next < row_hi) Tile::load(X + next * xs, n_cols, t, xq);  // in flight during the reductions
+    // four independent accumulators per thread keep the add/fma chains short
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      float x[EPV];
-      Io<T>::unpack(xq[v], x);
+    for (int v = 0; v < VPT; ++v)
 #pragma unroll
-      for (int k = 0; k < EPV; ++k) s += x[k];  // lanes >= n_cols hold 0
-    }
-    s = row_reduce<THREADS, false>(s, red);
+      for (int k = 0; k < EPV; ++k) s4[k & 3] += x[v][k];  // lanes >= n_cols hold 0
+    const float s = row_reduce2<THREADS>((s4[0] + s4[1]) + (s4[2] + s4[3]), red[0]);
     const float mean = s / fn;
-    float q = 0.f;
+    float q4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      float x[EPV];
-      Io<T>::unpack(xq[v], x);
+      if (Tile::col(v, EPV - 1, t) < n_cols) {
 #pragma unroll
-      for (int k = 0; k < EPV; ++k) {
-        const float d = (Tile::col(v, k, t) < n_cols) ? x[k] - mean : 0.f;
-        q += d * d;
+        for (int k = 0; k < EPV; ++k) {
+          const float d = x[v][k] - mean;
+          q4[k & 3] = fmaf(d, d, q4[k & 3]);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) {
+          const float d = (Tile::col(v, k, t) < n_cols) ? x[v][k] - mean : 0.f;
+          q4[k & 3] = fmaf(d, d, q4[k & 3]);
+        }
       }
     }
-    q = row_reduce<THREADS, false>(q, red);
+    const float q = row_reduce2<THREADS>((q4[0] + q4[1]) + (q4[2] + q4[3]), red[1]);
     const float var = q / fn;
     const float rstd = 1.0f / sqrtf(var + eps);
     if (t == 0) {
@@ -268,12 +307,16 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
     T *dst = Y + row * ys;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      float x[EPV], w[EPV], b[EPV], y[EPV];
-      Io<T>::unpack(xq[v], x);
-      Io<T>::unpack(Tile::get(sw, v, t), w);
-      Io<T>::unpack(Tile::get(sb, v, t), b);
+      float y[EPV];
 #pragma unroll
-      for (int k = 0; k < EPV; ++k) y[k] = ((x[k] - mean) * rstd) * w[k] + b[k];
+      for (int j = 0; j < EPV / 4; ++j) {
+        const float4 w = sw[j * SLOTS + v * THREADS + t];
+        const float4 b = sb[j * SLOTS + v * THREADS + t];
+        y[4 * j + 0] = ((x[v][4 * j + 0] - mean) * rstd) * w.x + b.x;
+        y[4 * j + 1] = ((x[v][4 * j + 1] - mean) * rstd) * w.y + b.y;
+        y[4 * j + 2] = ((x[v][4 * j + 2] - mean) * rstd) * w.z + b.z;
+        y[4 * j + 3] = ((x[v][4 * j + 3] - mean) * rstd) * w.w + b.w;
+      }
       if (ALIGNED && Tile::col(v, EPV - 1, t) < n_cols) {
         __stcs(reinterpret_cast<uint4 *>(dst + Tile::col(v, 0, t)), Io<T>::pack(y));
       } else {
@@ -281,10 +324,6 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
         for (int k = 0; k < EPV; ++k)
           if (Tile::col(v, k, t) < n_cols) Io<T>::st(dst + Tile::col(v, k, t), y[k]);
       }
-    }
-    if (next < row_hi) {
-#pragma unroll
-      for (int v = 0; v < VPT; ++v) xq[v] = xn[v];
     }
   }
 }
@@ -294,7 +333,7 @@ static int launch_ln(const void *x, void *y, const void *w, const void *b, float
                      long long xs, long long ys, int n_cols, float eps, long long row_lo,
                      long long row_hi, bool aligned, cudaStream_t s) {
   const long long rows = row_hi - row_lo;
-  constexpr int SMEM = 2 * THREADS * VPT * 16;  // weight + bias, one 16-byte vector per (thread, v)
+  constexpr int SMEM = 2 * THREADS * VPT * Io<T>::EPV * 4;  // weight + bias as fp32
   auto kt = layernorm_fwd_kernel<T, THREADS, VPT, true>;
   auto kf = layernorm_fwd_kernel<T, THREADS, VPT, false>;
   if (SMEM > 48 * 1024) {
@@ -308,11 +347,9 @@ static int launch_ln(const void *x, void *y, const void *w, const void *b, float
     TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kf, THREADS, SMEM));
   }
   if (per_sm < 1) per_sm = 1;
-  // resident CTAs, then shrunk so that every CTA walks the same number of rows (+-0)
+  // all resident CTAs, so that every SM carries the same number of them
   long long ctas = (long long)sm_count() * per_sm;
   if (ctas > rows) ctas = rows;
-  const long long rows_per_cta = (rows + ctas - 1) / ctas;
-  ctas = (rows + rows_per_cta - 1) / rows_per_cta;
   if (aligned)
     kt<<<(unsigned)ctas, THREADS, SMEM, s>>>((const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys,
                                             n_cols, eps, row_lo, row_hi);
@@ -342,10 +379,11 @@ static int dispatch_ln(const void *x, void *y, const void *w, const void *b, flo
   if (vecs <= 512) TSB_LN(256, 2);
   if (vecs <= 1024) TSB_LN(256, 4);
   if (vecs <= 2048) TSB_LN(512, 4);
-  if (vecs <= 4096) TSB_LN(1024, 4);
+  // weight and bias are held as fp32 in shared memory: 2 * 4 bytes per column, at most 227 KB
+  if (vecs <= 4096 && 2ll * 4096 * EPV * 4 <= 227 * 1024) TSB_LN(1024, 4);
 #undef TSB_LN
-  return fail(TSB_ERR_UNSUPPORTED, "tsb_layernorm_fwd: rows of %lld elements exceed the register-resident limit (%d)",
-              n_cols, 4096 * EPV);
+  return fail(TSB_ERR_UNSUPPORTED, "tsb_layernorm_fwd: rows of %lld elements exceed the on-chip limit (%d)",
+              n_cols, (2ll * 4096 * EPV * 4 <= 227 * 1024 ? 4096 : 2048) * EPV);
 }
 
 }  // namespace tsb
