@@ -211,6 +211,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: this backend has no CPU execution path")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        # keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     drv = triton_shared_b200.activate()
     peaks = measured_peaks()
@@ -425,7 +428,11 @@ def main():
                     if world > 1:
                         dist.all_reduce(tot)
             record("strided_reduce", red_step, 4 * RED_M * RED_NV + 4 * RED_M + 4, 1e9, "hbm", "GB/s", nbuf=nb,
-                   launches=3, graph=(world == 1))
+                   launches=3)
+            if "unavailable" in wl["strided_reduce"] and world > 1:
+                # the all-reduce could not be captured into a graph here: time eager launches instead
+                record("strided_reduce", red_step, 4 * RED_M * RED_NV + 4 * RED_M + 4, 1e9, "hbm", "GB/s", nbuf=nb,
+                       launches=3, graph=False)
 
         def wl_matmul():
             # bf16 matmul 8192^3, blocks 128/256/64, fp32 accumulation
