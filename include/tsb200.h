@@ -83,6 +83,23 @@ enum tsb_error {
  *   (fillWithValue, StructuredToMemref.cpp:192-224); without it those lanes are
  *   unspecified in the reference and read as zero here.
  */
+/*
+ * Wrap-around (modulo) contribution of one dim to an access's address: the element index gains
+ *     scale * ((offset + i_dim * stride) mod modulus),   offset = offset0 + sum_a offset_pid[a]*p[a]
+ * which is what `(pid*BLOCK + arange(BLOCK)) % N` scaled by a stride means in the kernel text.
+ * The reference lowers the same expression to "split pointers" (two contiguous chunks per
+ * block, StructuredToMemref.cpp:263-526); here the modulo is evaluated per lane.
+ */
+typedef struct tsb_wrap {
+  int32_t dim; /* dim of the iteration space */
+  int32_t pad_;
+  int64_t offset0;
+  int64_t offset_pid[3];
+  int64_t stride;
+  int64_t modulus; /* > 0 */
+  int64_t scale;
+} tsb_wrap;
+
 typedef struct tsb_access {
   void *base;
   int32_t dtype; /* enum tsb_dtype of the memory element */
@@ -101,6 +118,9 @@ typedef struct tsb_access {
   int64_t mask_start_pid[TSB_MAX_RANK][3];
   int64_t mask_bound[TSB_MAX_RANK];
   uint64_t other_bits; /* bit pattern of `other` in dtype (low bits) */
+  int32_t n_wrap;      /* 0..2 wrap-around terms added to the address */
+  int32_t pad2_;
+  tsb_wrap wrap[2];
 } tsb_access;
 
 /* Opcodes of the elementwise body (one linalg.generic each in the reference,

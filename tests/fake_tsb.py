@@ -109,6 +109,12 @@ class FakeLib:
                 off = A.offset0 + sum(A.offset_pid[k] * p[k] for k in range(3))
                 valid = np.ones(lanes, dtype=bool)
                 elem = np.full(lanes, off, dtype=np.int64)
+                for w in range(A.n_wrap):
+                    W = A.wrap[w]
+                    wo = W.offset0 + sum(W.offset_pid[k] * p[k] for k in range(3))
+                    inner = wo + idx[W.dim] * W.stride
+                    q = np.abs(inner) // W.modulus * np.sign(inner)
+                    elem = elem + W.scale * (inner - q * W.modulus)  # remainder with the dividend's sign
                 for d in range(rank):
                     elem = elem + idx[d] * A.strides[d]
                     if A.masked[d]:

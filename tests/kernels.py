@@ -210,3 +210,61 @@ def matmul_wrap_kernel(a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_ak, strid
     offs_cn = pid_n * BLOCK_N + tl.arange(0, BLOCK_N)
     c_ptrs = c_ptr + stride_cm * offs_cm[:, None] + stride_cn * offs_cn[None, :]
     tl.store(c_ptrs, c, mask=(offs_cm[:, None] < M) & (offs_cn[None, :] < N))
+
+
+# ---- loops without carried data, and wrap-around (modulo) offsets ---------------------------
+
+@triton.jit
+def grid_stride_copy_kernel(y_ptr, x_ptr, size, iterations, BLOCK_SIZE: tl.constexpr):
+    """Each program copies `iterations` blocks, striding by the whole grid; the index tensor and
+    therefore the mask start are loop-carried (the form of python/examples/test_mask_loop_iter_arg.py)."""
+    idx = tl.program_id(0) * BLOCK_SIZE + tl.arange(0, BLOCK_SIZE)
+    stride = tl.num_programs(0) * BLOCK_SIZE
+    for it in range(iterations):
+        mask = idx < size
+        x = tl.load(x_ptr + idx, mask=mask)
+        tl.store(y_ptr + idx, x * 2.0, mask=mask)
+        idx += stride
+
+
+@triton.jit
+def tile_walk_kernel(in_ptr, out_ptr, stride_m, stride_n, TM: tl.constexpr, TN: tl.constexpr,
+                     NI: tl.constexpr, NJ: tl.constexpr):
+    """Two nested loops walking NI x NJ tiles of TM x TN with loop-carried pointers."""
+    offs_m = tl.arange(0, TM)
+    offs_n = tl.arange(0, TN)
+    a_ptrs = in_ptr + offs_m[:, None] * stride_m + offs_n[None, :] * stride_n
+    c_ptrs = out_ptr + offs_m[:, None] * stride_m + offs_n[None, :] * stride_n
+    for i in range(0, NI):
+        a_row = a_ptrs
+        c_row = c_ptrs
+        for j in range(0, NJ):
+            tl.store(c_row, tl.load(a_row) + 1.0)
+            a_row += TN * stride_n
+            c_row += TN * stride_n
+        a_ptrs += TM * stride_m
+        c_ptrs += TM * stride_m
+
+
+@triton.jit
+def wrap_rows_kernel(a_ptr, c_ptr, M, stride_am, stride_an, stride_cm, stride_cn, START: tl.constexpr,
+                     BM: tl.constexpr, BN: tl.constexpr, STEPS: tl.constexpr):
+    """Rows (START + i) % M of A, column block by column block, into rows i of C: the row index
+    wraps around the matrix ("stacked" wrap-around of python/examples/test_modulo.py:7-52)."""
+    offs_am = (START + tl.arange(0, BM)) % M
+    offs_n = tl.arange(0, BN)
+    a_ptrs = a_ptr + offs_am[:, None] * stride_am + offs_n[None, :] * stride_an
+    c_ptrs = c_ptr + tl.arange(0, BM)[:, None] * stride_cm + offs_n[None, :] * stride_cn
+    for k in range(0, STEPS):
+        tl.store(c_ptrs, tl.load(a_ptrs))
+        a_ptrs += BN * stride_an
+        c_ptrs += BN * stride_cn
+
+
+@triton.jit
+def wrap_cols_kernel(a_ptr, c_ptr, N, row, stride_am, stride_an, stride_cn, START: tl.constexpr, BN: tl.constexpr):
+    """Columns (START + j) % N of one row: the wrap is on the innermost dim
+    ("side-by-side", python/examples/test_modulo.py:55-99)."""
+    offs_an = (START + tl.arange(0, BN)) % N
+    a = tl.load(a_ptr + row * stride_am + offs_an[None, :] * stride_an)
+    tl.store(c_ptr + tl.arange(0, BN)[None, :] * stride_cn, a)

@@ -66,7 +66,9 @@ def test_vec_add_descriptor_matches_reference_lowering():
     test/Conversion/StructuredToMemref/kernel-01-vector-add.mlir:29-52."""
     _, k = _family(K.add_kernel, {"x_ptr": "*fp32", "y_ptr": "*fp32", "out_ptr": "*fp32", "n_elements": "i32",
                                   "BLOCK_SIZE": "constexpr"}, {"BLOCK_SIZE": 1024})
-    p = json.loads(k.asm["plan"])["params"]
+    params = json.loads(k.asm["plan"])["params"]
+    assert params["tree"] == [["seg", 0]] and len(params["segments"]) == 1
+    p = params["segments"][0]
     assert p["space"] == [1024] and len(p["accs"]) == 3
     for acc, arg in zip(p["accs"], (0, 1, 2)):
         assert acc["arg"] == arg
@@ -260,3 +262,45 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(rt, "LIB_PATH", "/nonexistent/libtsb200.so")
     with pytest.raises(rt.TsbError, match="no fallback"):
         rt.lib()
+
+
+# ------------------------------------------------------------------ loops and wrap-around
+def _loop_and_wrap_cases(dev):
+    """Shared by the CPU (host stand-in) and GPU variants: returns a list of (name, got, expected)."""
+    out = []
+    # grid-stride copy with a loop-carried index/mask
+    x = torch.arange(0, 100, dtype=torch.float32, device=dev)
+    y = torch.full((104,), -1.0, device=dev)
+    K.grid_stride_copy_kernel[(3,)](y, x, 100, 5, BLOCK_SIZE=8)
+    exp = torch.full((104,), -1.0)
+    exp[:100] = 2.0 * torch.arange(0, 100, dtype=torch.float32)
+    out.append(("grid_stride_copy", y.cpu(), exp))
+    # nested tile walk
+    a = torch.arange(0, 12 * 20, dtype=torch.float32, device=dev).reshape(12, 20)
+    c = torch.zeros_like(a)
+    K.tile_walk_kernel[(1,)](a, c, 20, 1, TM=4, TN=4, NI=3, NJ=5)
+    out.append(("tile_walk", c.cpu(), a.cpu() + 1.0))
+    # stacked wrap-around: the exact expected matrix of python/examples/test_modulo.py:45-50
+    A = torch.arange(0, 32, dtype=torch.float32, device=dev).reshape(4, 8)
+    C = torch.full((4, 8), 88888.0, device=dev)
+    K.wrap_rows_kernel[(1,)](A, C, 4, 8, 1, 8, 1, START=2, BM=4, BN=4, STEPS=2)
+    exp = torch.tensor([[16, 17, 18, 19, 20, 21, 22, 23], [24, 25, 26, 27, 28, 29, 30, 31],
+                        [0, 1, 2, 3, 4, 5, 6, 7], [8, 9, 10, 11, 12, 13, 14, 15]], dtype=torch.float32)
+    out.append(("wrap_rows", C.cpu(), exp))
+    # side-by-side wrap-around: first row of the expected matrix of test_modulo.py:88-97
+    A = torch.arange(0, 64, dtype=torch.float32, device=dev).reshape(8, 8)
+    C = torch.full((8, 8), 88888.0, device=dev)
+    K.wrap_cols_kernel[(1,)](A, C, 8, 7, 8, 1, 1, START=6, BN=4)
+    exp = torch.full((8, 8), 88888.0)
+    exp[0, :4] = torch.tensor([62.0, 63.0, 56.0, 57.0])
+    out.append(("wrap_cols", C.cpu(), exp))
+    return out
+
+
+def test_loops_and_wraparound_on_host_stand_in():
+    with fake_device() as lib:
+        cases = _loop_and_wrap_cases("cpu")
+    for name, got, exp in cases:
+        assert torch.equal(got, exp), name
+    # 5 loop iterations, 3*5 tile steps, 2 wrap steps, 1 single launch
+    assert len(lib.calls) == 5 + 15 + 2 + 1

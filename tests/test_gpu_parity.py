@@ -333,3 +333,21 @@ def test_partitioned_launch_matches_full(drv, oracle_lib):
         with drv.partition(rank, 2):
             K.add_kernel[(97,)](x, y, parts, n, BLOCK_SIZE=1024)
     assert torch.equal(full, parts)
+
+
+def test_loops_and_wraparound_known_answers(drv):
+    """Loops without carried data (walked on the host) and wrap-around offsets, against the exact
+    expected matrices of python/examples/test_modulo.py:45-50 and :88-97 and plain copies."""
+    from test_cpu_host import _loop_and_wrap_cases
+    for name, got, exp in _loop_and_wrap_cases("cuda"):
+        assert torch.equal(got, exp), name
+
+
+def test_wraparound_large_blocks(drv):
+    """Row wrap-around on vector-width blocks: rows (START + i) % M, 16-byte path on the columns."""
+    M, N = 48, 256
+    A = torch.randn(M, N, device="cuda")
+    C = torch.zeros(64, N, device="cuda")
+    K.wrap_rows_kernel[(1,)](A, C, M, N, 1, N, 1, START=40, BM=64, BN=64, STEPS=4)
+    rows = (40 + torch.arange(64, device="cuda")) % M
+    assert torch.equal(C, A[rows])

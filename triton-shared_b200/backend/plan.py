@@ -274,7 +274,8 @@ class _EwLowering:
         self.nv += 1
         return self.nv - 1
 
-    def acc_for(self, kind: str, elem: str, shape, dimmap, offset: Poly, strides, mask, other, arg=None):
+    def acc_for(self, kind: str, elem: str, shape, dimmap, offset: Poly, strides, mask, other, arg=None,
+                wrapped=()):
         """Access descriptor promoted to the iteration space; returns its index."""
         r = len(self.space)
         st = [Poly.const(0)] * r
@@ -289,9 +290,19 @@ class _EwLowering:
                 # a masked unit dim gates the whole block: lane 0 valid iff start < bound
                 for s, bnd in mask["dims"][d]:
                     conds.append(Poly.fn("cmp_slt", s, bnd))
-        for p in [offset] + st + [x for dd in mdims for sb in dd for x in sb] + conds:
-            if p.depends_on(("it", "carry")):
-                raise UnsupportedTTIR("elementwise body with a loop-dependent access")
+        wraps = []
+        for w in wrapped:
+            it_d = dimmap[w.dim]
+            wraps.append({"dim": it_d, "offset": w.inner_offset, "stride": w.inner_stride,
+                          "modulus": w.modulus, "scale": w.scale})
+            for q in (w.inner_stride, w.modulus, w.scale):
+                if q.depends_on(("pid", "carry")):
+                    raise UnsupportedTTIR("wrap-around stride, modulus or scale depends on program_id")
+        if len(wraps) > 2:
+            raise UnsupportedTTIR("more than two wrap-around dims in one access")
+        for p in [offset] + st + [x for dd in mdims for sb in dd for x in sb] + conds + [w["offset"] for w in wraps]:
+            if p.depends_on(("carry",)):
+                raise UnsupportedTTIR("elementwise body with an unresolved loop-carried access")
             if not is_affine_in_pid(p):
                 raise UnsupportedTTIR("access offset is not affine in program_id")
         for p in st + [sb[1] for dd in mdims for sb in dd] + conds:
@@ -308,7 +319,8 @@ class _EwLowering:
                         bnd = Poly.fn("minsi", bnd, b2)
                     mdims[i] = [(dd[0][0], bnd)]
         desc = {"kind": kind, "elem": elem, "arg": arg, "offset": offset, "strides": st,
-                "mask": [dd[0] if dd else None for dd in mdims], "conds": conds, "other": other}
+                "mask": [dd[0] if dd else None for dd in mdims], "conds": conds, "other": other,
+                "wrap": wraps}
         self.accs.append(desc)
         return len(self.accs) - 1
 
@@ -329,11 +341,9 @@ class _EwLowering:
         op = n.op
         if op == "load":
             acc: Access = self.an.access_of(n)
-            if acc.wrapped:
-                raise UnsupportedTTIR("wrap-around (modulo) block load in an elementwise body")
             ob = other_bits(acc.other, acc.elem)
             ai = self.acc_for("load", acc.elem, acc.shape, dimmap, acc.offset, acc.strides,
-                              _mask_json(acc.mask, acc.shape), ob, acc.arg)
+                              _mask_json(acc.mask, acc.shape), ob, acc.arg, acc.wrapped)
             return self.emit("load", acc.elem, a=ai)
         if op in ("splat",):
             return self.value(n.args[0], ())
@@ -400,7 +410,7 @@ class _EwLowering:
             dimmap = tuple(range(len(self.space) - len(shape), len(self.space)))
             v = self.value(acc.value, dimmap)
             ai = self.acc_for("store", acc.elem, shape, dimmap, acc.offset, acc.strides,
-                              _mask_json(acc.mask, shape), None, acc.arg)
+                              _mask_json(acc.mask, shape), None, acc.arg, acc.wrapped)
             self.ops.append(["store", acc.elem, -1, ai, v, 0, 0, 0])
         return self.allocate()
 
@@ -470,66 +480,111 @@ def _remap(o, mapped):
 
 
 class ElementwisePlan(Plan):
+    """Loop-free bodies, and bodies whose scf.for loops carry no data (only pointers/integers):
+    every run of consecutive stores is one VM program ("segment"); loops are walked on the host,
+    one launch per iteration and segment, with the iteration counter folded into the offsets.
+    Launches are stream-ordered, so the sequential meaning of the loops is preserved."""
     family = "elementwise"
 
     @staticmethod
     def build(kernel: Kernel, an: Analyzer) -> "ElementwisePlan":
-        stores = []
-        for kind, e in kernel.effects:
-            if kind != "store":
-                raise UnsupportedTTIR("elementwise family: kernel contains a loop")
-            stores.append(e)
-        if not stores:
-            raise UnsupportedTTIR("kernel stores nothing")
-        shapes = {s.shape for s in stores}
-        full = max(shapes, key=lambda s: (len(s), int(np.prod(s)) if s else 1))
-        rank = max(len(full), 1)
-        space = tuple([1] * (rank - len(full)) + list(full))
-        for s in shapes:
-            pad = tuple([1] * (rank - len(s)) + list(s))
-            if any(a != b and a != 1 for a, b in zip(pad, space)):
-                raise UnsupportedTTIR("stores of different block shapes in one kernel")
-        if rank > rt.TSB_MAX_RANK:
-            raise UnsupportedTTIR(f"blocks of rank {rank} (max {rt.TSB_MAX_RANK})")
-        for s in stores:
-            if s.wrapped:
-                raise UnsupportedTTIR("wrap-around (modulo) block store")
-        low = _EwLowering(kernel, an, space)
-        ops = low.lower(stores)
-        return ElementwisePlan(kernel.name, {"space": list(space), "accs": low.accs, "ops": ops,
-                                             "ptr_args": sorted({s.arg for s in stores})})
+        segments: List[dict] = []
+        stored_args = set()
 
-    def __init__(self, name, params):
-        super().__init__(name, params)
-        self._cache = {}
+        def lower_segment(stores: List[Access]):
+            shapes = {s.shape for s in stores}
+            full = max(shapes, key=lambda sh: (len(sh), int(np.prod(sh)) if sh else 1))
+            rank = max(len(full), 1)
+            space = tuple([1] * (rank - len(full)) + list(full))
+            for sh in shapes:
+                pad = tuple([1] * (rank - len(sh)) + list(sh))
+                if any(x != y and x != 1 for x, y in zip(pad, space)):
+                    raise UnsupportedTTIR("stores of different block shapes in one kernel")
+            if rank > rt.TSB_MAX_RANK:
+                raise UnsupportedTTIR(f"blocks of rank {rank} (max {rt.TSB_MAX_RANK})")
+            low = _EwLowering(kernel, an, space)
+            ops = low.lower(stores)
+            segments.append({"space": list(space), "accs": low.accs, "ops": ops})
+            stored_args.update(s.arg for s in stores)
+            return len(segments) - 1
+
+        def walk(effects):
+            tree, run = [], []
+            for kind, e in effects:
+                if kind == "store":
+                    run.append(e)
+                    continue
+                if run:
+                    tree.append(["seg", lower_segment(run)])
+                    run = []
+                loop: Loop = e
+                for init in loop.inits:
+                    if isinstance(init, TData):
+                        raise UnsupportedTTIR("elementwise family: a loop carries block data (an accumulator)")
+                for q in (loop.lb, loop.ub, loop.step):
+                    if q.depends_on(("pid", "carry")):
+                        raise UnsupportedTTIR("elementwise family: loop bounds depend on program_id")
+                tree.append(["loop", loop.id, loop.lb, loop.ub, loop.step, walk(loop.effects)])
+            if run:
+                tree.append(["seg", lower_segment(run)])
+            return tree
+
+        tree = walk(kernel.effects)
+        if not segments:
+            raise UnsupportedTTIR("kernel stores nothing")
+        if len(segments) > 1:
+            # values are recomputed (reloaded) per segment: a pointer that is both read and written
+            # could then observe a different order than the kernel text
+            loaded = {d["arg"] for sg in segments for d in sg["accs"] if d["kind"] == "load"}
+            if loaded & stored_args:
+                raise UnsupportedTTIR("elementwise family: a buffer is both loaded and stored across loop segments")
+        return ElementwisePlan(kernel.name, {"segments": segments, "tree": tree})
 
     def launch(self, args, grid, pid_lo, pid_hi, stream):
-        p = self.p
-        scal_key = tuple((i, v) for i, v in sorted(args.scalars.items())) + tuple(grid) + \
-            tuple(sorted(args.floats.items()))
-        ent = self._cache.get(scal_key)
-        if ent is None:
-            ent = self._evaluate(args, grid)
-            if len(self._cache) > 64:
-                self._cache.clear()
-            self._cache[scal_key] = ent
-        accs, ops, arg_of = ent
-        for a, i in zip(accs, arg_of):
-            if i is not None:
-                a.base = args.pointer(i)
+        plan = self.memo(args, grid, lambda: self._schedule(args, grid))
         g = (ctypes.c_int32 * 3)(*grid)
-        rt.check(rt.lib().tsb_elementwise(accs, len(accs), ops, len(ops), g, pid_lo, pid_hi, stream),
-                 f"tsb_elementwise[{self.name}]")
+        fn = rt.lib().tsb_elementwise
+        for accs, ops, arg_of in plan:
+            for a, i in zip(accs, arg_of):
+                if i is not None:
+                    a.base = args.pointer(i)
+            rc = fn(accs, len(accs), ops, len(ops), g, pid_lo, pid_hi, stream)
+            if rc:
+                rt.check(rc, f"tsb_elementwise[{self.name}]")
 
-    def _evaluate(self, args, grid):
-        p = self.p
+    def _schedule(self, args, grid):
+        """Flatten the loop tree into the ordered list of launches for these scalar arguments."""
+        out = []
         env = LaunchEnv(args.scalars, grid)
-        space = p["space"]
+
+        def run(tree):
+            for node in tree:
+                if node[0] == "seg":
+                    out.append(self._evaluate(self.p["segments"][node[1]], args, env))
+                    continue
+                _, lid, lb, ub, step, children = node
+                e = env.at()
+                lo, hi, st = int(lb.evaluate(e)), int(ub.evaluate(e)), int(step.evaluate(e))
+                if st <= 0:
+                    raise UnsupportedTTIR("loop with a non-positive step")
+                trips = max(0, -(-(hi - lo) // st))
+                if len(out) + trips > 4096:
+                    raise UnsupportedTTIR("elementwise family: more than 4096 launches for one kernel call")
+                for it in range(trips):
+                    env.base[("it", lid)] = it
+                    run(children)
+                env.base.pop(("it", lid), None)
+        run(self.p["tree"])
+        return out
+
+    def _evaluate(self, seg, args, env):
+        space = seg["space"]
         rank = len(space)
-        n = len(p["accs"])
+        n = len(seg["accs"])
         accs = (rt.Access * n)()
         arg_of = []
-        for ai, d in enumerate(p["accs"]):
+        e0 = env.at()
+        for ai, d in enumerate(seg["accs"]):
             a = accs[ai]
             kind = d["kind"]
             a.dtype = rt.DTYPES[d["elem"]]
@@ -539,10 +594,10 @@ class ElementwisePlan(Plan):
             a.offset0 = off0
             for k in range(3):
                 a.offset_pid[k] = inc[k]
-            gate = all(int(c.evaluate(env.at())) != 0 for c in d["conds"])
+            gate = all(int(c.evaluate(e0)) != 0 for c in d["conds"])
             for k in range(rank):
                 a.sizes[k] = space[k]
-                a.strides[k] = int(d["strides"][k].evaluate(env.at()))
+                a.strides[k] = int(d["strides"][k].evaluate(e0))
                 m = d["mask"][k]
                 if m is not None:
                     a.masked[k] = 1
@@ -550,7 +605,7 @@ class ElementwisePlan(Plan):
                     a.mask_start0[k] = s0
                     for j in range(3):
                         a.mask_start_pid[k][j] = sinc[j]
-                    a.mask_bound[k] = int(m[1].evaluate(env.at()))
+                    a.mask_bound[k] = int(m[1].evaluate(e0))
             if not gate:
                 # a false scalar conjunct empties the block (MaskAnalysis.cpp:224-267)
                 a.masked[0] = 1
@@ -558,9 +613,23 @@ class ElementwisePlan(Plan):
             if d["other"] is not None:
                 a.has_other = 1
                 a.other_bits = d["other"]
-            arg_of.append(None)
-        ops = (rt.Op * len(p["ops"]))()
-        for k, o in enumerate(p["ops"]):
+            wraps = d.get("wrap") or []
+            a.n_wrap = len(wraps)
+            for wi, w in enumerate(wraps):
+                ww = a.wrap[wi]
+                ww.dim = w["dim"]
+                o0, oinc = env.affine_pid(w["offset"])
+                ww.offset0 = o0
+                for j in range(3):
+                    ww.offset_pid[j] = oinc[j]
+                ww.stride = int(w["stride"].evaluate(e0))
+                ww.modulus = int(w["modulus"].evaluate(e0))
+                ww.scale = int(w["scale"].evaluate(e0))
+                if ww.modulus <= 0:
+                    raise UnsupportedTTIR("wrap-around access with a non-positive modulus")
+            arg_of.append(d.get("arg"))
+        ops = (rt.Op * len(seg["ops"]))()
+        for k, o in enumerate(seg["ops"]):
             opc, dt, dst, ra, rb, rc, imm, imm2 = o
             x = ops[k]
             x.opcode = rt.OPCODES[opc]
@@ -568,16 +637,12 @@ class ElementwisePlan(Plan):
             x.dst, x.a, x.b, x.c = max(dst, 0), ra, rb, rc
             if isinstance(imm, (list, tuple)):
                 if imm[0] == "poly":
-                    v = int(imm[1].evaluate(env.at()))
-                    x.imm = v & 0xffffffff
+                    x.imm = int(imm[1].evaluate(e0)) & 0xffffffff
                 else:  # farg
                     x.imm = struct.unpack("<I", struct.pack("<f", float(args.floats[imm[1]])))[0]
             else:
                 x.imm = imm
             x.imm2 = imm2
-        # which kernel pointer argument backs each access
-        for ai, d in enumerate(p["accs"]):
-            arg_of[ai] = d.get("arg")
         return accs, ops, arg_of
 
 

@@ -37,6 +37,19 @@ CMPI = {"eq": 32, "ne": 33, "slt": 34, "sle": 35, "sgt": 36, "sge": 37, "ult": 3
         "ugt": 40, "uge": 41}
 
 
+class Wrap(ctypes.Structure):
+    """struct tsb_wrap"""
+    _fields_ = [
+        ("dim", ctypes.c_int32),
+        ("pad_", ctypes.c_int32),
+        ("offset0", ctypes.c_int64),
+        ("offset_pid", ctypes.c_int64 * 3),
+        ("stride", ctypes.c_int64),
+        ("modulus", ctypes.c_int64),
+        ("scale", ctypes.c_int64),
+    ]
+
+
 class Access(ctypes.Structure):
     """struct tsb_access"""
     _fields_ = [
@@ -55,6 +68,9 @@ class Access(ctypes.Structure):
         ("mask_start_pid", (ctypes.c_int64 * 3) * TSB_MAX_RANK),
         ("mask_bound", ctypes.c_int64 * TSB_MAX_RANK),
         ("other_bits", ctypes.c_uint64),
+        ("n_wrap", ctypes.c_int32),
+        ("pad2_", ctypes.c_int32),
+        ("wrap", Wrap * 2),
     ]
 
 

@@ -31,6 +31,12 @@ struct DAcc {
   int has_other;
   unsigned other; // fill value in register representation
   int kind;       // 0 memory load, 1 memory store, 2 mask probe, 3 index probe
+  int n_wrap;     // wrap-around (modulo) terms
+  int wrap_inner; // some wrap term is on the innermost dim (lanes of a vector differ non-linearly)
+  struct {
+    int dim;
+    long long off0, off_pid[3], stride, modulus, scale;
+  } wrap[2];
 };
 
 struct EwParams {
@@ -220,12 +226,25 @@ __device__ __forceinline__ unsigned cast_(unsigned v, int from, int to, unsigned
 
 struct ProgState {
   long long off;
+  long long woff[2];
   int dim[3];
 };
+
+// scale * ((offset + i*stride) mod modulus) summed over the access's wrap terms
+__device__ __forceinline__ long long wrap_addend(const DAcc &A, const ProgState &s, int i0, int i1, int i2) {
+  long long add = 0;
+  for (int w = 0; w < A.n_wrap; ++w) {
+    const int id = A.wrap[w].dim == 0 ? i0 : (A.wrap[w].dim == 1 ? i1 : i2);
+    add += A.wrap[w].scale * ((s.woff[w] + id * A.wrap[w].stride) % A.wrap[w].modulus);
+  }
+  return add;
+}
 
 __device__ __forceinline__ void program_state(const DAcc &A, const int size[3], long long px,
                                               long long py, long long pz, ProgState &s) {
   s.off = A.off0 + A.off_pid[0] * px + A.off_pid[1] * py + A.off_pid[2] * pz;
+  for (int w = 0; w < A.n_wrap; ++w)
+    s.woff[w] = A.wrap[w].off0 + A.wrap[w].off_pid[0] * px + A.wrap[w].off_pid[1] * py + A.wrap[w].off_pid[2] * pz;
 #pragma unroll
   for (int d = 0; d < 3; ++d) {
     int dim = size[d];
@@ -245,8 +264,22 @@ template <int VEC>
 __device__ __forceinline__ void load_vec(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
                                          unsigned out[VEC]) {
   const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
-  const long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
+  long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
   const unsigned fill = A.has_other ? A.other : 0u;
+  if (A.n_wrap) {
+    if (A.wrap_inner) {
+      // lanes of the vector wrap independently: one scalar access per lane
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const bool ok = outer && (i2 + k) < s.dim[2];
+        const long long ek = e + k * A.stride[2] + wrap_addend(A, s, i0, i1, i2 + k);
+        out[k] = A.kind == 2 ? (ok ? 1u : 0u)
+                             : (A.kind == 3 ? (unsigned)ek : (ok ? ld_elem(A.base + ek * A.esize, A.dtype) : fill));
+      }
+      return;
+    }
+    e += wrap_addend(A, s, i0, i1, i2);
+  }
   if (A.kind >= 2) {
     // probes read no memory: 2 yields the lane's mask bit, 3 its linear index
 #pragma unroll
@@ -289,7 +322,17 @@ __device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int
                                           const unsigned in[VEC]) {
   const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
   if (!outer) return;
-  const long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
+  long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
+  if (A.n_wrap) {
+    if (A.wrap_inner) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k)
+        if (i2 + k < s.dim[2])
+          st_elem(A.base + (e + k * A.stride[2] + wrap_addend(A, s, i0, i1, i2 + k)) * A.esize, A.dtype, in[k]);
+      return;
+    }
+    e += wrap_addend(A, s, i0, i1, i2);
+  }
   if (VEC == 4 && A.vec_ok && i2 + VEC <= s.dim[2]) {
     char *p = A.base + e * A.esize;
     if (A.esize == 4) {
@@ -723,11 +766,29 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
         d.bound[o] = s.mask_bound[k];
       }
     }
+    if (s.n_wrap < 0 || s.n_wrap > 2) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has %d wrap terms", a, s.n_wrap);
+    d.n_wrap = s.n_wrap;
+    d.wrap_inner = 0;
+    bool wrap_unaligned = false;
+    for (int w = 0; w < s.n_wrap; ++w) {
+      const tsb_wrap &sw = s.wrap[w];
+      if (sw.dim < 0 || sw.dim >= rank) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d wraps dim %d of rank %d", a, sw.dim, rank);
+      if (sw.modulus <= 0) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has wrap modulus %lld", a, (long long)sw.modulus);
+      d.wrap[w].dim = 3 - rank + sw.dim;
+      d.wrap[w].off0 = sw.offset0;
+      for (int j = 0; j < 3; ++j) d.wrap[w].off_pid[j] = sw.offset_pid[j];
+      d.wrap[w].stride = sw.stride;
+      d.wrap[w].modulus = sw.modulus;
+      d.wrap[w].scale = sw.scale;
+      if (d.wrap[w].dim == 2) d.wrap_inner = 1;
+      if (sw.scale % 4 != 0) wrap_unaligned = true;
+    }
     // 4-lane vectors need: unit inner stride, vector-aligned base and offsets
     const long long vb = 4ll * es;
     bool ok = vec == 4 && d.stride[2] == 1 && ((uintptr_t)d.base % vb) == 0 && d.off0 % 4 == 0;
     for (int k = 0; k < 3; ++k) ok = ok && (grid[k] <= 1 || d.off_pid[k] % 4 == 0);
     ok = ok && (P.size[1] <= 1 || d.stride[1] % 4 == 0) && (P.size[0] <= 1 || d.stride[0] % 4 == 0);
+    ok = ok && !d.wrap_inner && !wrap_unaligned;
     d.vec_ok = ok ? 1 : 0;
   }
   for (int k = 0; k < n_ops; ++k) {
@@ -764,6 +825,7 @@ static bool build_flat(const EwParams &P, int vec, FlatParams &F) {
   for (int a = 0; a < P.n_acc; ++a) {
     const DAcc &d = P.acc[a];
     if (d.masked & 3) return false;
+    if (d.n_wrap) return false;
     if (d.kind != 2 && (d.stride[2] != 1 || d.off_pid[0] != B)) return false;
     if ((d.masked & 4) && d.mstart_pid[2][0] != B) return false;
     FlatAcc &f = F.acc[a];
