@@ -41,12 +41,14 @@ MM = 8_192
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu
 # captures summarised under profiles/; None until a capture exists for the kernel.
+# Captures on reduced cases are scaled to the full-size launch by rows / elements (traffic is
+# proportional for these kernels); the summaries give the raw figures and the commands.
 NCU_TRAFFIC_BYTES = {
-    "softmax": None,
-    "vec_add": None,
-    "layernorm": None,
-    "strided_reduce": None,
-    "matmul": None,
+    "softmax": 1.94216e9,         # 65,536 x 4,096: 4 x (268.46 MB read + 217.08 MB written) at 16,384 rows
+    "vec_add": 12.5733e9,         # n = 2^30: 8 x (1.0738 GB + 497.8 MB) at n = 2^27
+    "layernorm": 121.35e6,        # 4,096 x 8,192 fp16: (268.55 MB + 216.84 MB) / 4 at 16,384 rows
+    "strided_reduce": 398.07e6,   # full size: 393.24 MB read + 4.83 MB written (row kernel)
+    "matmul": 1.51794e9,          # 8192^3 bf16: 1.3908 GB read + 127.2 MB written
 }
 
 
@@ -338,7 +340,8 @@ def main():
                    "eager_ms_per_step": eager_ms / args.steps,
                    "result_check": "row sums == 1" if ok else "FAILED row-sum check"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC_BYTES["softmax"],
+                     "frac": achieved / peaks["hbm"],
+                     "traffic": NCU_TRAFFIC_BYTES["softmax"] * rows / SOFTMAX_ROWS,
                      "peak_source": f"of {peaks['src']}", "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": rows * cols * 4 * world,
                 "d2h_bytes_per_step": rows * cols * 4 * world, "steps": e2e_steps,
