@@ -449,6 +449,21 @@ def main():
                                          C.stride(0), C.stride(1), BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
             record("matmul", mm_step, 2.0 * MM * MM * MM, 1e12, "tensor", "TFLOP/s")
             if "value" in wl.get("matmul", {}):
+                # single launches with idle gaps between them: the burst figure (the measured peak is
+                # quoted the same two ways: best single cuBLAS call, and seconds of back-to-back calls)
+                best = float("inf")
+                for _ in range(10):
+                    torch.cuda.synchronize()
+                    time.sleep(0.05)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    mm_step()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    best = min(best, e0.elapsed_time(e1))
+                burst = 2.0 * MM * MM * MM / (best * 1e-3) / 1e12
+                wl["matmul"]["burst"] = {"best_ms": best, "value": burst, "unit": "TFLOP/s",
+                                         "frac_of_burst_peak": burst / peaks["tensor"]}
                 ref = (A[:256].float() @ B.float())
                 err = (C[:256].float() - ref).abs().max().item() / ref.abs().max().item()
                 wl["matmul"]["result_check_rel_err"] = err

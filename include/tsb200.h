@@ -303,6 +303,23 @@ int tsb_gemm(const void *a, const void *b, void *c, int32_t dtype, int64_t M, in
              int32_t block_k, const int32_t *tile_of_pid, int64_t n_programs, int64_t pid_lo,
              int64_t pid_hi, int32_t *status, void *stream);
 
+/*
+ * Same product as tsb_gemm for PAIRS of vertically adjacent tiles: entry w of `pairs` (device
+ * int32 pairs) names tiles (tile_m, tile_n) and (tile_m + 1, tile_n), which two CTAs on two SMs
+ * compute together with tcgen05.mma.cta_group::2; each CTA stages its own A rows and half of the
+ * B block, which cuts shared-memory traffic per SM by a third.  Replaces the same reference loop
+ * nest as tsb_gemm (kernel-03-matrix-multiplication.mlir:157-204).  Requires block_m == 128,
+ * K > 0 and operands eligible for the tensor path (16-byte aligned bases and row pitches,
+ * unit stride along K for A, along N or K for B, block_n a multiple of 128 for [K,N] B and of
+ * 32 for [N,K] B); otherwise TSB_ERR_UNSUPPORTED is returned and nothing is launched, and the
+ * caller uses tsb_gemm.  A tile_m + 1 beyond M is allowed (its rows are never stored).
+ */
+int tsb_gemm_paired(const void *a, const void *b, void *c, int32_t dtype, int64_t M, int64_t N, int64_t K,
+                    int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
+                    int64_t stride_cm, int64_t stride_cn, int32_t block_m, int32_t block_n,
+                    int32_t block_k, const int32_t *pairs, int64_t n_pairs, int32_t *status,
+                    void *stream);
+
 #ifdef __cplusplus
 }
 #endif

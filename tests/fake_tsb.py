@@ -321,6 +321,22 @@ class FakeLib:
         return 0
 
 
+    def _gemm_paired(self, a, b, c, dt, M, N, K, sam, sak, sbk, sbn, scm, scn, bm, bn, bk, pairs, n_pairs, status, stream):
+        self.calls.append(("tsb_gemm_paired", 0, n_pairs))
+        if sak != 1 or sam % 8 or (sbn == 1 and (sbk % 8 or bn % 128)) or (sbn != 1 and (sbk != 1 or sbn % 8)) or bm != 128:
+            return -2
+        pr = np.ctypeslib.as_array((ctypes.c_int32 * (2 * n_pairs)).from_address(pairs)).reshape(-1, 2)
+        tiles = []
+        for tm, tn in pr:
+            tiles += [(tm, tn), (tm + 1, tn)]
+        t = np.ascontiguousarray(np.asarray(tiles, dtype=np.int32))
+        oracle.lib().orc_matmul(a, b, c, {1: 1, 2: 2}[dt], M, N, K, sam, sak, sbk, sbn, scm, scn, bm, bn, bk,
+                                t.ctypes.data, 0, len(tiles), 1)
+        return 0
+
+    tsb_gemm_paired = _gemm_paired
+
+
 class fake_device:
     """Context manager: route the driver plugin to FakeLib + host memory."""
 

@@ -218,10 +218,31 @@ def test_family_parameters_reach_the_c_abi(oracle_lib):
             ref = a.float() @ bm.float()
             assert torch.allclose(c.float(), ref, rtol=1e-2, atol=1e-2)
     names = [c[0] for c in lib.calls]
-    assert names == ["tsb_softmax_rows", "tsb_layernorm_fwd", "tsb_reduce_rows", "tsb_reduce_all", "tsb_gemm", "tsb_gemm"]
+    # 200 x 264 with 128 x 256 blocks: two vertically adjacent pairs of tiles, no single tile left over
+    assert names == ["tsb_softmax_rows", "tsb_layernorm_fwd", "tsb_reduce_rows", "tsb_reduce_all",
+                     "tsb_gemm_paired", "tsb_gemm_paired"]
 
 
 # ------------------------------------------------------------------ plugin surface
+def test_tile_pairing_for_the_two_cta_matmul():
+    """Pairs are (even tile_m, tile_n) with (tile_m + 1, tile_n) present; every tile lands in exactly one place."""
+    from triton_shared_b200.backend.plan import GemmPlan
+    tiles = np.asarray(oracle_tiles(5 * 128, 3 * 256), dtype=np.int32)  # 5 x 3 tiles: the last tile row has no partner
+    pairs, singles = GemmPlan.pair_tiles(tiles)
+    assert len(pairs) == 2 * 3 and len(singles) == 3 and set(singles[:, 0]) == {4}
+    covered = {(tm, tn) for tm, tn in pairs} | {(tm + 1, tn) for tm, tn in pairs} | {tuple(t) for t in singles}
+    assert covered == {tuple(t) for t in tiles}
+    # a partial range (what one of several GPUs gets) may cut a pair: the orphan becomes a single
+    pairs, singles = GemmPlan.pair_tiles(tiles[1:8])
+    covered = [(tm, tn) for tm, tn in pairs] + [(tm + 1, tn) for tm, tn in pairs] + [tuple(t) for t in singles]
+    assert sorted(covered) == sorted(tuple(t) for t in tiles[1:8])
+
+
+def oracle_tiles(M, N):
+    import oracle
+    return oracle.grouped_tiles(M, N, 128, 256, 8)
+
+
 def test_driver_surface_matches_reference():
     """Method set of CPUDriver (backend/driver.py:420-464 in the reference) and launcher call shape."""
     d = tsb.B200Driver()

@@ -1147,6 +1147,20 @@ class GemmPlan(Plan):
         return dict(M=M, N=N, K=K, sam=sam, sak=sak, sbk=sbk, sbn=sbn, scm=scm, scn=scn, tiles=tiles,
                     n_prog=n_prog, unmasked_rows=unmasked_rows)
 
+    @staticmethod
+    def pair_tiles(tiles: np.ndarray):
+        """Split a list of (tile_m, tile_n) into vertically adjacent pairs (even tile_m first) and the rest."""
+        index = {(int(tm), int(tn)): i for i, (tm, tn) in enumerate(tiles)}
+        used = np.zeros(len(tiles), dtype=bool)
+        pairs = []
+        for i, (tm, tn) in enumerate(tiles):
+            j = index.get((int(tm) + 1, int(tn)))
+            if tm % 2 == 0 and j is not None:
+                pairs.append((int(tm), int(tn)))
+                used[i] = used[j] = True
+        singles = tiles[~used]
+        return np.asarray(pairs, dtype=np.int32).reshape(-1, 2), np.ascontiguousarray(singles, dtype=np.int32)
+
     def launch(self, args, grid, pid_lo, pid_hi, stream):
         p = self.p
         key = tuple(sorted(args.scalars.items())) + tuple(grid)
@@ -1156,13 +1170,36 @@ class GemmPlan(Plan):
             if len(self._cache) > 16:
                 self._cache.clear()
             self._cache[key] = r
-        tiles_dev = args.device_table(("gemm_tiles", self.name) + key, r["tiles"], stream)
         status = args.status_word(stream)
-        rc = rt.lib().tsb_gemm(args.pointer(p["a"]), args.pointer(p["b"]), args.pointer(p["c"]),
-                               rt.DTYPES[p["elem"]], r["M"], r["N"], r["K"], r["sam"], r["sak"], r["sbk"],
-                               r["sbn"], r["scm"], r["scn"], p["BM"], p["BN"], p["BK"], tiles_dev,
-                               r["n_prog"], pid_lo, pid_hi, status, stream)
-        rt.check(rc, f"tsb_gemm[{self.name}]")
+        common = (args.pointer(p["a"]), args.pointer(p["b"]), args.pointer(p["c"]), rt.DTYPES[p["elem"]],
+                  r["M"], r["N"], r["K"], r["sam"], r["sak"], r["sbk"], r["sbn"], r["scm"], r["scn"],
+                  p["BM"], p["BN"], p["BK"])
+        L = rt.lib()
+        if p["BM"] == 128 and r["K"] > 0 and not r.get("no_pairs"):
+            # two-CTA form for every pair of vertically adjacent tiles in the range, one-CTA form for the rest
+            pk = ("split", pid_lo, pid_hi)
+            sp = r.get(pk)
+            if sp is None:
+                sp = r[pk] = self.pair_tiles(r["tiles"][pid_lo:pid_hi])
+            pairs, singles = sp
+            if len(pairs):
+                dev = args.device_table(("gemm_pairs", self.name, pid_lo, pid_hi) + key, pairs, stream)
+                rc = L.tsb_gemm_paired(*common, dev, len(pairs), status, stream)
+                if rc == -2:
+                    r["no_pairs"] = True  # operands not eligible: the one-CTA entry decides (tensor or SIMT)
+                else:
+                    if rc:
+                        rt.check(rc, f"tsb_gemm_paired[{self.name}]")
+                    if len(singles):
+                        dev1 = args.device_table(("gemm_singles", self.name, pid_lo, pid_hi) + key, singles, stream)
+                        rc = L.tsb_gemm(*common, dev1, len(singles), 0, len(singles), status, stream)
+                        if rc:
+                            rt.check(rc, f"tsb_gemm[{self.name}]")
+                    return
+        tiles_dev = args.device_table(("gemm_tiles", self.name) + key, r["tiles"], stream)
+        rc = L.tsb_gemm(*common, tiles_dev, r["n_prog"], pid_lo, pid_hi, status, stream)
+        if rc:
+            rt.check(rc, f"tsb_gemm[{self.name}]")
 
 
 _FAMILIES = {c.family: c for c in (GemmPlan, LayerNormPlan, SoftmaxPlan, ReduceRowsPlan, ReduceAllPlan,

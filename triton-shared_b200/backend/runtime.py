@@ -97,7 +97,7 @@ _lib = None
 # every symbol include/tsb200.h declares
 SYMBOLS = ["tsb_last_error", "tsb_version", "tsb_sm_count", "tsb_elementwise", "tsb_block_copy",
            "tsb_softmax_rows", "tsb_layernorm_fwd", "tsb_reduce_rows_scratch_bytes", "tsb_reduce_rows",
-           "tsb_reduce_rows_static", "tsb_reduce_all", "tsb_gemm"]
+           "tsb_reduce_rows_static", "tsb_reduce_all", "tsb_gemm", "tsb_gemm_paired"]
 
 
 def lib():
@@ -133,6 +133,8 @@ def lib():
     L.tsb_reduce_all.argtypes = [vp, vp, i64, i64, vp]
     L.tsb_gemm.restype = ctypes.c_int
     L.tsb_gemm.argtypes = [vp, vp, vp, i32] + [i64] * 9 + [i32, i32, i32, vp, i64, i64, i64, vp, vp]
+    L.tsb_gemm_paired.restype = ctypes.c_int
+    L.tsb_gemm_paired.argtypes = [vp, vp, vp, i32] + [i64] * 9 + [i32, i32, i32, vp, i64, vp, vp]
     _lib = L
     return L
 

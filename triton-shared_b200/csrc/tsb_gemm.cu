@@ -26,141 +26,13 @@
 // records where it gave up in status[], stops issuing work, drains its
 // outstanding copies with a second bounded wait, frees its tensor memory and
 // returns.
-#include "tsb_common.cuh"
-#include <cuda.h>
+#include "tsb_tcgen05.cuh"
 #include <string.h>
 
 namespace tsb {
 
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
-constexpr unsigned long long DRAIN_LIMIT_NS = 100000000ull;  // 0.1 s when draining after a failure
-
-// Bounded wait. Returns false when the limit expired or another role has already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  unsigned spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > limit_ns) return false;
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// mbarrier arrives once all MMAs issued so far by this thread have completed
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 lanes x 32 columns of 32-bit: thread t of the warp gets row (lane base + t), columns c..c+31
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// ------------------------------------------------------------------ descriptors
-// Shared-memory matrix descriptor, 128-byte swizzle:
-//   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte
-//   offset >> 4, [46,48) = 1 (descriptor version of this architecture), [61,64) = 2 (128B swizzle).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-// Instruction descriptor of kind::f16: fp32 accumulate, A K-major, B K- or MN-major.
-__host__ __device__ inline uint32_t make_idesc(int is_bf16, int b_mn_major, int m, int n) {
-  uint32_t d = 0;
-  d |= 1u << 4;                          // D format: f32
-  d |= (uint32_t)(is_bf16 ? 1 : 0) << 7;   // A format
-  d |= (uint32_t)(is_bf16 ? 1 : 0) << 10;  // B format
-  d |= (uint32_t)(b_mn_major ? 1 : 0) << 16;
-  d |= (uint32_t)(n >> 3) << 17;
-  d |= (uint32_t)(m >> 4) << 24;
-  return d;
-}
-
 // ------------------------------------------------------------------ tensor-core kernel
-constexpr int GEMM_BM = 128;
-constexpr int GEMM_BK = 64;        // elements per stage along K (one 128-byte swizzle row)
 constexpr int GEMM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr int A_STAGE_BYTES = GEMM_BM * GEMM_BK * 2;
 
 struct GemmParams {
   void *c;
@@ -484,7 +356,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D map over a row-major [rows, inner] matrix with `pitch` elements between rows.
-static int make_map(CUtensorMap *m, const void *base, int is_bf16, long long inner, long long rows,
+int make_map(CUtensorMap *m, const void *base, int is_bf16, long long inner, long long rows,
                     long long pitch, int box_inner, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(TSB_ERR_CUDA, "tsb_gemm: cuTensorMapEncodeTiled is not available from this driver");
@@ -502,7 +374,7 @@ static int make_map(CUtensorMap *m, const void *base, int is_bf16, long long inn
 
 // 0: not eligible for the tensor-core kernel; 1: B is MN-major ([K,N], unit stride along N);
 // 2: B is K-major (unit stride along K).
-static int tensor_path_mode(const void *a, const void *b, int dtype, long long sam, long long sak,
+int tensor_path_mode(const void *a, const void *b, int dtype, long long sam, long long sak,
                             long long sbk, long long sbn, long long scn, int bm, int bn, int bk) {
   if (dtype != TSB_BF16 && dtype != TSB_F16) return 0;
   if (bm != GEMM_BM || bk % GEMM_BK != 0 || bn < 16 || bn > 256 || bn % 16 != 0) return 0;
