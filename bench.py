@@ -209,6 +209,11 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # libraries (NCCL's version banner, for one) write to file descriptor 1: send that to stderr
+    # until the result line is printed
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: this backend has no CPU execution path")
     torch.cuda.set_device(local_rank)
@@ -481,10 +486,12 @@ def main():
         gbs, threads, srows, dt = cpu_softmax_rate()
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                                 "sample": f"{srows} of {SOFTMAX_ROWS} rows x {SOFTMAX_COLS} cols, one pass, {dt:.1f} s"}
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)  # stdout carries exactly one line
+    if rank == 0:
+        print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
