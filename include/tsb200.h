@@ -148,7 +148,8 @@ enum tsb_opcode {
   /* casts: imm = source dtype, type = destination dtype */
   TSB_OP_CAST = 90,
   TSB_OP_BITCAST = 91,
-  TSB_OP_FMA = 92 /* math.fma: single rounding */
+  TSB_OP_FMA = 92, /* math.fma: single rounding */
+  TSB_OP_REDUCE = 100 /* tsb_block_program only: dst <- fold of reg a along dim imm2 with combiner opcode imm */
 };
 
 enum tsb_cmp {
@@ -191,6 +192,21 @@ int tsb_sm_count(void);
  */
 int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
                     const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, void *stream);
+
+/*
+ * Run a body that also contains reductions along block axes (tt.reduce) over programs
+ * [pid_lo, pid_hi): one CTA per program, every intermediate block held in shared memory.
+ * Replaces kernels whose lowered form mixes memref.copy loads/stores, linalg.generic ops and
+ * linalg.reduce (ReduceConverter, ConversionPatterns.hpp:1203-1440) without a loop-carried
+ * accumulator.  Registers are numbered 0..n_regs-1; reg_masks[r] has bit d set when register r
+ * extends along dim d of the iteration space (absent dims are broadcast: a reduction result
+ * simply loses the reduced dim).  TSB_OP_STORE carries in imm the mask of dims the store walks.
+ * Float reductions combine in a tree, not left to right: results agree with the reference
+ * within rounding, not bit for bit.  All block values together must fit 200 KB.
+ */
+int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
+                      const int32_t *reg_masks, int n_regs, const int32_t grid[3], int64_t pid_lo,
+                      int64_t pid_hi, void *stream);
 
 /*
  * Plain structured block copy dst[block] <- src[block] for programs

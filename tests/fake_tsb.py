@@ -103,25 +103,7 @@ class FakeLib:
         idx = np.unravel_index(np.arange(lanes), sizes)
         for prog in range(pid_lo, pid_hi):
             p = (prog % g[0], (prog // g[0]) % g[1], prog // (g[0] * g[1]))
-            state = []
-            for a in range(n_acc):
-                A = accs[a]
-                off = A.offset0 + sum(A.offset_pid[k] * p[k] for k in range(3))
-                valid = np.ones(lanes, dtype=bool)
-                elem = np.full(lanes, off, dtype=np.int64)
-                for w in range(A.n_wrap):
-                    W = A.wrap[w]
-                    wo = W.offset0 + sum(W.offset_pid[k] * p[k] for k in range(3))
-                    inner = wo + idx[W.dim] * W.stride
-                    q = np.abs(inner) // W.modulus * np.sign(inner)
-                    elem = elem + W.scale * (inner - q * W.modulus)  # remainder with the dividend's sign
-                for d in range(rank):
-                    elem = elem + idx[d] * A.strides[d]
-                    if A.masked[d]:
-                        st = A.mask_start0[d] + sum(A.mask_start_pid[d][k] * p[k] for k in range(3))
-                        dim = max(min(st + sizes[d], A.mask_bound[d]), st) - st
-                        valid &= idx[d] < dim
-                state.append((elem, valid))
+            state = [self._acc_state(accs[a], p, rank, sizes, idx, lanes) for a in range(n_acc)]
             regs = {}
             for k in range(n_ops):
                 o = ops[k]
@@ -144,9 +126,83 @@ class FakeLib:
         return 0
 
     @staticmethod
-    def _mem(A, elem):
-        es = _SIZE[A.dtype]
-        return es
+    def _acc_state(A, p, rank, sizes, idx, lanes):
+        """(element index, validity) of every lane of the iteration space for program p."""
+        off = A.offset0 + sum(A.offset_pid[k] * p[k] for k in range(3))
+        valid = np.ones(lanes, dtype=bool)
+        elem = np.full(lanes, off, dtype=np.int64)
+        for w in range(A.n_wrap):
+            W = A.wrap[w]
+            wo = W.offset0 + sum(W.offset_pid[k] * p[k] for k in range(3))
+            inner = wo + idx[W.dim] * W.stride
+            q = np.abs(inner) // W.modulus * np.sign(inner)
+            elem = elem + W.scale * (inner - q * W.modulus)  # remainder with the dividend's sign
+        for d in range(rank):
+            elem = elem + idx[d] * A.strides[d]
+            if A.masked[d]:
+                st = A.mask_start0[d] + sum(A.mask_start_pid[d][k] * p[k] for k in range(3))
+                dim = max(min(st + sizes[d], A.mask_bound[d]), st) - st
+                valid &= idx[d] < dim
+        return elem, valid
+
+    def tsb_block_program(self, accs, n_acc, ops, n_ops, reg_masks, n_regs, grid, pid_lo, pid_hi, stream):
+        """Registers are numpy arrays of the iteration-space shape with absent dims collapsed to 1."""
+        self.calls.append(("tsb_block_program", pid_lo, pid_hi))
+        g = [max(int(grid[i]), 1) for i in range(3)]
+        rank = accs[0].rank
+        sizes = [int(accs[0].sizes[d]) for d in range(rank)]
+        lanes = int(np.prod(sizes))
+        idx = np.unravel_index(np.arange(lanes), sizes)
+        shape_of = lambda m: tuple(sizes[d] if m & (1 << d) else 1 for d in range(rank))
+        take = lambda full, m: full.reshape(sizes)[tuple(slice(None) if m & (1 << d) else slice(0, 1) for d in range(rank))]
+        ident = {"addf": 0, "mulf": 0x3f800000, "maxnumf": 0xff800000, "maximumf": 0xff800000, "minnumf": 0x7f800000,
+                 "minimumf": 0x7f800000, "muli": 1, "andi": 0xffffffff, "maxsi": 0x80000000, "minsi": 0x7fffffff,
+                 "minui": 0xffffffff}
+        for prog in range(pid_lo, pid_hi):
+            p = (prog % g[0], (prog // g[0]) % g[1], prog // (g[0] * g[1]))
+            R = {}
+            for k in range(n_ops):
+                o = ops[k]
+                name = _OPNAME[o.opcode]
+                if name == "load":
+                    A = accs[o.a]
+                    elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes)
+                    if A.is_store == 2:
+                        full = valid.astype(np.uint32)
+                    elif A.is_store == 3:
+                        full = elem.astype(np.uint32)
+                    else:
+                        full = self._load(A, elem, valid)
+                    R[o.dst] = take(full, reg_masks[o.dst]).copy()
+                elif name == "store":
+                    A = accs[o.a]
+                    elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes)
+                    m = int(o.imm)
+                    val = np.broadcast_to(R[o.b], shape_of(m))
+                    sel = take(np.arange(lanes), m).reshape(-1)  # one lane per walked element
+                    self._store(A, elem[sel], valid[sel], np.ascontiguousarray(val).reshape(-1))
+                elif name == "reduce":
+                    comb, d = _OPNAME[o.imm], int(o.imm2)
+                    src = R[o.a]
+                    acc = np.full(tuple(1 if i == d else n for i, n in enumerate(src.shape)), ident.get(comb, 0), dtype=np.uint32)
+                    op = type("O", (), {"type": o.type, "a": 0, "b": 1, "c": 0, "imm": 0, "imm2": 0})()
+                    for j in range(src.shape[d]):
+                        sl = np.take(src, [j], axis=d)
+                        flat = self._alu(comb, op, {0: np.ascontiguousarray(sl).reshape(-1), 1: acc.reshape(-1)}, sl.size)
+                        acc = flat.reshape(acc.shape)
+                    R[o.dst] = acc
+                else:
+                    shp = shape_of(reg_masks[o.dst])
+                    n = int(np.prod(shp))
+                    regs = {}
+                    unary = {"exp", "exp2", "log", "log2", "sqrt", "rsqrt", "sin", "cos", "tanh", "erf", "absf", "negf",
+                             "floor", "ceil", "absi", "cast", "bitcast", "mov"}
+                    used = () if name == "const" else ((o.a,) if name in unary else
+                                                      ((o.a, o.b, o.c) if name in ("select", "fma") else (o.a, o.b)))
+                    for r in used:
+                        regs[r] = np.ascontiguousarray(np.broadcast_to(R[r], shp)).reshape(-1)
+                    R[o.dst] = self._alu(name, o, regs, n).reshape(shp)
+        return 0
 
     def _load(self, A, elem, valid):
         es = _SIZE[A.dtype]

@@ -268,3 +268,39 @@ def wrap_cols_kernel(a_ptr, c_ptr, N, row, stride_am, stride_an, stride_cn, STAR
     offs_an = (START + tl.arange(0, BN)) % N
     a = tl.load(a_ptr + row * stride_am + offs_an[None, :] * stride_an)
     tl.store(c_ptr + tl.arange(0, BN)[None, :] * stride_cn, a)
+
+
+# ---- bodies with block reductions but no loop-carried accumulator ------------------------------
+
+@triton.jit
+def block_sum_kernel(x_ptr, out_ptr, stride, n_elements, BLOCK_SIZE: tl.constexpr):
+    """One masked 1-D block per program, summed to a scalar (the shape of python/examples/test_reduce.py:9-30)."""
+    pid = tl.program_id(0)
+    offs = tl.arange(0, BLOCK_SIZE)
+    x = tl.load(x_ptr + pid * stride + offs, mask=offs < n_elements, other=0.0)
+    tl.store(out_ptr + pid, tl.sum(x, axis=0))
+
+
+@triton.jit
+def rmsnorm_kernel(x_ptr, w_ptr, y_ptr, stride, n_cols, eps, BLOCK: tl.constexpr):
+    """y = x * rsqrt(mean(x^2) + eps) * w for one row per program (row fits one block)."""
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK)
+    m = cols < n_cols
+    x = tl.load(x_ptr + row * stride + cols, mask=m, other=0.0).to(tl.float32)
+    w = tl.load(w_ptr + cols, mask=m, other=0.0).to(tl.float32)
+    ms = tl.sum(x * x, axis=0) / n_cols
+    y = x * (1.0 / tl.sqrt(ms + eps)) * w
+    tl.store(y_ptr + row * stride + cols, y.to(y_ptr.dtype.element_ty), mask=m)
+
+
+@triton.jit
+def tile_max_kernel(x_ptr, rowmax_ptr, colmin_ptr, stride_m, M, N, BM: tl.constexpr, BN: tl.constexpr):
+    """Row maxima and column minima of one ragged int32 tile per program (axis 1 and axis 0 reductions)."""
+    pid = tl.program_id(0)
+    offs_m = pid * BM + tl.arange(0, BM)
+    offs_n = tl.arange(0, BN)
+    mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+    x = tl.load(x_ptr + offs_m[:, None] * stride_m + offs_n[None, :], mask=mask, other=0)
+    tl.store(rowmax_ptr + offs_m, tl.max(x, axis=1), mask=offs_m < M)
+    tl.store(colmin_ptr + pid * BN + offs_n, tl.min(x, axis=0), mask=offs_n < N)

@@ -325,3 +325,45 @@ def test_loops_and_wraparound_on_host_stand_in():
         assert torch.equal(got, exp), name
     # 5 loop iterations, 3*5 tile steps, 2 wrap steps, 1 single launch
     assert len(lib.calls) == 5 + 15 + 2 + 1
+
+
+# ------------------------------------------------------------------ block programs (reductions in the body)
+def _block_program_cases(dev):
+    out = []
+    torch.manual_seed(7)
+    x = torch.randn(9, 300, device=dev)
+    s = torch.zeros(9, device=dev)
+    K.block_sum_kernel[(9,)](x, s, 300, 290, BLOCK_SIZE=512)
+    out.append(("block_sum", s.cpu(), x[:, :290].sum(dim=1).cpu(), 1e-4))
+    xh = torch.randn(5, 1000, device=dev).half()
+    w = (torch.rand(1000, device=dev) + 0.5).half()
+    y = torch.zeros_like(xh)
+    K.rmsnorm_kernel[(5,)](xh, w, y, 1000, 1000, 1e-6, BLOCK=1024)
+    xf = xh.float()
+    ref = xf * torch.rsqrt((xf * xf).mean(dim=1, keepdim=True) + 1e-6) * w.float()
+    out.append(("rmsnorm", y.float().cpu(), ref.cpu(), 2e-2))
+    xi = torch.randint(-1000, 1000, (50, 24), dtype=torch.int32, device=dev)
+    rmax = torch.full((50,), -7, dtype=torch.int32, device=dev)
+    cmin = torch.full((4 * 32,), -7, dtype=torch.int32, device=dev)
+    K.tile_max_kernel[(4,)](xi, rmax, cmin, 24, 50, 24, BM=16, BN=32)
+    out.append(("tile_rowmax", rmax.cpu(), torch.maximum(xi.max(dim=1).values, torch.zeros(1, dtype=torch.int32, device=dev)).cpu(), 0))
+    exp_cmin = torch.full((4, 32), -7, dtype=torch.int32)
+    xc = xi.cpu()
+    for pid in range(4):
+        blk = torch.zeros(16, 32, dtype=torch.int32)
+        rows = xc[pid * 16:(pid + 1) * 16]
+        blk[:rows.shape[0], :24] = rows
+        exp_cmin[pid, :24] = blk.min(dim=0).values[:24]
+    out.append(("tile_colmin", cmin.cpu().reshape(4, 32), exp_cmin, 0))
+    return out
+
+
+def test_block_programs_on_host_stand_in():
+    with fake_device() as lib:
+        cases = _block_program_cases("cpu")
+    for name, got, exp, tol in cases:
+        if tol == 0:
+            assert torch.equal(got, exp), name
+        else:
+            assert torch.allclose(got, exp, rtol=tol, atol=tol), name
+    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 3

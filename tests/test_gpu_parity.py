@@ -351,3 +351,13 @@ def test_wraparound_large_blocks(drv):
     K.wrap_rows_kernel[(1,)](A, C, M, N, 1, N, 1, START=40, BM=64, BN=64, STEPS=4)
     rows = (40 + torch.arange(64, device="cuda")) % M
     assert torch.equal(C, A[rows])
+
+
+def test_block_programs(drv):
+    """Bodies with tt.reduce (sum to scalar, RMS norm, axis-0 and axis-1 integer max/min): block-program kernel."""
+    from test_cpu_host import _block_program_cases
+    for name, got, exp, tol in _block_program_cases("cuda"):
+        if tol == 0:
+            assert torch.equal(got, exp), name
+        else:
+            assert torch.allclose(got, exp, rtol=tol, atol=tol), name

@@ -460,7 +460,7 @@ def _reads(o):
     if opc in ("select", "fma"):
         return [o[3], o[4], o[5]]
     if opc in ("exp", "exp2", "log", "log2", "sqrt", "rsqrt", "sin", "cos", "tanh", "erf", "absf", "negf",
-               "floor", "ceil", "absi", "cast", "bitcast", "mov"):
+               "floor", "ceil", "absi", "cast", "bitcast", "mov", "reduce"):
         return [o[3]]
     return [o[3], o[4]]
 
@@ -635,7 +635,9 @@ class ElementwisePlan(Plan):
             x.opcode = rt.OPCODES[opc]
             x.type = rt.DTYPES[dt]
             x.dst, x.a, x.b, x.c = max(dst, 0), ra, rb, rc
-            if isinstance(imm, (list, tuple)):
+            if isinstance(imm, str):
+                x.imm = rt.OPCODES[imm]  # combiner of a reduction
+            elif isinstance(imm, (list, tuple)):
                 if imm[0] == "poly":
                     x.imm = int(imm[1].evaluate(e0)) & 0xffffffff
                 else:  # farg
@@ -644,6 +646,238 @@ class ElementwisePlan(Plan):
                 x.imm = imm
             x.imm2 = imm2
         return accs, ops, arg_of
+
+
+# --------------------------------------------------------------------------
+# block programs: loop-free bodies with reductions along block axes
+
+class _DimUnion:
+    """Union-find over symbolic block dims, used to discover the iteration space of a body with reductions."""
+
+    def __init__(self):
+        self.parent, self.size = {}, {}
+
+    def fresh(self, size: int):
+        d = len(self.parent)
+        self.parent[d], self.size[d] = d, size
+        return d
+
+    def find(self, d):
+        while self.parent[d] != d:
+            self.parent[d] = self.parent[self.parent[d]]
+            d = self.parent[d]
+        return d
+
+    def union(self, a, b):
+        ra, rb = self.find(a), self.find(b)
+        if ra == rb:
+            return
+        if self.size[ra] != self.size[rb]:
+            raise UnsupportedTTIR("block program: dims of different sizes would have to coincide")
+        self.parent[max(ra, rb)] = min(ra, rb)
+
+
+def _discover_space(stores: List[Access]):
+    """Symbolic dims of every node reachable from the stores.  A reduction introduces a dim its result
+    does not have; a node reached along two paths has one set of dims (they are unified).
+    Returns (ordered space dims, {node id: tuple of space positions})."""
+    uf = _DimUnion()
+    node_dims: Dict[int, tuple] = {}
+    order: List[tuple] = []  # (a, b): dim a precedes dim b in some node
+    red_dim: Dict[int, int] = {}
+
+    def visit(n: Node, dims: tuple):
+        if n.id in node_dims:
+            for a, b in zip(node_dims[n.id], dims):
+                uf.union(a, b)
+            return
+        node_dims[n.id] = dims
+        order.extend(zip(dims, dims[1:]))
+        if n.op in ("splat",):
+            visit(n.args[0], ())
+        elif n.op == "broadcast":
+            visit(n.args[0], dims)
+        elif n.op == "expand_dims":
+            ax = n.attr("axis")
+            visit(n.args[0], dims[:ax] + dims[ax + 1:])
+        elif n.op == "reduce":
+            ax = n.attr("axis")
+            src = n.args[0]
+            d = red_dim.setdefault(n.id, uf.fresh(src.shape[ax]))
+            visit(src, dims[:ax] + (d,) + dims[ax:])
+        elif n.op in ("dot", "iter_arg", "loop_result"):
+            raise UnsupportedTTIR(f"block program: operation {n.op}")
+        else:
+            for a in n.args:
+                if isinstance(a, Node):
+                    visit(a, dims if a.shape == n.shape or len(a.shape) == len(dims) else ())
+
+    for st in stores:
+        visit(st.value, tuple(uf.fresh(sz) for sz in st.shape))
+        node_dims[("store", id(st))] = node_dims[st.value.id]
+    reps = []
+    for dims in node_dims.values():
+        r = [uf.find(d) for d in dims]
+        if len(set(r)) != len(r):
+            raise UnsupportedTTIR("block program: one value is indexed twice by the same dim")
+        for d in r:
+            if d not in reps:
+                reps.append(d)
+    # order the space so that every node's dims appear in increasing position
+    edges = {(uf.find(a), uf.find(b)) for a, b in order if uf.find(a) != uf.find(b)}
+    space: List[int] = []
+    remaining = list(reps)
+    while remaining:
+        free = [d for d in remaining if not any(b == d and a in remaining for a, b in edges)]
+        if not free:
+            raise UnsupportedTTIR("block program: the values' dims cannot be ordered consistently (transposed use)")
+        space.append(free[0])
+        remaining.remove(free[0])
+    pos = {d: i for i, d in enumerate(space)}
+    maps = {k: tuple(pos[uf.find(d)] for d in dims) for k, dims in node_dims.items()}
+    sizes = [uf.size[d] for d in space]
+    red_pos = {nid: pos[uf.find(d)] for nid, d in red_dim.items()}
+    return sizes, maps, red_pos
+
+
+class _BpLowering(_EwLowering):
+    """Lowering for tsb_block_program: registers carry a mask of the space dims they extend along."""
+
+    def __init__(self, kernel, an, space, red_pos):
+        super().__init__(kernel, an, tuple(space))
+        self.vmask: Dict[int, int] = {}
+        self.acc_mask: Dict[int, int] = {}
+        self.red_pos = red_pos
+
+    def acc_for(self, kind, elem, shape, dimmap, *a, **kw):
+        ai = super().acc_for(kind, elem, shape, dimmap, *a, **kw)
+        m = 0
+        for d, it_d in enumerate(dimmap):
+            if shape[d] > 1:
+                m |= 1 << it_d
+        self.acc_mask[ai] = m
+        return ai
+
+    def emit(self, opcode, dtype, a=0, b=0, c=0, imm=0, imm2=0, mask=None):
+        dst = self.new()
+        op = [opcode, dtype, dst, a, b, c, imm, imm2]
+        if mask is None:
+            if opcode == "load":
+                mask = self.acc_mask[a]
+            else:
+                mask = 0
+                for r in _reads(op):
+                    mask |= self.vmask[r]
+        self.vmask[dst] = mask
+        self.ops.append(op)
+        return dst
+
+    def _value(self, n: Node, dimmap):
+        if n.op == "reduce":
+            ax, comb = n.attr("axis"), n.attr("comb")
+            if comb not in ("addf", "mulf", "maxnumf", "minnumf", "maximumf", "minimumf", "addi", "muli", "maxsi",
+                            "minsi", "maxui", "minui", "andi", "ori", "xori"):
+                raise UnsupportedTTIR(f"block program: reduction with combiner {comb}")
+            d = self.red_pos[n.id]
+            src = self.value(n.args[0], dimmap[:ax] + (d,) + dimmap[ax:])
+            return self.emit("reduce", n.dtype, a=src, imm=comb, imm2=d, mask=self.vmask[src] & ~(1 << d))
+        return super()._value(n, dimmap)
+
+    def lower(self, stores, maps):
+        for acc in stores:
+            dimmap = maps[("store", id(acc))]
+            v = self.value(acc.value, dimmap)
+            ai = self.acc_for("store", acc.elem, acc.shape, dimmap, acc.offset, acc.strides,
+                              _mask_json(acc.mask, acc.shape), None, acc.arg, acc.wrapped)
+            self.ops.append(["store", acc.elem, -1, ai, v, 0, self.acc_mask[ai], 0])
+        return self.allocate_masked()
+
+    def allocate_masked(self):
+        """Physical registers are shared-memory regions; a region is reused only by values of the same mask."""
+        ops = self.ops
+        last_use: Dict[int, int] = {}
+        for i, o in enumerate(ops):
+            for r in _reads(o):
+                last_use[r] = i
+        free: Dict[int, List[int]] = {}
+        masks: List[int] = []
+        phys: Dict[int, int] = {}
+        out = []
+        for i, o in enumerate(ops):
+            o = list(o)
+            reads = _reads(o)
+            mapped = {r: phys[r] for r in reads}
+            if o[0] != "store":
+                m = self.vmask[o[2]]
+                # an elementwise result may overwrite an operand of the same mask that dies here; a
+                # reduction never writes into its own source
+                if o[0] != "reduce":
+                    for r in set(reads):
+                        if last_use[r] == i and r in phys:
+                            free.setdefault(self.vmask[r], []).append(phys.pop(r))
+                if free.get(m):
+                    dst = free[m].pop()
+                else:
+                    dst = len(masks)
+                    masks.append(m)
+                if o[2] in last_use:
+                    phys[o[2]] = dst
+                else:
+                    free.setdefault(m, []).append(dst)
+                o[2] = dst
+            _remap(o, mapped)
+            for r in set(reads):
+                if last_use[r] == i and r in phys:
+                    free.setdefault(self.vmask[r], []).append(phys.pop(r))
+            out.append(o)
+        if len(masks) > 24:
+            raise UnsupportedTTIR("block program: more than 24 block values alive")
+        if len(out) > rt.TSB_MAX_OPS or len(self.accs) > rt.TSB_MAX_ACCESSES:
+            raise UnsupportedTTIR("block program: too many ops or accesses")
+        words = sum(int(np.prod([self.space[d] for d in range(len(self.space)) if m & (1 << d)])) for m in masks)
+        if words * 4 > 200 * 1024:
+            raise UnsupportedTTIR(f"block program: {words * 4} bytes of block values exceed the 200 KB on-chip budget")
+        return out, masks
+
+
+class BlockProgramPlan(Plan):
+    """Loop-free bodies with tt.reduce along block axes: one CTA per program, values in shared memory."""
+    family = "block_program"
+
+    @staticmethod
+    def build(kernel: Kernel, an: Analyzer) -> "BlockProgramPlan":
+        stores = []
+        for kind, e in kernel.effects:
+            if kind != "store":
+                raise UnsupportedTTIR("block_program family: kernel contains a loop")
+            stores.append(e)
+        if not stores:
+            raise UnsupportedTTIR("kernel stores nothing")
+        sizes, maps, red_pos = _discover_space(stores)
+        if not red_pos:
+            raise UnsupportedTTIR("block_program family: no reduction in the body")
+        if not sizes:
+            sizes = [1]
+        if len(sizes) > rt.TSB_MAX_RANK:
+            raise UnsupportedTTIR(f"block program: iteration space of rank {len(sizes)}")
+        low = _BpLowering(kernel, an, sizes, red_pos)
+        ops, masks = low.lower(stores, maps)
+        return BlockProgramPlan(kernel.name, {"seg": {"space": list(sizes), "accs": low.accs, "ops": ops},
+                                              "reg_masks": masks})
+
+    def launch(self, args, grid, pid_lo, pid_hi, stream):
+        def compute():
+            accs, ops, arg_of = ElementwisePlan._evaluate(self, self.p["seg"], args, LaunchEnv(args.scalars, grid))
+            masks = (ctypes.c_int32 * len(self.p["reg_masks"]))(*self.p["reg_masks"])
+            return accs, ops, arg_of, masks
+        accs, ops, arg_of, masks = self.memo(args, grid, compute)
+        for a, i in zip(accs, arg_of):
+            if i is not None:
+                a.base = args.pointer(i)
+        g = (ctypes.c_int32 * 3)(*grid)
+        rc = rt.lib().tsb_block_program(accs, len(accs), ops, len(ops), masks, len(masks), g, pid_lo, pid_hi, stream)
+        if rc:
+            rt.check(rc, f"tsb_block_program[{self.name}]")
 
 
 # --------------------------------------------------------------------------
@@ -1203,8 +1437,8 @@ class GemmPlan(Plan):
 
 
 _FAMILIES = {c.family: c for c in (GemmPlan, LayerNormPlan, SoftmaxPlan, ReduceRowsPlan, ReduceAllPlan,
-                                   ElementwisePlan)}
-_ORDER = [GemmPlan, LayerNormPlan, SoftmaxPlan, ReduceRowsPlan, ReduceAllPlan, ElementwisePlan]
+                                   ElementwisePlan, BlockProgramPlan)}
+_ORDER = [GemmPlan, LayerNormPlan, SoftmaxPlan, ReduceRowsPlan, ReduceAllPlan, ElementwisePlan, BlockProgramPlan]
 
 
 def make_plan(kernel: Kernel, an: Analyzer) -> Plan:

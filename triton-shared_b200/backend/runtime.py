@@ -29,7 +29,7 @@ OPCODES = {
     "addi": 50, "subi": 51, "muli": 52, "divsi": 53, "remsi": 54, "divui": 55, "remui": 56,
     "minsi": 57, "maxsi": 58, "minui": 59, "maxui": 60, "andi": 61, "ori": 62, "xori": 63,
     "shli": 64, "shrsi": 65, "shrui": 66, "absi": 67,
-    "cmpf": 80, "cmpi": 81, "select": 82, "cast": 90, "bitcast": 91, "fma": 92,
+    "cmpf": 80, "cmpi": 81, "select": 82, "cast": 90, "bitcast": 91, "fma": 92, "reduce": 100,
 }
 CMPF = {"oeq": 1, "ogt": 2, "oge": 3, "olt": 4, "ole": 5, "one": 6, "ord": 7, "ueq": 8, "ugt": 9,
         "uge": 10, "ult": 11, "ule": 12, "une": 13, "uno": 14}
@@ -95,7 +95,7 @@ class TsbError(RuntimeError):
 _lib = None
 
 # every symbol include/tsb200.h declares
-SYMBOLS = ["tsb_last_error", "tsb_version", "tsb_sm_count", "tsb_elementwise", "tsb_block_copy",
+SYMBOLS = ["tsb_last_error", "tsb_version", "tsb_sm_count", "tsb_elementwise", "tsb_block_program", "tsb_block_copy",
            "tsb_softmax_rows", "tsb_layernorm_fwd", "tsb_reduce_rows_scratch_bytes", "tsb_reduce_rows",
            "tsb_reduce_rows_static", "tsb_reduce_all", "tsb_gemm", "tsb_gemm_paired"]
 
@@ -117,6 +117,9 @@ def lib():
     L.tsb_elementwise.restype = ctypes.c_int
     L.tsb_elementwise.argtypes = [ctypes.POINTER(Access), ctypes.c_int, ctypes.POINTER(Op), ctypes.c_int,
                                   ctypes.POINTER(i32), i64, i64, vp]
+    L.tsb_block_program.restype = ctypes.c_int
+    L.tsb_block_program.argtypes = [ctypes.POINTER(Access), ctypes.c_int, ctypes.POINTER(Op), ctypes.c_int,
+                                    ctypes.POINTER(i32), ctypes.c_int, ctypes.POINTER(i32), i64, i64, vp]
     L.tsb_block_copy.restype = ctypes.c_int
     L.tsb_block_copy.argtypes = [ctypes.POINTER(Access), ctypes.POINTER(Access), ctypes.POINTER(i32), i64, i64, vp]
     L.tsb_softmax_rows.restype = ctypes.c_int

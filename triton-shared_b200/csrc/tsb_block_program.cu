@@ -1,0 +1,240 @@
+// Block programs: bodies that mix structured loads/stores, elementwise ops and reductions
+// over whole blocks (tt.reduce along an axis), one Triton program per CTA.
+//
+// Reference semantics (paths inside microsoft/triton-shared): tt.reduce becomes a transpose
+// plus linalg.reduce with a single-op combiner folded from the combiner's identity
+// (ReduceConverter, ConversionPatterns.hpp:1203-1440); the surrounding ops are the same
+// linalg.generic / memref.copy forms as in tsb_elementwise.cu.  The CPU backend keeps every
+// intermediate block in a malloc'ed buffer; here every intermediate lives in shared memory
+// for the lifetime of the program and never touches HBM.
+//
+// Values ("registers") are indexed by the coordinates of one iteration space of rank <= 3; a
+// register extends along a subset of the dims (its mask) and is broadcast along the others,
+// which is how splat / expand_dims / broadcast and keep-dim reduction results are expressed.
+// Ops run one after another over the whole block with a barrier between them.  This is the
+// general path: the dedicated softmax / LayerNorm / reduction kernels are faster where they apply.
+#include "tsb_vm.cuh"
+
+namespace tsb {
+
+constexpr int BP_MAX_REGS = 24;
+constexpr int BP_THREADS = 256;
+
+struct BpParams {
+  DAcc acc[TSB_MAX_ACCESSES];
+  tsb_op ops[TSB_MAX_OPS];
+  int n_acc, n_ops, n_regs;
+  int size[3];
+  int grid[3];
+  long long pid_lo, pid_hi;
+  int reg_mask[BP_MAX_REGS];  // bit d set: the register extends along dim d
+  int reg_off[BP_MAX_REGS];   // offset (32-bit words) in dynamic shared memory
+  int reg_n[BP_MAX_REGS];     // number of elements
+};
+
+// coordinates of element e of a register with mask m (row-major over its present dims)
+__device__ __forceinline__ void reg_coords(const int size[3], int m, int e, int &i0, int &i1, int &i2) {
+  const int s2 = (m & 4) ? size[2] : 1, s1 = (m & 2) ? size[1] : 1;
+  i2 = e % s2;
+  e /= s2;
+  i1 = e % s1;
+  i0 = e / s1;
+}
+// element index of coordinates (i0,i1,i2) in a register with mask m (absent dims are broadcast)
+__device__ __forceinline__ int reg_index(const int size[3], int m, int i0, int i1, int i2) {
+  const int s2 = (m & 4) ? size[2] : 1, s1 = (m & 2) ? size[1] : 1;
+  return (((m & 1) ? i0 : 0) * s1 + ((m & 2) ? i1 : 0)) * s2 + ((m & 4) ? i2 : 0);
+}
+
+__device__ __forceinline__ unsigned alu_scalar(const tsb_op &op, unsigned a, unsigned b, unsigned c) {
+  const int opc = op.opcode;
+  if (opc == TSB_OP_CONST) return op.imm;
+  if (opc == TSB_OP_MOV || opc == TSB_OP_BITCAST) return a;
+  if (opc >= TSB_OP_ADDF && opc < TSB_OP_EXP)
+    return __float_as_uint(round_to(binf(opc, __uint_as_float(a), __uint_as_float(b)), op.type));
+  if (opc >= TSB_OP_EXP && opc < TSB_OP_ADDI) return __float_as_uint(round_to(unf(opc, __uint_as_float(a)), op.type));
+  if (opc == TSB_OP_ABSI) return wrap_to((unsigned)abs((int)a), op.type);
+  if (opc >= TSB_OP_ADDI && opc < TSB_OP_CMPF) return wrap_to(bini(opc, a, b), op.type);
+  if (opc == TSB_OP_CMPF) return cmpf_(op.imm, __uint_as_float(a), __uint_as_float(b));
+  if (opc == TSB_OP_CMPI) return cmpi_(op.imm, a, b);
+  if (opc == TSB_OP_SELECT) return (a & 1u) ? b : c;
+  if (opc == TSB_OP_CAST) return cast_(a, (int)op.imm, op.type, op.imm2);
+  if (opc == TSB_OP_FMA)
+    return __float_as_uint(round_to(fmaf(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c)), op.type));
+  return 0u;
+}
+
+__device__ __forceinline__ unsigned combine(int comb, int type, unsigned a, unsigned b) {
+  if (comb >= TSB_OP_ADDF && comb < TSB_OP_EXP)
+    return __float_as_uint(round_to(binf(comb, __uint_as_float(a), __uint_as_float(b)), type));
+  return wrap_to(bini(comb, a, b), type);
+}
+// identity of the combiner (what the reference initialises the accumulator with,
+// ConversionPatterns.hpp:1227-1278)
+__device__ __forceinline__ unsigned combine_identity(int comb) {
+  switch (comb) {
+    case TSB_OP_ADDF: return 0u;
+    case TSB_OP_MULF: return 0x3f800000u;
+    case TSB_OP_MAXNUMF: case TSB_OP_MAXIMUMF: return 0xff800000u;
+    case TSB_OP_MINNUMF: case TSB_OP_MINIMUMF: return 0x7f800000u;
+    case TSB_OP_MULI: return 1u;
+    case TSB_OP_ANDI: return 0xffffffffu;
+    case TSB_OP_MAXSI: return 0x80000000u;
+    case TSB_OP_MINSI: return 0x7fffffffu;
+    case TSB_OP_MINUI: return 0xffffffffu;
+  }
+  return 0u;  // addi, ori, xori, maxui
+}
+
+__global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_constant__ BpParams P) {
+  extern __shared__ unsigned bp_smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
+    long long px, py, pz;
+    split_pid(P.grid, prog, px, py, pz);
+    for (int k = 0; k < P.n_ops; ++k) {
+      __syncthreads();  // every op may read what other threads wrote in the previous one
+      const tsb_op &op = P.ops[k];
+      if (op.opcode == TSB_OP_LOAD) {
+        const DAcc &A = P.acc[op.a];
+        ProgState st;
+        program_state(A, P.size, px, py, pz, st);
+        const int m = P.reg_mask[op.dst];
+        unsigned *dst = bp_smem + P.reg_off[op.dst];
+        for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
+          int i0, i1, i2;
+          reg_coords(P.size, m, e, i0, i1, i2);
+          unsigned v[1];
+          load_vec<1>(A, st, i0, i1, i2, v);
+          dst[e] = v[0];
+        }
+      } else if (op.opcode == TSB_OP_STORE) {
+        const DAcc &A = P.acc[op.a];
+        ProgState st;
+        program_state(A, P.size, px, py, pz, st);
+        const int m = (int)op.imm;  // dims the store extends along
+        const int ms = P.reg_mask[op.b];
+        const unsigned *src = bp_smem + P.reg_off[op.b];
+        const int n = ((m & 1) ? P.size[0] : 1) * ((m & 2) ? P.size[1] : 1) * ((m & 4) ? P.size[2] : 1);
+        for (int e = tid; e < n; e += BP_THREADS) {
+          int i0, i1, i2;
+          reg_coords(P.size, m, e, i0, i1, i2);
+          unsigned v[1] = {src[reg_index(P.size, ms, i0, i1, i2)]};
+          store_vec<1>(A, st, i0, i1, i2, v);
+        }
+      } else if (op.opcode == TSB_OP_REDUCE) {
+        // dst = fold of src along dim imm2 with combiner imm; one warp per output element
+        const int d = (int)op.imm2, comb = (int)op.imm;
+        const int ms = P.reg_mask[op.a], md = P.reg_mask[op.dst];
+        const unsigned *src = bp_smem + P.reg_off[op.a];
+        unsigned *dst = bp_smem + P.reg_off[op.dst];
+        const int len = P.size[d];
+        for (int o = warp; o < P.reg_n[op.dst]; o += BP_THREADS / 32) {
+          int c[3];
+          reg_coords(P.size, md, o, c[0], c[1], c[2]);
+          unsigned acc = combine_identity(comb);
+          for (int j = lane; j < len; j += 32) {
+            c[d] = j;
+            acc = combine(comb, op.type, src[reg_index(P.size, ms, c[0], c[1], c[2])], acc);
+          }
+#pragma unroll
+          for (int s = 16; s > 0; s >>= 1) acc = combine(comb, op.type, __shfl_xor_sync(0xffffffffu, acc, s), acc);
+          if (lane == 0) dst[o] = acc;
+        }
+      } else {
+        const int md = P.reg_mask[op.dst];
+        unsigned *dst = bp_smem + P.reg_off[op.dst];
+        const int ma = P.reg_mask[op.a], mb = P.reg_mask[op.b], mc = P.reg_mask[op.c];
+        const unsigned *ra = bp_smem + P.reg_off[op.a], *rb = bp_smem + P.reg_off[op.b], *rc = bp_smem + P.reg_off[op.c];
+        for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
+          int i0, i1, i2;
+          reg_coords(P.size, md, e, i0, i1, i2);
+          dst[e] = alu_scalar(op, ra[reg_index(P.size, ma, i0, i1, i2)], rb[reg_index(P.size, mb, i0, i1, i2)],
+                              rc[reg_index(P.size, mc, i0, i1, i2)]);
+        }
+      }
+    }
+    __syncthreads();  // the next program reuses the registers
+  }
+}
+
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
+                                 const int32_t *reg_masks, int n_regs, const int32_t grid[3],
+                                 int64_t pid_lo, int64_t pid_hi, void *stream) {
+  if (!acc || !ops || !reg_masks || !grid) return fail(TSB_ERR_INVALID, "tsb_block_program: null argument");
+  if (n_acc < 1 || n_acc > TSB_MAX_ACCESSES || n_ops < 1 || n_ops > TSB_MAX_OPS || n_regs < 1 || n_regs > BP_MAX_REGS)
+    return fail(TSB_ERR_UNSUPPORTED, "tsb_block_program: %d accesses / %d ops / %d registers (max %d / %d / %d)", n_acc,
+                n_ops, n_regs, TSB_MAX_ACCESSES, TSB_MAX_OPS, BP_MAX_REGS);
+  const long long total = (long long)grid[0] * grid[1] * grid[2];
+  if (pid_lo < 0 || pid_hi > total || pid_lo > pid_hi)
+    return fail(TSB_ERR_INVALID, "tsb_block_program: program range [%lld,%lld) outside grid of %lld",
+                (long long)pid_lo, (long long)pid_hi, total);
+  static thread_local BpParams P;
+  memset(&P, 0, sizeof(P));
+  const int rank = acc[0].rank;
+  if (rank < 1 || rank > TSB_MAX_RANK) return fail(TSB_ERR_UNSUPPORTED, "tsb_block_program: rank %d", rank);
+  P.size[0] = P.size[1] = P.size[2] = 1;
+  for (int d = 0; d < rank; ++d) {
+    if (acc[0].sizes[d] < 1 || acc[0].sizes[d] > (1 << 20)) return fail(TSB_ERR_INVALID, "tsb_block_program: bad block size");
+    P.size[3 - rank + d] = (int)acc[0].sizes[d];
+  }
+  for (int a = 0; a < n_acc; ++a) {
+    int rc = convert_access(acc, a, rank, P.size, grid, 1, P.acc[a]);
+    if (rc != TSB_OK) return rc;
+  }
+  long long words = 0;
+  for (int r = 0; r < n_regs; ++r) {
+    const int m = reg_masks[r];
+    if (m < 0 || m > 7) return fail(TSB_ERR_INVALID, "tsb_block_program: register %d has mask %d", r, m);
+    // masks are given over the access rank; shift to the padded rank-3 space
+    const int pm = m << (3 - rank);
+    long long n = 1;
+    for (int d = 0; d < 3; ++d)
+      if (pm & (1 << d)) n *= P.size[d];
+    P.reg_mask[r] = pm;
+    P.reg_off[r] = (int)words;
+    P.reg_n[r] = (int)n;
+    words += n;
+  }
+  const long long smem = words * 4;
+  if (smem > 200 * 1024)
+    return fail(TSB_ERR_UNSUPPORTED, "tsb_block_program: %lld bytes of block values exceed the 200 KB on-chip budget", smem);
+  for (int k = 0; k < n_ops; ++k) {
+    tsb_op o = ops[k];
+    const bool mem = o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_STORE;
+    if (mem && (o.a < 0 || o.a >= n_acc)) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d names access %d", k, o.a);
+    if (o.opcode == TSB_OP_LOAD && acc[o.a].is_store == 1) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d loads from a store access", k);
+    if (o.opcode == TSB_OP_STORE && acc[o.a].is_store != 1) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d stores to a load access", k);
+    if (o.opcode == TSB_OP_STORE) o.imm = o.imm << (3 - rank);
+    if (o.opcode == TSB_OP_REDUCE) {
+      if (o.imm2 >= (unsigned)rank) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d reduces dim %u of rank %d", k, o.imm2, rank);
+      o.imm2 += 3 - rank;
+    }
+    const int regs[4] = {o.opcode == TSB_OP_STORE ? 0 : o.dst, mem || o.opcode == TSB_OP_CONST ? 0 : o.a,
+                         o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_CONST ? 0 : o.b, o.c};
+    for (int r = 0; r < 4; ++r)
+      if (regs[r] < 0 || regs[r] >= n_regs) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d register %d out of range", k, regs[r]);
+    P.ops[k] = o;
+  }
+  P.n_acc = n_acc; P.n_ops = n_ops; P.n_regs = n_regs;
+  for (int k = 0; k < 3; ++k) P.grid[k] = grid[k] > 0 ? grid[k] : 1;
+  P.pid_lo = pid_lo; P.pid_hi = pid_hi;
+  if (pid_hi == pid_lo) return TSB_OK;
+  static long long smem_set = 0;
+  if (smem > 48 * 1024 && smem_set < smem) {
+    TSB_CUDA_OK(cudaFuncSetAttribute(block_program_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    smem_set = 200 * 1024;
+  }
+  long long per_sm = smem > 0 ? (220 * 1024) / (smem + 1024) : 8;
+  if (per_sm > 8) per_sm = 8;
+  if (per_sm < 1) per_sm = 1;
+  long long ctas = (long long)sm_count() * per_sm;
+  if (ctas > pid_hi - pid_lo) ctas = pid_hi - pid_lo;
+  block_program_kernel<<<(unsigned)ctas, BP_THREADS, (size_t)smem, (cudaStream_t)stream>>>(P);
+  TSB_LAUNCH_OK("block_program_kernel");
+  return TSB_OK;
+}

@@ -10,34 +10,9 @@
 //   elementwise op  lib/Conversion/TritonArithToLinalg/TritonArithToLinalg.cpp:104
 // The CPU backend materialises every block in a malloc'ed buffer and runs one
 // scalar loop per op; here a lane's values stay in registers from load to store.
-#include "tsb_common.cuh"
-#include <math.h>
-#include <string.h>
+#include "tsb_vm.cuh"
 
 namespace tsb {
-
-struct DAcc {
-  char *base;
-  long long off0;
-  long long off_pid[3];
-  long long stride[3];
-  long long mstart0[3];
-  long long mstart_pid[3][3];
-  long long bound[3];
-  int masked;     // bit d set: dim d carries a mask
-  int dtype;
-  int esize;
-  int vec_ok;     // innermost dim contiguous and every vector 16B/8B/4B aligned
-  int has_other;
-  unsigned other; // fill value in register representation
-  int kind;       // 0 memory load, 1 memory store, 2 mask probe, 3 index probe
-  int n_wrap;     // wrap-around (modulo) terms
-  int wrap_inner; // some wrap term is on the innermost dim (lanes of a vector differ non-linearly)
-  struct {
-    int dim;
-    long long off0, off_pid[3], stride, modulus, scale;
-  } wrap[2];
-};
 
 struct EwParams {
   DAcc acc[TSB_MAX_ACCESSES];
@@ -49,316 +24,6 @@ struct EwParams {
   int grid[3];
   long long pid_lo, pid_hi;
 };
-
-// ---- register representation -------------------------------------------------
-// Every VM lane is 32 bits: f32 bits for all float types (f16/bf16 values are
-// held exactly widened and re-rounded after each op), sign/zero-extended ints.
-
-__device__ __forceinline__ unsigned ld_elem(const char *p, int dt) {
-  switch (dt) {
-    case TSB_F32: case TSB_I32: case TSB_U32: return *reinterpret_cast<const unsigned *>(p);
-    case TSB_F16: return __float_as_uint(__half2float(*reinterpret_cast<const __half *>(p)));
-    case TSB_BF16: return __float_as_uint(__bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p)));
-    case TSB_I16: return (unsigned)(int)*reinterpret_cast<const short *>(p);
-    case TSB_U16: return (unsigned)*reinterpret_cast<const unsigned short *>(p);
-    case TSB_I8: return (unsigned)(int)*reinterpret_cast<const signed char *>(p);
-    case TSB_U8: case TSB_I1: return (unsigned)*reinterpret_cast<const unsigned char *>(p);
-  }
-  return 0u;
-}
-__device__ __forceinline__ void st_elem(char *p, int dt, unsigned v) {
-  switch (dt) {
-    case TSB_F32: case TSB_I32: case TSB_U32: *reinterpret_cast<unsigned *>(p) = v; break;
-    case TSB_F16: *reinterpret_cast<__half *>(p) = __float2half_rn(__uint_as_float(v)); break;
-    case TSB_BF16: *reinterpret_cast<__nv_bfloat16 *>(p) = __float2bfloat16_rn(__uint_as_float(v)); break;
-    case TSB_I16: case TSB_U16: *reinterpret_cast<unsigned short *>(p) = (unsigned short)v; break;
-    case TSB_I8: case TSB_U8: *reinterpret_cast<unsigned char *>(p) = (unsigned char)v; break;
-    case TSB_I1: *reinterpret_cast<unsigned char *>(p) = (unsigned char)(v & 1u); break;
-  }
-}
-
-// Round an fp32 result to the value set of `dt` (identity for f32).
-__device__ __forceinline__ float round_to(float x, int dt) {
-  if (dt == TSB_F16) return __half2float(__float2half_rn(x));
-  if (dt == TSB_BF16) return __bfloat162float(__float2bfloat16_rn(x));
-  return x;
-}
-// Wrap an integer result to the width of `dt`.
-__device__ __forceinline__ unsigned wrap_to(unsigned x, int dt) {
-  switch (dt) {
-    case TSB_I16: return (unsigned)(int)(short)x;
-    case TSB_U16: return x & 0xffffu;
-    case TSB_I8: return (unsigned)(int)(signed char)x;
-    case TSB_U8: return x & 0xffu;
-    case TSB_I1: return x & 1u;
-  }
-  return x;
-}
-
-__device__ __forceinline__ float maximumf_(float a, float b) {
-  return (a != a || b != b) ? __uint_as_float(0x7fc00000u) : fmaxf(a, b);
-}
-__device__ __forceinline__ float minimumf_(float a, float b) {
-  return (a != a || b != b) ? __uint_as_float(0x7fc00000u) : fminf(a, b);
-}
-
-__device__ __forceinline__ float binf(int opc, float a, float b) {
-  switch (opc) {
-    case TSB_OP_ADDF: return a + b;
-    case TSB_OP_SUBF: return a - b;
-    case TSB_OP_MULF: return a * b;
-    case TSB_OP_DIVF: return a / b;
-    case TSB_OP_MAXNUMF: return fmaxf(a, b);
-    case TSB_OP_MINNUMF: return fminf(a, b);
-    case TSB_OP_MAXIMUMF: return maximumf_(a, b);
-    case TSB_OP_MINIMUMF: return minimumf_(a, b);
-    case TSB_OP_REMF: return fmodf(a, b);
-  }
-  return 0.f;
-}
-__device__ __forceinline__ float unf(int opc, float a) {
-  switch (opc) {
-    case TSB_OP_EXP: return expf(a);
-    case TSB_OP_EXP2: return exp2f(a);
-    case TSB_OP_LOG: return logf(a);
-    case TSB_OP_LOG2: return log2f(a);
-    case TSB_OP_SQRT: return sqrtf(a);
-    case TSB_OP_RSQRT: return 1.0f / sqrtf(a);
-    case TSB_OP_SIN: return sinf(a);
-    case TSB_OP_COS: return cosf(a);
-    case TSB_OP_TANH: return tanhf(a);
-    case TSB_OP_ERF: return erff(a);
-    case TSB_OP_ABSF: return fabsf(a);
-    case TSB_OP_NEGF: return -a;
-    case TSB_OP_FLOOR: return floorf(a);
-    case TSB_OP_CEIL: return ceilf(a);
-  }
-  return 0.f;
-}
-__device__ __forceinline__ unsigned bini(int opc, unsigned ua, unsigned ub) {
-  int a = (int)ua, b = (int)ub;
-  switch (opc) {
-    case TSB_OP_ADDI: return ua + ub;
-    case TSB_OP_SUBI: return ua - ub;
-    case TSB_OP_MULI: return ua * ub;
-    case TSB_OP_DIVSI: return b == 0 ? 0u : (b == -1 ? (unsigned)(0u - ua) : (unsigned)(a / b));
-    case TSB_OP_REMSI: return (b == 0 || b == -1) ? 0u : (unsigned)(a % b);
-    case TSB_OP_DIVUI: return ub == 0 ? 0u : ua / ub;
-    case TSB_OP_REMUI: return ub == 0 ? 0u : ua % ub;
-    case TSB_OP_MINSI: return (unsigned)min(a, b);
-    case TSB_OP_MAXSI: return (unsigned)max(a, b);
-    case TSB_OP_MINUI: return min(ua, ub);
-    case TSB_OP_MAXUI: return max(ua, ub);
-    case TSB_OP_ANDI: return ua & ub;
-    case TSB_OP_ORI: return ua | ub;
-    case TSB_OP_XORI: return ua ^ ub;
-    case TSB_OP_SHLI: return ub >= 32 ? 0u : ua << ub;
-    case TSB_OP_SHRSI: return (unsigned)(a >> (ub >= 32 ? 31 : ub));
-    case TSB_OP_SHRUI: return ub >= 32 ? 0u : ua >> ub;
-  }
-  return 0u;
-}
-__device__ __forceinline__ unsigned cmpf_(unsigned pred, float a, float b) {
-  bool un = (a != a) || (b != b);
-  switch (pred) {
-    case TSB_CMPF_OEQ: return !un && a == b;
-    case TSB_CMPF_OGT: return !un && a > b;
-    case TSB_CMPF_OGE: return !un && a >= b;
-    case TSB_CMPF_OLT: return !un && a < b;
-    case TSB_CMPF_OLE: return !un && a <= b;
-    case TSB_CMPF_ONE: return !un && a != b;
-    case TSB_CMPF_ORD: return !un;
-    case TSB_CMPF_UEQ: return un || a == b;
-    case TSB_CMPF_UGT: return un || a > b;
-    case TSB_CMPF_UGE: return un || a >= b;
-    case TSB_CMPF_ULT: return un || a < b;
-    case TSB_CMPF_ULE: return un || a <= b;
-    case TSB_CMPF_UNE: return un || a != b;
-    case TSB_CMPF_UNO: return un;
-  }
-  return 0u;
-}
-__device__ __forceinline__ unsigned cmpi_(unsigned pred, unsigned ua, unsigned ub) {
-  int a = (int)ua, b = (int)ub;
-  switch (pred) {
-    case TSB_CMPI_EQ: return ua == ub;
-    case TSB_CMPI_NE: return ua != ub;
-    case TSB_CMPI_SLT: return a < b;
-    case TSB_CMPI_SLE: return a <= b;
-    case TSB_CMPI_SGT: return a > b;
-    case TSB_CMPI_SGE: return a >= b;
-    case TSB_CMPI_ULT: return ua < ub;
-    case TSB_CMPI_ULE: return ua <= ub;
-    case TSB_CMPI_UGT: return ua > ub;
-    case TSB_CMPI_UGE: return ua >= ub;
-  }
-  return 0u;
-}
-__device__ __forceinline__ bool is_float_dt(int dt) {
-  return dt == TSB_F32 || dt == TSB_F16 || dt == TSB_BF16;
-}
-__device__ __forceinline__ bool is_unsigned_dt(int dt) {
-  return dt == TSB_U32 || dt == TSB_U16 || dt == TSB_U8 || dt == TSB_I1;
-}
-// arith.extf/truncf/sitofp/uitofp/fptosi/fptoui/extsi/extui/trunci between
-// register representations.
-__device__ __forceinline__ unsigned cast_(unsigned v, int from, int to, unsigned mode) {
-  bool ff = is_float_dt(from), tf = is_float_dt(to);
-  if (ff && tf) return __float_as_uint(round_to(__uint_as_float(v), to));
-  if (!ff && tf) {
-    // mode 1: treat the source as unsigned (uitofp)
-    float f = (mode == 1u || is_unsigned_dt(from)) ? __uint2float_rn(v) : __int2float_rn((int)v);
-    return __float_as_uint(round_to(f, to));
-  }
-  if (ff && !tf) {
-    float f = __uint_as_float(v);
-    unsigned r = (mode == 1u || is_unsigned_dt(to)) ? __float2uint_rz(f) : (unsigned)__float2int_rz(f);
-    return wrap_to(r, to);
-  }
-  // int -> int: mode 1 = zero extension of the source width (extui)
-  if (mode == 1u) {
-    int fs = dtype_size(from);
-    if (fs == 1) v &= (from == TSB_I1 ? 1u : 0xffu);
-    else if (fs == 2) v &= 0xffffu;
-  }
-  return wrap_to(v, to);
-}
-
-struct ProgState {
-  long long off;
-  long long woff[2];
-  int dim[3];
-};
-
-// scale * ((offset + i*stride) mod modulus) summed over the access's wrap terms
-__device__ __forceinline__ long long wrap_addend(const DAcc &A, const ProgState &s, int i0, int i1, int i2) {
-  long long add = 0;
-  for (int w = 0; w < A.n_wrap; ++w) {
-    const int id = A.wrap[w].dim == 0 ? i0 : (A.wrap[w].dim == 1 ? i1 : i2);
-    add += A.wrap[w].scale * ((s.woff[w] + id * A.wrap[w].stride) % A.wrap[w].modulus);
-  }
-  return add;
-}
-
-__device__ __forceinline__ void program_state(const DAcc &A, const int size[3], long long px,
-                                              long long py, long long pz, ProgState &s) {
-  s.off = A.off0 + A.off_pid[0] * px + A.off_pid[1] * py + A.off_pid[2] * pz;
-  for (int w = 0; w < A.n_wrap; ++w)
-    s.woff[w] = A.wrap[w].off0 + A.wrap[w].off_pid[0] * px + A.wrap[w].off_pid[1] * py + A.wrap[w].off_pid[2] * pz;
-#pragma unroll
-  for (int d = 0; d < 3; ++d) {
-    int dim = size[d];
-    if (A.masked & (1 << d)) {
-      long long st = A.mstart0[d] + A.mstart_pid[d][0] * px + A.mstart_pid[d][1] * py +
-                     A.mstart_pid[d][2] * pz;
-      long long en = st + size[d];
-      long long m = en < A.bound[d] ? en : A.bound[d];
-      m = m > st ? m : st;
-      dim = (int)(m - st);
-    }
-    s.dim[d] = dim;
-  }
-}
-
-template <int VEC>
-__device__ __forceinline__ void load_vec(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
-                                         unsigned out[VEC]) {
-  const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
-  long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
-  const unsigned fill = A.has_other ? A.other : 0u;
-  if (A.n_wrap) {
-    if (A.wrap_inner) {
-      // lanes of the vector wrap independently: one scalar access per lane
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        const bool ok = outer && (i2 + k) < s.dim[2];
-        const long long ek = e + k * A.stride[2] + wrap_addend(A, s, i0, i1, i2 + k);
-        out[k] = A.kind == 2 ? (ok ? 1u : 0u)
-                             : (A.kind == 3 ? (unsigned)ek : (ok ? ld_elem(A.base + ek * A.esize, A.dtype) : fill));
-      }
-      return;
-    }
-    e += wrap_addend(A, s, i0, i1, i2);
-  }
-  if (A.kind >= 2) {
-    // probes read no memory: 2 yields the lane's mask bit, 3 its linear index
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      const bool ok = outer && (i2 + k) < s.dim[2];
-      out[k] = A.kind == 2 ? (ok ? 1u : 0u) : (unsigned)(e + k * A.stride[2]);
-    }
-    return;
-  }
-  if (VEC == 4 && A.vec_ok && outer && i2 + VEC <= s.dim[2]) {
-    const char *p = A.base + e * A.esize;
-    if (A.esize == 4) {
-      uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
-      out[0] = v.x; out[1 % VEC] = v.y; out[2 % VEC] = v.z; out[3 % VEC] = v.w;
-    } else if (A.esize == 2) {
-      uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
-      unsigned short h[4] = {(unsigned short)(v.x & 0xffff), (unsigned short)(v.x >> 16),
-                             (unsigned short)(v.y & 0xffff), (unsigned short)(v.y >> 16)};
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) out[k] = ld_elem(reinterpret_cast<const char *>(&h[k]), A.dtype);
-    } else {
-      unsigned v = __ldg(reinterpret_cast<const unsigned *>(p));
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        unsigned char b = (unsigned char)(v >> (8 * k));
-        out[k] = ld_elem(reinterpret_cast<const char *>(&b), A.dtype);
-      }
-    }
-    return;
-  }
-#pragma unroll
-  for (int k = 0; k < VEC; ++k) {
-    bool ok = outer && (i2 + k) < s.dim[2];
-    out[k] = ok ? ld_elem(A.base + (e + k * A.stride[2]) * A.esize, A.dtype) : fill;
-  }
-}
-
-template <int VEC>
-__device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
-                                          const unsigned in[VEC]) {
-  const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
-  if (!outer) return;
-  long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
-  if (A.n_wrap) {
-    if (A.wrap_inner) {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k)
-        if (i2 + k < s.dim[2])
-          st_elem(A.base + (e + k * A.stride[2] + wrap_addend(A, s, i0, i1, i2 + k)) * A.esize, A.dtype, in[k]);
-      return;
-    }
-    e += wrap_addend(A, s, i0, i1, i2);
-  }
-  if (VEC == 4 && A.vec_ok && i2 + VEC <= s.dim[2]) {
-    char *p = A.base + e * A.esize;
-    if (A.esize == 4) {
-      *reinterpret_cast<uint4 *>(p) = make_uint4(in[0], in[1 % VEC], in[2 % VEC], in[3 % VEC]);
-    } else if (A.esize == 2) {
-      unsigned short h[4];
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) st_elem(reinterpret_cast<char *>(&h[k]), A.dtype, in[k]);
-      *reinterpret_cast<uint2 *>(p) =
-          make_uint2((unsigned)h[0] | ((unsigned)h[1] << 16), (unsigned)h[2] | ((unsigned)h[3] << 16));
-    } else {
-      unsigned v = 0;
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        unsigned char b;
-        st_elem(reinterpret_cast<char *>(&b), A.dtype, in[k]);
-        v |= (unsigned)b << (8 * k);
-      }
-      *reinterpret_cast<unsigned *>(p) = v;
-    }
-    return;
-  }
-#pragma unroll
-  for (int k = 0; k < VEC; ++k)
-    if (i2 + k < s.dim[2]) st_elem(A.base + (e + k * A.stride[2]) * A.esize, A.dtype, in[k]);
-}
 
 // ---- general body: a small register VM ----------------------------------------
 // One pass over the op list for VEC lanes; `ld(access, regs)` and `st(access, regs)`
@@ -422,19 +87,6 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, LoadFn ld,
 }
 
 // Program id of a linearised program index (x fastest). 1-D grids skip the divisions.
-__device__ __forceinline__ void split_pid(const int grid[3], long long prog, long long &px, long long &py,
-                                          long long &pz) {
-  if (grid[1] == 1 && grid[2] == 1) {
-    px = prog; py = 0; pz = 0;
-    return;
-  }
-  const unsigned long long gx = (unsigned long long)grid[0], gy = (unsigned long long)grid[1];
-  const unsigned long long q = (unsigned long long)prog / gx;
-  px = (long long)((unsigned long long)prog - q * gx);
-  py = (long long)(q % gy);
-  pz = (long long)(q / gy);
-}
-
 template <int VEC>
 __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwParams P) {
   const int items = P.lanes / VEC;
@@ -681,30 +333,6 @@ __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__
   }
 }
 
-static unsigned other_to_reg(uint64_t bits, int dt) {
-  switch (dt) {
-    case TSB_F32: case TSB_I32: case TSB_U32: return (unsigned)bits;
-    case TSB_F16: {
-      __half_raw hr; hr.x = (unsigned short)bits;
-      float f = __half2float(__half(hr));
-      unsigned u; memcpy(&u, &f, 4); return u;
-    }
-    case TSB_BF16: return ((unsigned)(bits & 0xffffu)) << 16;
-    case TSB_I16: return (unsigned)(int)(short)bits;
-    case TSB_U16: return (unsigned)(bits & 0xffffu);
-    case TSB_I8: return (unsigned)(int)(signed char)bits;
-    case TSB_U8: return (unsigned)(bits & 0xffu);
-    case TSB_I1: return (unsigned)(bits & 1u);
-  }
-  return 0u;
-}
-
-static int ilog2_exact(long long v) {
-  int l = 0;
-  while ((1ll << l) < v) ++l;
-  return ((1ll << l) == v) ? l : -1;
-}
-
 static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
                         const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, EwParams &P,
                         int &vec) {
@@ -735,61 +363,8 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
   P.lanes = (int)lanes;
   vec = (sz[2] % 4 == 0) ? 4 : 1;
   for (int a = 0; a < n_acc; ++a) {
-    const tsb_access &s = acc[a];
-    DAcc &d = P.acc[a];
-    if (s.rank != rank) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has rank %d, expected %d", a, s.rank, rank);
-    const int es = dtype_size(s.dtype);
-    if (es == 0 || es == 8)
-      return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: access %d has unsupported dtype %d", a, s.dtype);
-    if (s.is_store < 0 || s.is_store > 3)
-      return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has kind %d", a, s.is_store);
-    if (!s.base && s.is_store < 2)
-      return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has a null base pointer", a);
-    d.kind = s.is_store;
-    d.base = (char *)s.base;
-    d.dtype = s.dtype;
-    d.esize = es;
-    d.off0 = s.offset0;
-    for (int k = 0; k < 3; ++k) d.off_pid[k] = s.offset_pid[k];
-    d.has_other = s.has_other;
-    d.other = other_to_reg(s.other_bits, s.dtype);
-    for (int k = 0; k < 3; ++k) { d.stride[k] = 0; d.bound[k] = 0; }
-    for (int k = 0; k < rank; ++k) {
-      const int o = 3 - rank + k;
-      if (s.sizes[k] != acc[0].sizes[k])
-        return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d block shape differs in dim %d", a, k);
-      d.stride[o] = s.strides[k];
-      if (s.masked[k]) {
-        d.masked |= 1 << o;
-        d.mstart0[o] = s.mask_start0[k];
-        for (int j = 0; j < 3; ++j) d.mstart_pid[o][j] = s.mask_start_pid[k][j];
-        d.bound[o] = s.mask_bound[k];
-      }
-    }
-    if (s.n_wrap < 0 || s.n_wrap > 2) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has %d wrap terms", a, s.n_wrap);
-    d.n_wrap = s.n_wrap;
-    d.wrap_inner = 0;
-    bool wrap_unaligned = false;
-    for (int w = 0; w < s.n_wrap; ++w) {
-      const tsb_wrap &sw = s.wrap[w];
-      if (sw.dim < 0 || sw.dim >= rank) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d wraps dim %d of rank %d", a, sw.dim, rank);
-      if (sw.modulus <= 0) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has wrap modulus %lld", a, (long long)sw.modulus);
-      d.wrap[w].dim = 3 - rank + sw.dim;
-      d.wrap[w].off0 = sw.offset0;
-      for (int j = 0; j < 3; ++j) d.wrap[w].off_pid[j] = sw.offset_pid[j];
-      d.wrap[w].stride = sw.stride;
-      d.wrap[w].modulus = sw.modulus;
-      d.wrap[w].scale = sw.scale;
-      if (d.wrap[w].dim == 2) d.wrap_inner = 1;
-      if (sw.scale % 4 != 0) wrap_unaligned = true;
-    }
-    // 4-lane vectors need: unit inner stride, vector-aligned base and offsets
-    const long long vb = 4ll * es;
-    bool ok = vec == 4 && d.stride[2] == 1 && ((uintptr_t)d.base % vb) == 0 && d.off0 % 4 == 0;
-    for (int k = 0; k < 3; ++k) ok = ok && (grid[k] <= 1 || d.off_pid[k] % 4 == 0);
-    ok = ok && (P.size[1] <= 1 || d.stride[1] % 4 == 0) && (P.size[0] <= 1 || d.stride[0] % 4 == 0);
-    ok = ok && !d.wrap_inner && !wrap_unaligned;
-    d.vec_ok = ok ? 1 : 0;
+    int rc = convert_access(acc, a, rank, P.size, grid, vec, P.acc[a]);
+    if (rc != TSB_OK) return rc;
   }
   for (int k = 0; k < n_ops; ++k) {
     const tsb_op &o = ops[k];
