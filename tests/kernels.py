@@ -304,3 +304,15 @@ def tile_max_kernel(x_ptr, rowmax_ptr, colmin_ptr, stride_m, M, N, BM: tl.conste
     x = tl.load(x_ptr + offs_m[:, None] * stride_m + offs_n[None, :], mask=mask, other=0)
     tl.store(rowmax_ptr + offs_m, tl.max(x, axis=1), mask=offs_m < M)
     tl.store(colmin_ptr + pid * BN + offs_n, tl.min(x, axis=0), mask=offs_n < N)
+
+
+@triton.jit
+def block_ptr_sum_kernel(x_ptr, out_ptr, stride, n_elements, BLOCK_SIZE: tl.constexpr):
+    """Block-pointer form of a per-program 1-D sum with a boundary check
+    (python/examples/test_reduce.py:9-30): Triton rewrites the block pointer into 64-bit offset
+    arithmetic with a `>= 0` and a `< bound` mask."""
+    pid = tl.program_id(0)
+    bp = tl.make_block_ptr(base=x_ptr, shape=[n_elements * tl.num_programs(0)], strides=[1],
+                           offsets=[stride * pid], block_shape=[BLOCK_SIZE], order=[0])
+    x = tl.load(bp, boundary_check=[0])
+    tl.store(out_ptr + pid, tl.sum(x, axis=0))

@@ -335,6 +335,11 @@ def _block_program_cases(dev):
     s = torch.zeros(9, device=dev)
     K.block_sum_kernel[(9,)](x, s, 300, 290, BLOCK_SIZE=512)
     out.append(("block_sum", s.cpu(), x[:, :290].sum(dim=1).cpu(), 1e-4))
+    # the reference's own block-pointer test: 32 programs of 16 elements (test_reduce.py:33-43, rtol 1e-3)
+    xb = torch.rand(32, 16, device=dev)
+    sb = torch.zeros(32, device=dev)
+    K.block_ptr_sum_kernel[(32,)](xb, sb, 16, 16, BLOCK_SIZE=16)
+    out.append(("block_ptr_sum", sb.cpu(), xb.sum(dim=1).cpu(), 1e-3))
     xh = torch.randn(5, 1000, device=dev).half()
     w = (torch.rand(1000, device=dev) + 0.5).half()
     y = torch.zeros_like(xh)
@@ -366,4 +371,4 @@ def test_block_programs_on_host_stand_in():
             assert torch.equal(got, exp), name
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
-    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 3
+    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 4

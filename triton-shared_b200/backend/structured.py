@@ -652,11 +652,9 @@ class Analyzer:
             if pred == "sgt" and a.uniform:  # bound > idx  ==  idx < bound
                 return self._cmpi("slt", b, a, ty)
             if pred == "sge" and b.uniform and b.offset.is_zero:
-                # idx >= 0: the lower bound is implicitly zero (MaskAnalysis.cpp:522-532);
-                # require the start to be provably non-negative at launch via a scalar condition
-                vd = a.varying_dims()
-                if len(vd) <= 1:
-                    return TMask(a.shape, tuple(() for _ in a.shape), (Poly.fn("cmp_sge", a.offset, Poly.const(0)),))
+                # idx >= 0: the reference assumes this comparison is true: dims already carry an implicit
+                # lower bound of zero (lib/Analysis/MaskAnalysis.cpp:522-532)
+                return TMask(a.shape, tuple(() for _ in a.shape))
         na, nb = self.as_data(a), self.as_data(b)
         return TData(self.node("cmpi", (na, nb), {"pred": pred}, ty.shape, "i1"))
 
