@@ -360,7 +360,9 @@ def main():
 
     # ------------------------------------------------------------------ secondary workloads
     names = {"vec_add", "layernorm", "strided_reduce", "matmul"}
-    chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names}
+    # kernels of the widened rows (general engines rather than dedicated kernels); not part of "all"
+    extra = {"gelu_bias", "rmsnorm", "wrap_rows"}
+    chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names | extra}
     if chosen:
         wl = {}
         steps2, warm2 = (3, 3) if args.small else (10, 3)
@@ -474,8 +476,41 @@ def main():
                 wl["matmul"]["result_check_rel_err"] = err
                 wl["matmul"]["roofline"]["frac_of_sustained"] = wl["matmul"]["roofline"]["achieved"] / peaks["tensor_sustained"]
 
+        def wl_gelu_bias():
+            # register-VM elementwise body (25 ops, fp16 I/O, broadcast bias), 16,384 x 8,192
+            R, C = (4096, 8192) if args.small else (16384, 8192)
+            x = torch.randn(R, C, device="cuda").half()
+            b = torch.randn(C, device="cuda").half()
+            o = torch.empty_like(x)
+
+            def step():
+                K.gelu_bias_kernel[(R, C // 1024)](x, b, o, C, BLOCK=1024)
+            record("gelu_bias", step, 4 * R * C + 2 * C, 1e9, "hbm", "GB/s")
+
+        def wl_rmsnorm():
+            # block-program kernel (reduction in the body, values in shared memory), fp16 16,384 x 4,096
+            R, C = (4096, 4096) if args.small else (16384, 4096)
+            x = torch.randn(R, C, device="cuda").half()
+            w = (torch.rand(C, device="cuda") + 0.5).half()
+            y = torch.empty_like(x)
+
+            def step():
+                K.rmsnorm_kernel[(R,)](x, w, y, C, C, 1e-6, BLOCK=4096)
+            record("rmsnorm", step, 4 * R * C + 2 * C, 1e9, "hbm", "GB/s")
+
+        def wl_wrap_rows():
+            # wrap-around row gather copy: 64 programs' worth in one program is tiny, so use many column steps
+            M, N = 4096, 16384
+            A = torch.randn(M, N, device="cuda")
+            Cc = torch.empty(64, N, device="cuda")
+
+            def step():
+                K.wrap_rows_kernel[(1,)](A, Cc, M, N, 1, N, 1, START=4090, BM=64, BN=64, STEPS=N // 64)
+            record("wrap_rows", step, 8 * 64 * N, 1e9, "hbm", "GB/s", launches=N // 64)
+
         for name, fn in (("vec_add", wl_vec_add), ("layernorm", wl_layernorm),
-                         ("strided_reduce", wl_strided_reduce), ("matmul", wl_matmul)):
+                         ("strided_reduce", wl_strided_reduce), ("matmul", wl_matmul),
+                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("wrap_rows", wl_wrap_rows)):
             if name in chosen:
                 fn()
                 torch.cuda.empty_cache()

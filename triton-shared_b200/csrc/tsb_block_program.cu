@@ -25,6 +25,7 @@ struct BpParams {
   tsb_op ops[TSB_MAX_OPS];
   int n_acc, n_ops, n_regs;
   int size[3];
+  int lg[3];  // log2 of size
   int grid[3];
   long long pid_lo, pid_hi;
   int reg_mask[BP_MAX_REGS];  // bit d set: the register extends along dim d
@@ -32,36 +33,57 @@ struct BpParams {
   int reg_n[BP_MAX_REGS];     // number of elements
 };
 
+// Block sizes are powers of two, so coordinates come from shifts and masks.
 // coordinates of element e of a register with mask m (row-major over its present dims)
-__device__ __forceinline__ void reg_coords(const int size[3], int m, int e, int &i0, int &i1, int &i2) {
-  const int s2 = (m & 4) ? size[2] : 1, s1 = (m & 2) ? size[1] : 1;
-  i2 = e % s2;
-  e /= s2;
-  i1 = e % s1;
-  i0 = e / s1;
+__device__ __forceinline__ void reg_coords(const int lg[3], int m, int e, int &i0, int &i1, int &i2) {
+  const int l2 = (m & 4) ? lg[2] : 0, l1 = (m & 2) ? lg[1] : 0;
+  i2 = e & ((1 << l2) - 1);
+  e >>= l2;
+  i1 = e & ((1 << l1) - 1);
+  i0 = e >> l1;
 }
 // element index of coordinates (i0,i1,i2) in a register with mask m (absent dims are broadcast)
-__device__ __forceinline__ int reg_index(const int size[3], int m, int i0, int i1, int i2) {
-  const int s2 = (m & 4) ? size[2] : 1, s1 = (m & 2) ? size[1] : 1;
-  return (((m & 1) ? i0 : 0) * s1 + ((m & 2) ? i1 : 0)) * s2 + ((m & 4) ? i2 : 0);
+__device__ __forceinline__ int reg_index(const int lg[3], int m, int i0, int i1, int i2) {
+  const int l2 = (m & 4) ? lg[2] : 0, l1 = (m & 2) ? lg[1] : 0;
+  return (((((m & 1) ? i0 : 0) << l1) + ((m & 2) ? i1 : 0)) << l2) + ((m & 4) ? i2 : 0);
 }
 
-__device__ __forceinline__ unsigned alu_scalar(const tsb_op &op, unsigned a, unsigned b, unsigned c) {
-  const int opc = op.opcode;
-  if (opc == TSB_OP_CONST) return op.imm;
-  if (opc == TSB_OP_MOV || opc == TSB_OP_BITCAST) return a;
-  if (opc >= TSB_OP_ADDF && opc < TSB_OP_EXP)
-    return __float_as_uint(round_to(binf(opc, __uint_as_float(a), __uint_as_float(b)), op.type));
-  if (opc >= TSB_OP_EXP && opc < TSB_OP_ADDI) return __float_as_uint(round_to(unf(opc, __uint_as_float(a)), op.type));
-  if (opc == TSB_OP_ABSI) return wrap_to((unsigned)abs((int)a), op.type);
-  if (opc >= TSB_OP_ADDI && opc < TSB_OP_CMPF) return wrap_to(bini(opc, a, b), op.type);
-  if (opc == TSB_OP_CMPF) return cmpf_(op.imm, __uint_as_float(a), __uint_as_float(b));
-  if (opc == TSB_OP_CMPI) return cmpi_(op.imm, a, b);
-  if (opc == TSB_OP_SELECT) return (a & 1u) ? b : c;
-  if (opc == TSB_OP_CAST) return cast_(a, (int)op.imm, op.type, op.imm2);
-  if (opc == TSB_OP_FMA)
-    return __float_as_uint(round_to(fmaf(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c)), op.type));
-  return 0u;
+// dst[e] = OPC(a, b, c) for this thread's elements; operands with the destination's mask are read
+// at the same index, scalars at 0, anything else through its coordinates
+template <int OPC>
+__device__ __forceinline__ void ew_loop(const tsb_op &op, const int lg[3], unsigned *dst, int n, int md,
+                                        const unsigned *ra, int ma, const unsigned *rb, int mb,
+                                        const unsigned *rc, int mc) {
+  constexpr int AR = alu_arity<OPC>();
+  const bool sa = ma == md || ma == 0, sb = AR < 2 || mb == md || mb == 0, sc = AR < 3 || mc == md || mc == 0;
+  if (sa && sb && sc && (n & 3) == 0) {
+    // four consecutive elements per thread and step: one 16-byte access per full-size operand,
+    // scalars (mask 0) read once
+    const uint4 *pa = reinterpret_cast<const uint4 *>(ra), *pb = reinterpret_cast<const uint4 *>(rb),
+                *pc = reinterpret_cast<const uint4 *>(rc);
+    const unsigned a0 = ra[0], b0 = AR >= 2 ? rb[0] : 0u, c0 = AR >= 3 ? rc[0] : 0u;
+    for (int e = threadIdx.x; e < (n >> 2); e += blockDim.x) {
+      const uint4 A = ma == md ? pa[e] : make_uint4(a0, a0, a0, a0);
+      const uint4 B = (AR >= 2 && mb == md) ? pb[e] : make_uint4(b0, b0, b0, b0);
+      const uint4 C = (AR >= 3 && mc == md) ? pc[e] : make_uint4(c0, c0, c0, c0);
+      uint4 r;
+      r.x = alu_op<OPC>(op, A.x, B.x, C.x);
+      r.y = alu_op<OPC>(op, A.y, B.y, C.y);
+      r.z = alu_op<OPC>(op, A.z, B.z, C.z);
+      r.w = alu_op<OPC>(op, A.w, B.w, C.w);
+      reinterpret_cast<uint4 *>(dst)[e] = r;
+    }
+  } else if (sa && sb && sc) {
+    const int ka = ma == md ? 1 : 0, kb = (AR >= 2 && mb == md) ? 1 : 0, kc = (AR >= 3 && mc == md) ? 1 : 0;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) dst[e] = alu_op<OPC>(op, ra[e * ka], rb[e * kb], rc[e * kc]);
+  } else {
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+      int i0, i1, i2;
+      reg_coords(lg, md, e, i0, i1, i2);
+      dst[e] = alu_op<OPC>(op, ra[reg_index(lg, ma, i0, i1, i2)], rb[reg_index(lg, mb, i0, i1, i2)],
+                           rc[reg_index(lg, mc, i0, i1, i2)]);
+    }
+  }
 }
 
 __device__ __forceinline__ unsigned combine(int comb, int type, unsigned a, unsigned b) {
@@ -87,7 +109,8 @@ __device__ __forceinline__ unsigned combine_identity(int comb) {
 }
 
 __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_constant__ BpParams P) {
-  extern __shared__ unsigned bp_smem[];
+  extern __shared__ __align__(16) unsigned bp_smem[];
+  __shared__ unsigned red[BP_THREADS / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
     long long px, py, pz;
@@ -103,7 +126,7 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         unsigned *dst = bp_smem + P.reg_off[op.dst];
         for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
           int i0, i1, i2;
-          reg_coords(P.size, m, e, i0, i1, i2);
+          reg_coords(P.lg, m, e, i0, i1, i2);
           unsigned v[1];
           load_vec<1>(A, st, i0, i1, i2, v);
           dst[e] = v[0];
@@ -118,8 +141,8 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         const int n = ((m & 1) ? P.size[0] : 1) * ((m & 2) ? P.size[1] : 1) * ((m & 4) ? P.size[2] : 1);
         for (int e = tid; e < n; e += BP_THREADS) {
           int i0, i1, i2;
-          reg_coords(P.size, m, e, i0, i1, i2);
-          unsigned v[1] = {src[reg_index(P.size, ms, i0, i1, i2)]};
+          reg_coords(P.lg, m, e, i0, i1, i2);
+          unsigned v[1] = {src[reg_index(P.lg, ms, i0, i1, i2)]};
           store_vec<1>(A, st, i0, i1, i2, v);
         }
       } else if (op.opcode == TSB_OP_REDUCE) {
@@ -129,28 +152,58 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         const unsigned *src = bp_smem + P.reg_off[op.a];
         unsigned *dst = bp_smem + P.reg_off[op.dst];
         const int len = P.size[d];
-        for (int o = warp; o < P.reg_n[op.dst]; o += BP_THREADS / 32) {
-          int c[3];
-          reg_coords(P.size, md, o, c[0], c[1], c[2]);
-          unsigned acc = combine_identity(comb);
-          for (int j = lane; j < len; j += 32) {
-            c[d] = j;
-            acc = combine(comb, op.type, src[reg_index(P.size, ms, c[0], c[1], c[2])], acc);
-          }
+        const int n_out = P.reg_n[op.dst];
+        if (n_out < BP_THREADS / 32) {
+          // few outputs (a 1-D block folded to a scalar): the whole CTA works on each of them
+          for (int o = 0; o < n_out; ++o) {
+            int c[3];
+            reg_coords(P.lg, md, o, c[0], c[1], c[2]);
+            unsigned acc = combine_identity(comb);
+            for (int j = tid; j < len; j += BP_THREADS) {
+              c[d] = j;
+              acc = combine(comb, op.type, src[reg_index(P.lg, ms, c[0], c[1], c[2])], acc);
+            }
 #pragma unroll
-          for (int s = 16; s > 0; s >>= 1) acc = combine(comb, op.type, __shfl_xor_sync(0xffffffffu, acc, s), acc);
-          if (lane == 0) dst[o] = acc;
+            for (int s = 16; s > 0; s >>= 1) acc = combine(comb, op.type, __shfl_xor_sync(0xffffffffu, acc, s), acc);
+            if (lane == 0) red[warp] = acc;
+            __syncthreads();
+            if (tid == 0) {
+              unsigned r = red[0];
+              for (int w = 1; w < BP_THREADS / 32; ++w) r = combine(comb, op.type, red[w], r);
+              dst[o] = r;
+            }
+            __syncthreads();
+          }
+        } else {
+          for (int o = warp; o < n_out; o += BP_THREADS / 32) {
+            int c[3];
+            reg_coords(P.lg, md, o, c[0], c[1], c[2]);
+            unsigned acc = combine_identity(comb);
+            for (int j = lane; j < len; j += 32) {
+              c[d] = j;
+              acc = combine(comb, op.type, src[reg_index(P.lg, ms, c[0], c[1], c[2])], acc);
+            }
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) acc = combine(comb, op.type, __shfl_xor_sync(0xffffffffu, acc, s), acc);
+            if (lane == 0) dst[o] = acc;
+          }
         }
       } else {
         const int md = P.reg_mask[op.dst];
         unsigned *dst = bp_smem + P.reg_off[op.dst];
         const int ma = P.reg_mask[op.a], mb = P.reg_mask[op.b], mc = P.reg_mask[op.c];
         const unsigned *ra = bp_smem + P.reg_off[op.a], *rb = bp_smem + P.reg_off[op.b], *rc = bp_smem + P.reg_off[op.c];
-        for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
-          int i0, i1, i2;
-          reg_coords(P.size, md, e, i0, i1, i2);
-          dst[e] = alu_scalar(op, ra[reg_index(P.size, ma, i0, i1, i2)], rb[reg_index(P.size, mb, i0, i1, i2)],
-                              rc[reg_index(P.size, mc, i0, i1, i2)]);
+        const int n = P.reg_n[op.dst];
+        if (op.opcode == TSB_OP_CONST) {
+          for (int e = tid; e < n; e += BP_THREADS) dst[e] = op.imm;
+        } else {
+          switch (op.opcode) {
+#define TSB_BP_CASE(O) \
+  case O: ew_loop<O>(op, P.lg, dst, n, md, ra, ma, rb, mb, rc, mc); break;
+            TSB_ALU_OPCODES(TSB_BP_CASE)
+#undef TSB_BP_CASE
+            default: break;
+          }
         }
       }
     }
@@ -182,6 +235,10 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
     if (acc[0].sizes[d] < 1 || acc[0].sizes[d] > (1 << 20)) return fail(TSB_ERR_INVALID, "tsb_block_program: bad block size");
     P.size[3 - rank + d] = (int)acc[0].sizes[d];
   }
+  for (int d = 0; d < 3; ++d) {
+    P.lg[d] = ilog2_exact(P.size[d]);
+    if (P.lg[d] < 0) return fail(TSB_ERR_INVALID, "tsb_block_program: block size %d is not a power of two", P.size[d]);
+  }
   for (int a = 0; a < n_acc; ++a) {
     int rc = convert_access(acc, a, rank, P.size, grid, 1, P.acc[a]);
     if (rc != TSB_OK) return rc;
@@ -198,7 +255,7 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
     P.reg_mask[r] = pm;
     P.reg_off[r] = (int)words;
     P.reg_n[r] = (int)n;
-    words += n;
+    words += (n + 3) & ~3ll;  // 16-byte aligned registers
   }
   const long long smem = words * 4;
   if (smem > 200 * 1024)

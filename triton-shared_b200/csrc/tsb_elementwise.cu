@@ -28,81 +28,97 @@ struct EwParams {
 // ---- general body: a small register VM ----------------------------------------
 // One pass over the op list for VEC lanes; `ld(access, regs)` and `st(access, regs)`
 // are supplied by the kernel (blocked or flat addressing).
+// The VM's registers live in shared memory: register r of thread t is the VEC consecutive
+// words starting at (r*blockDim + t)*VEC, so one 16-byte access per register and thread (VEC = 4)
+// and consecutive threads touch consecutive 16-byte slots (conflict-free).  A register file
+// indexed by run-time register numbers cannot live in hardware registers; kept as a per-thread
+// local array it overflowed L1.  The kernels are bound by instruction issue, so the opcode
+// switch is taken once per op and thread, with operand count known inside each case.
+template <int VEC>
+struct VmRegs {
+  unsigned *base;  // shared memory
+  int nt, t;
+  __device__ __forceinline__ void get(int reg, unsigned (&v)[VEC]) const {
+    const unsigned *p = base + ((size_t)reg * nt + t) * VEC;
+    if (VEC == 4) {
+      const uint4 q = *reinterpret_cast<const uint4 *>(p);
+      v[0] = q.x; v[1 % VEC] = q.y; v[2 % VEC] = q.z; v[3 % VEC] = q.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[k] = p[k];
+    }
+  }
+  __device__ __forceinline__ void put(int reg, const unsigned (&v)[VEC]) const {
+    unsigned *p = base + ((size_t)reg * nt + t) * VEC;
+    if (VEC == 4) {
+      *reinterpret_cast<uint4 *>(p) = make_uint4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) p[k] = v[k];
+    }
+  }
+};
+
+template <int OPC, int VEC>
+__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC> &R) {
+  unsigned a[VEC], b[VEC], c[VEC], r[VEC];
+  R.get(op.a, a);
+  if (alu_arity<OPC>() >= 2) R.get(op.b, b);
+  if (alu_arity<OPC>() >= 3) R.get(op.c, c);
+#pragma unroll
+  for (int v = 0; v < VEC; ++v)
+    r[v] = alu_op<OPC>(op, a[v], alu_arity<OPC>() >= 2 ? b[v] : 0u, alu_arity<OPC>() >= 3 ? c[v] : 0u);
+  R.put(op.dst, r);
+}
+
 template <int VEC, typename LoadFn, typename StoreFn>
-__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, LoadFn ld, StoreFn st) {
-  unsigned R[TSB_NUM_REGS][VEC];
+__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC> R, LoadFn ld, StoreFn st) {
   for (int k = 0; k < n_ops; ++k) {
     const tsb_op &op = ops[k];
-    const int opc = op.opcode;
-    if (opc == TSB_OP_LOAD) {
-      ld(op.a, R[op.dst]);
-    } else if (opc == TSB_OP_STORE) {
-      st(op.a, R[op.b]);
-    } else if (opc == TSB_OP_CONST) {
+    unsigned t[VEC];
+    switch (op.opcode) {
+      case TSB_OP_LOAD:
+        ld(op.a, t);
+        R.put(op.dst, t);
+        break;
+      case TSB_OP_STORE:
+        R.get(op.b, t);
+        st(op.a, t);
+        break;
+      case TSB_OP_CONST:
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = op.imm;
-    } else if (opc == TSB_OP_MOV) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = R[op.a][v];
-    } else if (opc >= TSB_OP_ADDF && opc < TSB_OP_EXP) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v)
-        R[op.dst][v] = __float_as_uint(round_to(
-            binf(opc, __uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v])), op.type));
-    } else if (opc >= TSB_OP_EXP && opc < TSB_OP_ADDI) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v)
-        R[op.dst][v] = __float_as_uint(round_to(unf(opc, __uint_as_float(R[op.a][v])), op.type));
-    } else if (opc == TSB_OP_ABSI) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = wrap_to((unsigned)abs((int)R[op.a][v]), op.type);
-    } else if (opc >= TSB_OP_ADDI && opc < TSB_OP_CMPF) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = wrap_to(bini(opc, R[op.a][v], R[op.b][v]), op.type);
-    } else if (opc == TSB_OP_CMPF) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v)
-        R[op.dst][v] = cmpf_(op.imm, __uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v]));
-    } else if (opc == TSB_OP_CMPI) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = cmpi_(op.imm, R[op.a][v], R[op.b][v]);
-    } else if (opc == TSB_OP_SELECT) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = (R[op.a][v] & 1u) ? R[op.b][v] : R[op.c][v];
-    } else if (opc == TSB_OP_CAST) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = cast_(R[op.a][v], (int)op.imm, op.type, op.imm2);
-    } else if (opc == TSB_OP_BITCAST) {
-      // only 32-bit <-> 32-bit bitcasts keep their bits in this representation
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) R[op.dst][v] = R[op.a][v];
-    } else if (opc == TSB_OP_FMA) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v)
-        R[op.dst][v] = __float_as_uint(round_to(
-            fmaf(__uint_as_float(R[op.a][v]), __uint_as_float(R[op.b][v]), __uint_as_float(R[op.c][v])),
-            op.type));
+        for (int v = 0; v < VEC; ++v) t[v] = op.imm;
+        R.put(op.dst, t);
+        break;
+#define TSB_VM_CASE(O) \
+  case O: vm_alu<O, VEC>(op, R); break;
+        TSB_ALU_OPCODES(TSB_VM_CASE)
+#undef TSB_VM_CASE
+      default: break;
     }
   }
 }
 
-// Program id of a linearised program index (x fastest). 1-D grids skip the divisions.
 template <int VEC>
 __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwParams P) {
+  extern __shared__ __align__(16) unsigned vm_smem[];
+  __shared__ ProgState st[TSB_MAX_ACCESSES];
+  const VmRegs<VEC> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
   const int items = P.lanes / VEC;
   const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
     long long px, py, pz;
     split_pid(P.grid, prog, px, py, pz);
-    ProgState st[TSB_MAX_ACCESSES];
-    for (int a = 0; a < P.n_acc; ++a) program_state(P.acc[a], P.size, px, py, pz, st[a]);
+    __syncthreads();  // the previous program's state is no longer read
+    if (threadIdx.x < P.n_acc) program_state(P.acc[threadIdx.x], P.size, px, py, pz, st[threadIdx.x]);
+    __syncthreads();
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
       const int l = it * VEC;
       const int i2 = l & (P.size[2] - 1);
       const int i1 = (l >> sh1) & (P.size[1] - 1);
       const int i0 = l >> sh0;
       vm_exec<VEC>(
-          P.ops, P.n_ops,
+          P.ops, P.n_ops, R,
           [&](int a, unsigned(&r)[VEC]) { load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r); },
           [&](int a, const unsigned(&r)[VEC]) { store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r); });
     }
@@ -323,12 +339,14 @@ __global__ void __launch_bounds__(256) ew_flat_binary_f32_kernel(const __grid_co
 }
 
 __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__ FlatParams P) {
+  extern __shared__ __align__(16) unsigned vm_smem[];
+  const VmRegs<4> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
   const long long n_vec = (P.g_hi - P.g_lo) >> 2;
   const long long step = (long long)gridDim.x * blockDim.x;
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += step) {
     const long long g = P.g_lo + v * 4;
     vm_exec<4>(
-        P.ops, P.n_ops, [&](int a, unsigned(&r)[4]) { flat_load(P.acc[a], g, r); },
+        P.ops, P.n_ops, R, [&](int a, unsigned(&r)[4]) { flat_load(P.acc[a], g, r); },
         [&](int a, const unsigned(&r)[4]) { flat_store(P.acc[a], g, r); });
   }
 }
@@ -418,6 +436,17 @@ static bool build_flat(const EwParams &P, int vec, FlatParams &F) {
   return true;
 }
 
+// Registers the body touches (highest register number + 1): sizes the VM's shared-memory file.
+static int vm_regs_used(const tsb_op *ops, int n_ops) {
+  int hi = 0;
+  for (int k = 0; k < n_ops; ++k) {
+    const tsb_op &o = ops[k];
+    if (o.opcode != TSB_OP_STORE && o.dst > hi) hi = o.dst;
+    if (o.opcode == TSB_OP_STORE && o.b > hi) hi = o.b;
+  }
+  return hi + 1;
+}
+
 static bool is_fast_binary(const tsb_access *acc, const tsb_op *ops, int n_ops) {
   if (n_ops != 4) return false;
   if (ops[0].opcode != TSB_OP_LOAD || ops[1].opcode != TSB_OP_LOAD || ops[3].opcode != TSB_OP_STORE)
@@ -454,8 +483,17 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     long long ctas = (n_vec + per_cta - 1) / per_cta;
     const long long cap = (long long)sm_count() * 8 * 4;
     if (ctas > cap) ctas = cap;
-    if (fast) ew_flat_binary_f32_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
-    else ew_flat_vm_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
+    if (fast) {
+      ew_flat_binary_f32_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
+    } else {
+      const size_t smem = (size_t)vm_regs_used(ops, n_ops) * 4 * 256 * sizeof(unsigned);
+      static size_t set_flat = 0;
+      if (smem > 48 * 1024 && set_flat < smem) {
+        TSB_CUDA_OK(cudaFuncSetAttribute(ew_flat_vm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        set_flat = 64 * 1024;
+      }
+      ew_flat_vm_kernel<<<(unsigned)ctas, 256, smem, s>>>(F);
+    }
     TSB_LAUNCH_OK("ew_flat_kernel");
     return TSB_OK;
   }
@@ -468,8 +506,14 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     return TSB_OK;
   }
   long long ctas = n_prog < max_ctas ? n_prog : max_ctas;
-  if (vec == 4) ew_vm_kernel<4><<<(unsigned)ctas, threads, 0, s>>>(P);
-  else ew_vm_kernel<1><<<(unsigned)ctas, threads, 0, s>>>(P);
+  const size_t smem = (size_t)vm_regs_used(ops, n_ops) * vec * threads * sizeof(unsigned);
+  static size_t set_vm = 0;
+  if (smem > 48 * 1024 && set_vm < smem) {
+    TSB_CUDA_OK(cudaFuncSetAttribute(ew_vm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    set_vm = 64 * 1024;
+  }
+  if (vec == 4) ew_vm_kernel<4><<<(unsigned)ctas, threads, smem, s>>>(P);
+  else ew_vm_kernel<1><<<(unsigned)ctas, threads, smem, s>>>(P);
   TSB_LAUNCH_OK("ew_vm_kernel");
   return TSB_OK;
 }

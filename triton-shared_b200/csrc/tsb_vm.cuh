@@ -343,6 +343,48 @@ __device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int
 }
 
 
+// One ALU op on one lane with the opcode known at compile time: the per-op switch is taken
+// once per thread (see TSB_ALU_OPCODES), not once per lane.
+template <int OPC>
+__device__ __forceinline__ unsigned alu_op(const tsb_op &op, unsigned a, unsigned b, unsigned c) {
+  if constexpr (OPC == TSB_OP_MOV || OPC == TSB_OP_BITCAST) return a;  // 32-bit <-> 32-bit bitcasts keep their bits
+  else if constexpr (OPC >= TSB_OP_ADDF && OPC < TSB_OP_EXP)
+    return __float_as_uint(round_to(binf(OPC, __uint_as_float(a), __uint_as_float(b)), op.type));
+  else if constexpr (OPC >= TSB_OP_EXP && OPC < TSB_OP_ADDI)
+    return __float_as_uint(round_to(unf(OPC, __uint_as_float(a)), op.type));
+  else if constexpr (OPC == TSB_OP_ABSI) return wrap_to((unsigned)abs((int)a), op.type);
+  else if constexpr (OPC >= TSB_OP_ADDI && OPC < TSB_OP_CMPF) return wrap_to(bini(OPC, a, b), op.type);
+  else if constexpr (OPC == TSB_OP_CMPF) return cmpf_(op.imm, __uint_as_float(a), __uint_as_float(b));
+  else if constexpr (OPC == TSB_OP_CMPI) return cmpi_(op.imm, a, b);
+  else if constexpr (OPC == TSB_OP_SELECT) return (a & 1u) ? b : c;
+  else if constexpr (OPC == TSB_OP_CAST) return cast_(a, (int)op.imm, op.type, op.imm2);
+  else if constexpr (OPC == TSB_OP_FMA)
+    return __float_as_uint(round_to(fmaf(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c)), op.type));
+  else return 0u;
+}
+
+// Operands an ALU opcode reads (1, 2 or 3), known at compile time.
+template <int OPC>
+__device__ __forceinline__ constexpr int alu_arity() {
+  if (OPC == TSB_OP_SELECT || OPC == TSB_OP_FMA) return 3;
+  if ((OPC >= TSB_OP_EXP && OPC < TSB_OP_ADDI) || OPC == TSB_OP_ABSI || OPC == TSB_OP_CAST ||
+      OPC == TSB_OP_BITCAST || OPC == TSB_OP_MOV)
+    return 1;
+  return 2;
+}
+
+// X(opcode) for every ALU opcode
+#define TSB_ALU_OPCODES(X)                                                                          \
+  X(TSB_OP_MOV) X(TSB_OP_BITCAST) X(TSB_OP_ADDF) X(TSB_OP_SUBF) X(TSB_OP_MULF) X(TSB_OP_DIVF)        \
+  X(TSB_OP_MAXNUMF) X(TSB_OP_MINNUMF) X(TSB_OP_MAXIMUMF) X(TSB_OP_MINIMUMF) X(TSB_OP_REMF)          \
+  X(TSB_OP_EXP) X(TSB_OP_EXP2) X(TSB_OP_LOG) X(TSB_OP_LOG2) X(TSB_OP_SQRT) X(TSB_OP_RSQRT)          \
+  X(TSB_OP_SIN) X(TSB_OP_COS) X(TSB_OP_TANH) X(TSB_OP_ERF) X(TSB_OP_ABSF) X(TSB_OP_NEGF)            \
+  X(TSB_OP_FLOOR) X(TSB_OP_CEIL) X(TSB_OP_ADDI) X(TSB_OP_SUBI) X(TSB_OP_MULI) X(TSB_OP_DIVSI)       \
+  X(TSB_OP_REMSI) X(TSB_OP_DIVUI) X(TSB_OP_REMUI) X(TSB_OP_MINSI) X(TSB_OP_MAXSI) X(TSB_OP_MINUI)   \
+  X(TSB_OP_MAXUI) X(TSB_OP_ANDI) X(TSB_OP_ORI) X(TSB_OP_XORI) X(TSB_OP_SHLI) X(TSB_OP_SHRSI)        \
+  X(TSB_OP_SHRUI) X(TSB_OP_ABSI) X(TSB_OP_CMPF) X(TSB_OP_CMPI) X(TSB_OP_SELECT) X(TSB_OP_CAST)      \
+  X(TSB_OP_FMA)
+
 __device__ __forceinline__ void split_pid(const int grid[3], long long prog, long long &px, long long &py,
                                           long long &pz) {
   if (grid[1] == 1 && grid[2] == 1) {
