@@ -124,12 +124,34 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         program_state(A, P.size, px, py, pz, st);
         const int m = P.reg_mask[op.dst];
         unsigned *dst = bp_smem + P.reg_off[op.dst];
-        for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
-          int i0, i1, i2;
-          reg_coords(P.lg, m, e, i0, i1, i2);
-          unsigned v[1];
-          load_vec<1>(A, st, i0, i1, i2, v);
-          dst[e] = v[0];
+        if ((m & 4) && (P.size[2] & 3) == 0) {
+          // 4-lane vectors along the innermost dim, four independent loads in flight per thread
+          const int n4 = P.reg_n[op.dst] >> 2;
+          for (int e0 = tid; e0 < n4; e0 += BP_THREADS * 4) {
+            unsigned v[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int e4 = e0 + u * BP_THREADS;
+              if (e4 < n4) {
+                int i0, i1, i2;
+                reg_coords(P.lg, m, e4 * 4, i0, i1, i2);
+                load_vec<4>(A, st, i0, i1, i2, v[u]);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int e4 = e0 + u * BP_THREADS;
+              if (e4 < n4) reinterpret_cast<uint4 *>(dst)[e4] = make_uint4(v[u][0], v[u][1], v[u][2], v[u][3]);
+            }
+          }
+        } else {
+          for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
+            int i0, i1, i2;
+            reg_coords(P.lg, m, e, i0, i1, i2);
+            unsigned v[1];
+            load_vec<1>(A, st, i0, i1, i2, v);
+            dst[e] = v[0];
+          }
         }
       } else if (op.opcode == TSB_OP_STORE) {
         const DAcc &A = P.acc[op.a];
@@ -139,11 +161,21 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         const int ms = P.reg_mask[op.b];
         const unsigned *src = bp_smem + P.reg_off[op.b];
         const int n = ((m & 1) ? P.size[0] : 1) * ((m & 2) ? P.size[1] : 1) * ((m & 4) ? P.size[2] : 1);
-        for (int e = tid; e < n; e += BP_THREADS) {
-          int i0, i1, i2;
-          reg_coords(P.lg, m, e, i0, i1, i2);
-          unsigned v[1] = {src[reg_index(P.lg, ms, i0, i1, i2)]};
-          store_vec<1>(A, st, i0, i1, i2, v);
+        if ((m & 4) && ms == m && (P.size[2] & 3) == 0) {
+          for (int e4 = tid; e4 < (n >> 2); e4 += BP_THREADS) {
+            int i0, i1, i2;
+            reg_coords(P.lg, m, e4 * 4, i0, i1, i2);
+            const uint4 q = reinterpret_cast<const uint4 *>(src)[e4];
+            const unsigned v[4] = {q.x, q.y, q.z, q.w};
+            store_vec<4>(A, st, i0, i1, i2, v);
+          }
+        } else {
+          for (int e = tid; e < n; e += BP_THREADS) {
+            int i0, i1, i2;
+            reg_coords(P.lg, m, e, i0, i1, i2);
+            unsigned v[1] = {src[reg_index(P.lg, ms, i0, i1, i2)]};
+            store_vec<1>(A, st, i0, i1, i2, v);
+          }
         }
       } else if (op.opcode == TSB_OP_REDUCE) {
         // dst = fold of src along dim imm2 with combiner imm; one warp per output element
@@ -240,7 +272,7 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
     if (P.lg[d] < 0) return fail(TSB_ERR_INVALID, "tsb_block_program: block size %d is not a power of two", P.size[d]);
   }
   for (int a = 0; a < n_acc; ++a) {
-    int rc = convert_access(acc, a, rank, P.size, grid, 1, P.acc[a]);
+    int rc = convert_access(acc, a, rank, P.size, grid, (P.size[2] % 4 == 0) ? 4 : 1, P.acc[a]);
     if (rc != TSB_OK) return rc;
   }
   long long words = 0;

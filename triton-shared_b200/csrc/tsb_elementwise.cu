@@ -34,12 +34,17 @@ struct EwParams {
 // indexed by run-time register numbers cannot live in hardware registers; kept as a per-thread
 // local array it overflowed L1.  The kernels are bound by instruction issue, so the opcode
 // switch is taken once per op and thread, with operand count known inside each case.
-template <int VEC>
+// Each thread carries U independent lane-vectors ("sub-items") through the op list, so the cost
+// of decoding an op is shared by U*VEC lanes and U loads per access are in flight per thread.
+template <int VEC, int U>
 struct VmRegs {
   unsigned *base;  // shared memory
   int nt, t;
-  __device__ __forceinline__ void get(int reg, unsigned (&v)[VEC]) const {
-    const unsigned *p = base + ((size_t)reg * nt + t) * VEC;
+  __device__ __forceinline__ unsigned *slot(int reg, int u) const {
+    return base + (((size_t)reg * U + u) * nt + t) * VEC;
+  }
+  __device__ __forceinline__ void get(int reg, int u, unsigned (&v)[VEC]) const {
+    const unsigned *p = slot(reg, u);
     if (VEC == 4) {
       const uint4 q = *reinterpret_cast<const uint4 *>(p);
       v[0] = q.x; v[1 % VEC] = q.y; v[2 % VEC] = q.z; v[3 % VEC] = q.w;
@@ -48,8 +53,8 @@ struct VmRegs {
       for (int k = 0; k < VEC; ++k) v[k] = p[k];
     }
   }
-  __device__ __forceinline__ void put(int reg, const unsigned (&v)[VEC]) const {
-    unsigned *p = base + ((size_t)reg * nt + t) * VEC;
+  __device__ __forceinline__ void put(int reg, int u, const unsigned (&v)[VEC]) const {
+    unsigned *p = slot(reg, u);
     if (VEC == 4) {
       *reinterpret_cast<uint4 *>(p) = make_uint4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
     } else {
@@ -59,39 +64,54 @@ struct VmRegs {
   }
 };
 
-template <int OPC, int VEC>
-__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC> &R) {
-  unsigned a[VEC], b[VEC], c[VEC], r[VEC];
-  R.get(op.a, a);
-  if (alu_arity<OPC>() >= 2) R.get(op.b, b);
-  if (alu_arity<OPC>() >= 3) R.get(op.c, c);
+template <int OPC, int VEC, int U>
+__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R) {
 #pragma unroll
-  for (int v = 0; v < VEC; ++v)
-    r[v] = alu_op<OPC>(op, a[v], alu_arity<OPC>() >= 2 ? b[v] : 0u, alu_arity<OPC>() >= 3 ? c[v] : 0u);
-  R.put(op.dst, r);
+  for (int u = 0; u < U; ++u) {
+    unsigned a[VEC], b[VEC], c[VEC], r[VEC];
+    R.get(op.a, u, a);
+    if (alu_arity<OPC>() >= 2) R.get(op.b, u, b);
+    if (alu_arity<OPC>() >= 3) R.get(op.c, u, c);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+      r[v] = alu_op<OPC>(op, a[v], alu_arity<OPC>() >= 2 ? b[v] : 0u, alu_arity<OPC>() >= 3 ? c[v] : 0u);
+    R.put(op.dst, u, r);
+  }
 }
 
-template <int VEC, typename LoadFn, typename StoreFn>
-__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC> R, LoadFn ld, StoreFn st) {
+// ld(access, u, regs) / st(access, u, regs) address sub-item u; inactive sub-items load zeros and store nothing
+template <int VEC, int U, typename LoadFn, typename StoreFn>
+__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC, U> R, LoadFn ld, StoreFn st) {
   for (int k = 0; k < n_ops; ++k) {
     const tsb_op &op = ops[k];
-    unsigned t[VEC];
     switch (op.opcode) {
-      case TSB_OP_LOAD:
-        ld(op.a, t);
-        R.put(op.dst, t);
+      case TSB_OP_LOAD: {
+        unsigned t[U][VEC];
+#pragma unroll
+        for (int u = 0; u < U; ++u) ld(op.a, u, t[u]);  // all loads issued before the first use
+#pragma unroll
+        for (int u = 0; u < U; ++u) R.put(op.dst, u, t[u]);
         break;
+      }
       case TSB_OP_STORE:
-        R.get(op.b, t);
-        st(op.a, t);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          unsigned t[VEC];
+          R.get(op.b, u, t);
+          st(op.a, u, t);
+        }
         break;
       case TSB_OP_CONST:
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) t[v] = op.imm;
-        R.put(op.dst, t);
+        for (int u = 0; u < U; ++u) {
+          unsigned t[VEC];
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) t[v] = op.imm;
+          R.put(op.dst, u, t);
+        }
         break;
 #define TSB_VM_CASE(O) \
-  case O: vm_alu<O, VEC>(op, R); break;
+  case O: vm_alu<O, VEC, U>(op, R); break;
         TSB_ALU_OPCODES(TSB_VM_CASE)
 #undef TSB_VM_CASE
       default: break;
@@ -99,11 +119,11 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRe
   }
 }
 
-template <int VEC>
+template <int VEC, int U>
 __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwParams P) {
   extern __shared__ __align__(16) unsigned vm_smem[];
   __shared__ ProgState st[TSB_MAX_ACCESSES];
-  const VmRegs<VEC> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
+  const VmRegs<VEC, U> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
   const int items = P.lanes / VEC;
   const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
@@ -112,15 +132,30 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
     __syncthreads();  // the previous program's state is no longer read
     if (threadIdx.x < P.n_acc) program_state(P.acc[threadIdx.x], P.size, px, py, pz, st[threadIdx.x]);
     __syncthreads();
-    for (int it = threadIdx.x; it < items; it += blockDim.x) {
-      const int l = it * VEC;
-      const int i2 = l & (P.size[2] - 1);
-      const int i1 = (l >> sh1) & (P.size[1] - 1);
-      const int i0 = l >> sh0;
-      vm_exec<VEC>(
+    for (int it0 = threadIdx.x; it0 < items; it0 += blockDim.x * U) {
+      auto coords = [&](int u, int &i0, int &i1, int &i2) {
+        const int it = it0 + u * (int)blockDim.x;
+        const int l = it * VEC;
+        i2 = l & (P.size[2] - 1);
+        i1 = (l >> sh1) & (P.size[1] - 1);
+        i0 = l >> sh0;
+        return it < items;
+      };
+      vm_exec<VEC, U>(
           P.ops, P.n_ops, R,
-          [&](int a, unsigned(&r)[VEC]) { load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r); },
-          [&](int a, const unsigned(&r)[VEC]) { store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r); });
+          [&](int a, int u, unsigned(&r)[VEC]) {
+            int i0, i1, i2;
+            if (coords(u, i0, i1, i2)) {
+              load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
+            } else {
+#pragma unroll
+              for (int v = 0; v < VEC; ++v) r[v] = 0u;
+            }
+          },
+          [&](int a, int u, const unsigned(&r)[VEC]) {
+            int i0, i1, i2;
+            if (coords(u, i0, i1, i2)) store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
+          });
     }
   }
 }
@@ -209,17 +244,13 @@ __device__ __forceinline__ void flat_load(const FlatAcc &A, long long g, unsigne
       out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
     } else if (A.esize == 2) {
       const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(p));
-      unsigned short h[4] = {(unsigned short)(v.x & 0xffff), (unsigned short)(v.x >> 16),
-                             (unsigned short)(v.y & 0xffff), (unsigned short)(v.y >> 16)};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) out[k] = ld_elem(reinterpret_cast<const char *>(&h[k]), A.dtype);
+      out[0] = v.x & 0xffffu; out[1] = v.x >> 16; out[2] = v.y & 0xffffu; out[3] = v.y >> 16;
+      raw_to_reg<4>(A.dtype, out);
     } else {
       const unsigned v = __ldcs(reinterpret_cast<const unsigned *>(p));
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        unsigned char b = (unsigned char)(v >> (8 * k));
-        out[k] = ld_elem(reinterpret_cast<const char *>(&b), A.dtype);
-      }
+      for (int k = 0; k < 4; ++k) out[k] = (v >> (8 * k)) & 0xffu;
+      raw_to_reg<4>(A.dtype, out);
     }
     return;
   }
@@ -234,20 +265,13 @@ __device__ __forceinline__ void flat_store(const FlatAcc &A, long long g, const 
     if (A.esize == 4) {
       __stcs(reinterpret_cast<uint4 *>(p), make_uint4(in[0], in[1], in[2], in[3]));
     } else if (A.esize == 2) {
-      unsigned short h[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) st_elem(reinterpret_cast<char *>(&h[k]), A.dtype, in[k]);
-      __stcs(reinterpret_cast<uint2 *>(p),
-             make_uint2((unsigned)h[0] | ((unsigned)h[1] << 16), (unsigned)h[2] | ((unsigned)h[3] << 16)));
+      unsigned h[4] = {in[0], in[1], in[2], in[3]};
+      reg_to_raw<4>(A.dtype, h);
+      __stcs(reinterpret_cast<uint2 *>(p), make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16)));
     } else {
-      unsigned v = 0;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        unsigned char b;
-        st_elem(reinterpret_cast<char *>(&b), A.dtype, in[k]);
-        v |= (unsigned)b << (8 * k);
-      }
-      __stcs(reinterpret_cast<unsigned *>(p), v);
+      unsigned h[4] = {in[0], in[1], in[2], in[3]};
+      reg_to_raw<4>(A.dtype, h);
+      __stcs(reinterpret_cast<unsigned *>(p), h[0] | (h[1] << 8) | (h[2] << 16) | (h[3] << 24));
     }
     return;
   }
@@ -338,18 +362,31 @@ __global__ void __launch_bounds__(256) ew_flat_binary_f32_kernel(const __grid_co
   }
 }
 
+constexpr int FLAT_VM_U = 4;
+
 __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__ FlatParams P) {
   extern __shared__ __align__(16) unsigned vm_smem[];
-  const VmRegs<4> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
+  const VmRegs<4, FLAT_VM_U> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
   const long long n_vec = (P.g_hi - P.g_lo) >> 2;
-  const long long step = (long long)gridDim.x * blockDim.x;
-  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += step) {
-    const long long g = P.g_lo + v * 4;
-    vm_exec<4>(
-        P.ops, P.n_ops, R, [&](int a, unsigned(&r)[4]) { flat_load(P.acc[a], g, r); },
-        [&](int a, const unsigned(&r)[4]) { flat_store(P.acc[a], g, r); });
+  const long long step = (long long)gridDim.x * blockDim.x * FLAT_VM_U;
+  for (long long v0 = (long long)blockIdx.x * blockDim.x * FLAT_VM_U + threadIdx.x; v0 < n_vec; v0 += step) {
+    vm_exec<4, FLAT_VM_U>(
+        P.ops, P.n_ops, R,
+        [&](int a, int u, unsigned(&r)[4]) {
+          const long long v = v0 + (long long)u * blockDim.x;
+          if (v < n_vec) {
+            flat_load(P.acc[a], P.g_lo + v * 4, r);
+          } else {
+            r[0] = r[1] = r[2] = r[3] = 0u;
+          }
+        },
+        [&](int a, int u, const unsigned(&r)[4]) {
+          const long long v = v0 + (long long)u * blockDim.x;
+          if (v < n_vec) flat_store(P.acc[a], P.g_lo + v * 4, r);
+        });
   }
 }
+
 
 static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
                         const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, EwParams &P,
@@ -479,20 +516,24 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
   if (build_flat(P, vec, F)) {
     const long long n_vec = (F.g_hi - F.g_lo) / 4;
     const bool fast = is_fast_binary(acc, ops, n_ops);
-    const long long per_cta = 256ll * (fast ? FLAT_UNROLL : 1);
+    // the VM's register file lives in shared memory: fewer threads per CTA when the body uses many registers
+    int flat_threads = 256;
+    const size_t regs_bytes = (size_t)vm_regs_used(ops, n_ops) * FLAT_VM_U * 4 * sizeof(unsigned);
+    while (!fast && regs_bytes * flat_threads > 96 * 1024 && flat_threads > 32) flat_threads /= 2;
+    const long long per_cta = fast ? 256ll * FLAT_UNROLL : (long long)flat_threads * FLAT_VM_U;
     long long ctas = (n_vec + per_cta - 1) / per_cta;
     const long long cap = (long long)sm_count() * 8 * 4;
     if (ctas > cap) ctas = cap;
     if (fast) {
       ew_flat_binary_f32_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
     } else {
-      const size_t smem = (size_t)vm_regs_used(ops, n_ops) * 4 * 256 * sizeof(unsigned);
+      const size_t smem = regs_bytes * flat_threads;
       static size_t set_flat = 0;
       if (smem > 48 * 1024 && set_flat < smem) {
-        TSB_CUDA_OK(cudaFuncSetAttribute(ew_flat_vm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        set_flat = 64 * 1024;
+        TSB_CUDA_OK(cudaFuncSetAttribute(ew_flat_vm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        set_flat = 200 * 1024;
       }
-      ew_flat_vm_kernel<<<(unsigned)ctas, 256, smem, s>>>(F);
+      ew_flat_vm_kernel<<<(unsigned)ctas, flat_threads, smem, s>>>(F);
     }
     TSB_LAUNCH_OK("ew_flat_kernel");
     return TSB_OK;
@@ -505,15 +546,23 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     TSB_LAUNCH_OK("ew_binary_f32_kernel");
     return TSB_OK;
   }
+  // four lane-vectors per thread when the block is large enough to keep at least a warp busy
+  const int U = (vec == 4 && items >= 128) ? 4 : 1;
+  if (U == 4) {
+    threads = items / 4 >= 256 ? 256 : (items / 4 >= 128 ? 128 : (items / 4 >= 64 ? 64 : 32));
+  }
+  while ((size_t)vm_regs_used(ops, n_ops) * U * vec * threads * sizeof(unsigned) > 96 * 1024 && threads > 32) threads /= 2;
   long long ctas = n_prog < max_ctas ? n_prog : max_ctas;
-  const size_t smem = (size_t)vm_regs_used(ops, n_ops) * vec * threads * sizeof(unsigned);
+  const size_t smem = (size_t)vm_regs_used(ops, n_ops) * U * vec * threads * sizeof(unsigned);
   static size_t set_vm = 0;
   if (smem > 48 * 1024 && set_vm < smem) {
-    TSB_CUDA_OK(cudaFuncSetAttribute(ew_vm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-    set_vm = 64 * 1024;
+    TSB_CUDA_OK(cudaFuncSetAttribute(ew_vm_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    TSB_CUDA_OK(cudaFuncSetAttribute(ew_vm_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    set_vm = 200 * 1024;
   }
-  if (vec == 4) ew_vm_kernel<4><<<(unsigned)ctas, threads, smem, s>>>(P);
-  else ew_vm_kernel<1><<<(unsigned)ctas, threads, smem, s>>>(P);
+  if (U == 4) ew_vm_kernel<4, 4><<<(unsigned)ctas, threads, smem, s>>>(P);
+  else if (vec == 4) ew_vm_kernel<4, 1><<<(unsigned)ctas, threads, smem, s>>>(P);
+  else ew_vm_kernel<1, 1><<<(unsigned)ctas, threads, smem, s>>>(P);
   TSB_LAUNCH_OK("ew_vm_kernel");
   return TSB_OK;
 }

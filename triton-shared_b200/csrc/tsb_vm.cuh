@@ -36,27 +36,75 @@ struct DAcc {
 // Every VM lane is 32 bits: f32 bits for all float types (f16/bf16 values are
 // held exactly widened and re-rounded after each op), sign/zero-extended ints.
 
-__device__ __forceinline__ unsigned ld_elem(const char *p, int dt) {
+// raw element bits (zero-extended) <-> register representation, for VEC lanes with ONE switch on
+// the element type (the conversions stay in registers; nothing is punned through memory)
+template <int VEC>
+__device__ __forceinline__ void raw_to_reg(int dt, unsigned (&x)[VEC]) {
   switch (dt) {
-    case TSB_F32: case TSB_I32: case TSB_U32: return *reinterpret_cast<const unsigned *>(p);
-    case TSB_F16: return __float_as_uint(__half2float(*reinterpret_cast<const __half *>(p)));
-    case TSB_BF16: return __float_as_uint(__bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p)));
-    case TSB_I16: return (unsigned)(int)*reinterpret_cast<const short *>(p);
-    case TSB_U16: return (unsigned)*reinterpret_cast<const unsigned short *>(p);
-    case TSB_I8: return (unsigned)(int)*reinterpret_cast<const signed char *>(p);
-    case TSB_U8: case TSB_I1: return (unsigned)*reinterpret_cast<const unsigned char *>(p);
+    case TSB_F16:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] = __float_as_uint(__half2float(__ushort_as_half((unsigned short)x[k])));
+      break;
+    case TSB_BF16:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] = x[k] << 16;
+      break;
+    case TSB_I16:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] = (unsigned)(int)(short)x[k];
+      break;
+    case TSB_I8:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] = (unsigned)(int)(signed char)x[k];
+      break;
+    default: break;  // 32-bit types and unsigned narrow types are already in place
   }
-  return 0u;
+}
+template <int VEC>
+__device__ __forceinline__ void reg_to_raw(int dt, unsigned (&x)[VEC]) {
+  switch (dt) {
+    case TSB_F16:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] = __half_as_ushort(__float2half_rn(__uint_as_float(x[k])));
+      break;
+    case TSB_BF16:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(x[k])));
+      break;
+    case TSB_I16: case TSB_U16:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] &= 0xffffu;
+      break;
+    case TSB_I8: case TSB_U8:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] &= 0xffu;
+      break;
+    case TSB_I1:
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] &= 1u;
+      break;
+    default: break;
+  }
+}
+__device__ __forceinline__ unsigned ld_raw(const char *p, int esize) {
+  if (esize == 4) return *reinterpret_cast<const unsigned *>(p);
+  if (esize == 2) return *reinterpret_cast<const unsigned short *>(p);
+  return *reinterpret_cast<const unsigned char *>(p);
+}
+__device__ __forceinline__ void st_raw(char *p, int esize, unsigned v) {
+  if (esize == 4) *reinterpret_cast<unsigned *>(p) = v;
+  else if (esize == 2) *reinterpret_cast<unsigned short *>(p) = (unsigned short)v;
+  else *reinterpret_cast<unsigned char *>(p) = (unsigned char)v;
+}
+__device__ __forceinline__ unsigned ld_elem(const char *p, int dt) {
+  unsigned x[1] = {ld_raw(p, dtype_size(dt))};
+  raw_to_reg<1>(dt, x);
+  return x[0];
 }
 __device__ __forceinline__ void st_elem(char *p, int dt, unsigned v) {
-  switch (dt) {
-    case TSB_F32: case TSB_I32: case TSB_U32: *reinterpret_cast<unsigned *>(p) = v; break;
-    case TSB_F16: *reinterpret_cast<__half *>(p) = __float2half_rn(__uint_as_float(v)); break;
-    case TSB_BF16: *reinterpret_cast<__nv_bfloat16 *>(p) = __float2bfloat16_rn(__uint_as_float(v)); break;
-    case TSB_I16: case TSB_U16: *reinterpret_cast<unsigned short *>(p) = (unsigned short)v; break;
-    case TSB_I8: case TSB_U8: *reinterpret_cast<unsigned char *>(p) = (unsigned char)v; break;
-    case TSB_I1: *reinterpret_cast<unsigned char *>(p) = (unsigned char)(v & 1u); break;
-  }
+  unsigned x[1] = {v};
+  reg_to_raw<1>(dt, x);
+  st_raw(p, dtype_size(dt), x[0]);
 }
 
 // Round an fp32 result to the value set of `dt` (identity for f32).
@@ -244,7 +292,7 @@ __device__ __forceinline__ void program_state(const DAcc &A, const int size[3], 
 
 template <int VEC>
 __device__ __forceinline__ void load_vec(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
-                                         unsigned out[VEC]) {
+                                         unsigned (&out)[VEC]) {
   const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
   long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
   const unsigned fill = A.has_other ? A.other : 0u;
@@ -278,30 +326,31 @@ __device__ __forceinline__ void load_vec(const DAcc &A, const ProgState &s, int 
       out[0] = v.x; out[1 % VEC] = v.y; out[2 % VEC] = v.z; out[3 % VEC] = v.w;
     } else if (A.esize == 2) {
       uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
-      unsigned short h[4] = {(unsigned short)(v.x & 0xffff), (unsigned short)(v.x >> 16),
-                             (unsigned short)(v.y & 0xffff), (unsigned short)(v.y >> 16)};
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) out[k] = ld_elem(reinterpret_cast<const char *>(&h[k]), A.dtype);
+      out[0] = v.x & 0xffffu; out[1 % VEC] = v.x >> 16; out[2 % VEC] = v.y & 0xffffu; out[3 % VEC] = v.y >> 16;
+      raw_to_reg<VEC>(A.dtype, out);
     } else {
       unsigned v = __ldg(reinterpret_cast<const unsigned *>(p));
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        unsigned char b = (unsigned char)(v >> (8 * k));
-        out[k] = ld_elem(reinterpret_cast<const char *>(&b), A.dtype);
-      }
+      for (int k = 0; k < VEC; ++k) out[k] = (v >> (8 * k)) & 0xffu;
+      raw_to_reg<VEC>(A.dtype, out);
     }
     return;
   }
+  bool okk[VEC];
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
-    bool ok = outer && (i2 + k) < s.dim[2];
-    out[k] = ok ? ld_elem(A.base + (e + k * A.stride[2]) * A.esize, A.dtype) : fill;
+    okk[k] = outer && (i2 + k) < s.dim[2];
+    out[k] = okk[k] ? ld_raw(A.base + (e + k * A.stride[2]) * A.esize, A.esize) : 0u;
   }
+  raw_to_reg<VEC>(A.dtype, out);
+#pragma unroll
+  for (int k = 0; k < VEC; ++k)
+    if (!okk[k]) out[k] = fill;
 }
 
 template <int VEC>
 __device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
-                                          const unsigned in[VEC]) {
+                                          const unsigned (&in)[VEC]) {
   const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
   if (!outer) return;
   long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
@@ -320,26 +369,30 @@ __device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int
     if (A.esize == 4) {
       *reinterpret_cast<uint4 *>(p) = make_uint4(in[0], in[1 % VEC], in[2 % VEC], in[3 % VEC]);
     } else if (A.esize == 2) {
-      unsigned short h[4];
+      unsigned h[VEC];
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) st_elem(reinterpret_cast<char *>(&h[k]), A.dtype, in[k]);
-      *reinterpret_cast<uint2 *>(p) =
-          make_uint2((unsigned)h[0] | ((unsigned)h[1] << 16), (unsigned)h[2] | ((unsigned)h[3] << 16));
+      for (int k = 0; k < VEC; ++k) h[k] = in[k];
+      reg_to_raw<VEC>(A.dtype, h);
+      *reinterpret_cast<uint2 *>(p) = make_uint2(h[0] | (h[1 % VEC] << 16), h[2 % VEC] | (h[3 % VEC] << 16));
     } else {
+      unsigned h[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) h[k] = in[k];
+      reg_to_raw<VEC>(A.dtype, h);
       unsigned v = 0;
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        unsigned char b;
-        st_elem(reinterpret_cast<char *>(&b), A.dtype, in[k]);
-        v |= (unsigned)b << (8 * k);
-      }
+      for (int k = 0; k < VEC; ++k) v |= h[k] << (8 * k);
       *reinterpret_cast<unsigned *>(p) = v;
     }
     return;
   }
+  unsigned h[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) h[k] = in[k];
+  reg_to_raw<VEC>(A.dtype, h);
 #pragma unroll
   for (int k = 0; k < VEC; ++k)
-    if (i2 + k < s.dim[2]) st_elem(A.base + (e + k * A.stride[2]) * A.esize, A.dtype, in[k]);
+    if (i2 + k < s.dim[2]) st_raw(A.base + (e + k * A.stride[2]) * A.esize, A.esize, h[k]);
 }
 
 
