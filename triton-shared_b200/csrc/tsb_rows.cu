@@ -240,6 +240,10 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
   // buffer 0 is next written a full reduction (and its barrier) after its last read
   __shared__ float red[2][THREADS / 32];
   const int t = threadIdx.x;
+  // the first row's loads go out before weight and bias are staged, so the two latencies overlap
+  long long row = row_lo + blockIdx.x;
+  uint4 xq[VPT];
+  if (row < row_hi) Tile::load(X + row * xs, n_cols, t, xq);
   {
     uint4 q[VPT];
     Tile::load(W, n_cols, t, q);
@@ -263,9 +267,6 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
   }
   // each thread reads back only the slots it wrote: no barrier needed
   const float fn = (float)n_cols;
-  long long row = row_lo + blockIdx.x;
-  uint4 xq[VPT];
-  if (row < row_hi) Tile::load(X + row * xs, n_cols, t, xq);
   for (; row < row_hi; row += gridDim.x) {
     float x[VPT][EPV];
 #pragma unroll
@@ -286,14 +287,14 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
       if (Tile::col(v, EPV - 1, t) < n_cols) {
 #pragma unroll
         for (int k = 0; k < EPV; ++k) {
-          const float d = x[v][k] - mean;
-          q4[k & 3] = fmaf(d, d, q4[k & 3]);
+          x[v][k] = x[v][k] - mean;  // kept: the output pass starts from the centred value
+          q4[k & 3] = fmaf(x[v][k], x[v][k], q4[k & 3]);
         }
       } else {
 #pragma unroll
         for (int k = 0; k < EPV; ++k) {
-          const float d = (Tile::col(v, k, t) < n_cols) ? x[v][k] - mean : 0.f;
-          q4[k & 3] = fmaf(d, d, q4[k & 3]);
+          x[v][k] = (Tile::col(v, k, t) < n_cols) ? x[v][k] - mean : 0.f;
+          q4[k & 3] = fmaf(x[v][k], x[v][k], q4[k & 3]);
         }
       }
     }
@@ -312,10 +313,11 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
       for (int j = 0; j < EPV / 4; ++j) {
         const float4 w = sw[j * SLOTS + v * THREADS + t];
         const float4 b = sb[j * SLOTS + v * THREADS + t];
-        y[4 * j + 0] = ((x[v][4 * j + 0] - mean) * rstd) * w.x + b.x;
-        y[4 * j + 1] = ((x[v][4 * j + 1] - mean) * rstd) * w.y + b.y;
-        y[4 * j + 2] = ((x[v][4 * j + 2] - mean) * rstd) * w.z + b.z;
-        y[4 * j + 3] = ((x[v][4 * j + 3] - mean) * rstd) * w.w + b.w;
+        // x already holds x - mean: ((x - mean) * rstd) * w + b, one rounding per op
+        y[4 * j + 0] = (x[v][4 * j + 0] * rstd) * w.x + b.x;
+        y[4 * j + 1] = (x[v][4 * j + 1] * rstd) * w.y + b.y;
+        y[4 * j + 2] = (x[v][4 * j + 2] * rstd) * w.z + b.z;
+        y[4 * j + 3] = (x[v][4 * j + 3] * rstd) * w.w + b.w;
       }
       if (ALIGNED && Tile::col(v, EPV - 1, t) < n_cols) {
         __stcs(reinterpret_cast<uint4 *>(dst + Tile::col(v, 0, t)), Io<T>::pack(y));
