@@ -284,6 +284,15 @@ class FakeLib:
                 q = np.abs(a) // np.abs(bz) * np.sign(a) * np.sign(bz)
                 r = {"divsi": q, "remsi": a - q * bz, "minsi": np.minimum(a, b), "maxsi": np.maximum(a, b)}[name]
                 return self._wrap(r.astype(np.int32).view(np.uint32), dt)
+            if name in ("shli", "shrsi", "shrui", "divui", "remui", "minui", "maxui"):
+                a64, b64 = u(o.a).astype(np.uint64), u(o.b).astype(np.uint64)
+                sh = np.minimum(b64, 63)
+                bz = np.where(b64 == 0, 1, b64)
+                r = {"shli": np.where(b64 >= 32, 0, a64 << sh), "shrui": np.where(b64 >= 32, 0, a64 >> sh),
+                     "shrsi": (i(o.a).astype(np.int64) >> np.minimum(b64, 31).astype(np.int64)).astype(np.uint64),
+                     "divui": np.where(b64 == 0, 0, a64 // bz), "remui": np.where(b64 == 0, 0, a64 % bz),
+                     "minui": np.minimum(a64, b64), "maxui": np.maximum(a64, b64)}[name]
+                return self._wrap((r & 0xffffffff).astype(np.uint32), dt)
             if name == "absi":
                 return self._wrap(np.abs(i(o.a)).view(np.uint32), dt)
             if name == "cmpf":

@@ -316,3 +316,38 @@ def block_ptr_sum_kernel(x_ptr, out_ptr, stride, n_elements, BLOCK_SIZE: tl.cons
                            offsets=[stride * pid], block_shape=[BLOCK_SIZE], order=[0])
     x = tl.load(bp, boundary_check=[0])
     tl.store(out_ptr + pid, tl.sum(x, axis=0))
+
+
+# ---- a spread of elementwise ops for the register VM ------------------------------------------
+
+@triton.jit
+def mixed_float_kernel(x_ptr, y_ptr, o1_ptr, o2_ptr, o3_ptr, n, slope, BLOCK: tl.constexpr):
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    m = offs < n
+    x = tl.load(x_ptr + offs, mask=m, other=0.0)
+    y = tl.load(y_ptr + offs, mask=m, other=1.0)
+    leaky = tl.where(x > 0, x, slope * x)
+    tl.store(o1_ptr + offs, leaky, mask=m)
+    sig = 1.0 / (1.0 + tl.exp(-x))
+    tl.store(o2_ptr + offs, tl.maximum(sig, tl.minimum(tl.abs(y), 0.75)) + tl.sqrt(tl.abs(x)) * tl.log(tl.abs(y) + 1.0), mask=m)
+    tl.store(o3_ptr + offs, tl.floor(x * 4.0) + tl.cos(y) * tl.sin(x), mask=m)
+
+
+@triton.jit
+def mixed_int_kernel(a_ptr, b_ptr, o1_ptr, o2_ptr, o3_ptr, n, BLOCK: tl.constexpr):
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    m = offs < n
+    a = tl.load(a_ptr + offs, mask=m, other=1)
+    b = tl.load(b_ptr + offs, mask=m, other=1)
+    tl.store(o1_ptr + offs, (a * 3 + b) // 7 + (a % 5) - tl.minimum(a, b), mask=m)
+    tl.store(o2_ptr + offs, ((a & b) | (a ^ 21)) + (b << 2) + (a >> 1), mask=m)
+    tl.store(o3_ptr + offs, (a.to(tl.float32) * 0.5 + offs.to(tl.float32)).to(tl.int32), mask=m)
+
+
+@triton.jit
+def bytes_kernel(x_ptr, o_ptr, n, BLOCK: tl.constexpr):
+    """uint8 in, uint8 out: saturating brighten (narrow integer I/O through the 32-bit lanes)."""
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    m = offs < n
+    x = tl.load(x_ptr + offs, mask=m, other=0).to(tl.int32)
+    tl.store(o_ptr + offs, tl.minimum(x * 2 + 10, 255).to(tl.uint8), mask=m)

@@ -372,3 +372,42 @@ def test_block_programs_on_host_stand_in():
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
     assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 4
+
+
+# ------------------------------------------------------------------ a spread of elementwise ops
+def _mixed_op_cases(dev):
+    out = []
+    torch.manual_seed(11)
+    n = 3000
+    x = torch.randn(n, device=dev)
+    y = torch.randn(n, device=dev)
+    o1, o2, o3 = (torch.zeros(n, device=dev) for _ in range(3))
+    K.mixed_float_kernel[(3,)](x, y, o1, o2, o3, n, 0.1, BLOCK=1024)
+    out.append(("leaky", o1.cpu(), torch.where(x > 0, x, 0.1 * x).cpu(), 1e-6))
+    sig = 1.0 / (1.0 + torch.exp(-x))
+    ref2 = torch.maximum(sig, torch.minimum(y.abs(), torch.tensor(0.75, device=dev))) + x.abs().sqrt() * torch.log(y.abs() + 1.0)
+    out.append(("sigmoid_mix", o2.cpu(), ref2.cpu(), 1e-5))
+    out.append(("floor_trig", o3.cpu(), (torch.floor(x * 4.0) + torch.cos(y) * torch.sin(x)).cpu(), 1e-5))
+    a = torch.randint(0, 1000, (n,), dtype=torch.int32, device=dev)
+    b = torch.randint(1, 1000, (n,), dtype=torch.int32, device=dev)
+    i1, i2, i3 = (torch.zeros(n, dtype=torch.int32, device=dev) for _ in range(3))
+    K.mixed_int_kernel[(3,)](a, b, i1, i2, i3, n, BLOCK=1024)
+    out.append(("int_arith", i1.cpu(), ((a * 3 + b) // 7 + (a % 5) - torch.minimum(a, b)).cpu(), 0))
+    out.append(("int_bits", i2.cpu(), (((a & b) | (a ^ 21)) + (b << 2) + (a >> 1)).cpu(), 0))
+    offs = torch.arange(n, device=dev)
+    out.append(("int_float_int", i3.cpu(), (a.float() * 0.5 + offs.float()).to(torch.int32).cpu(), 0))
+    u = torch.randint(0, 256, (n,), dtype=torch.uint8, device=dev)
+    uo = torch.zeros(n, dtype=torch.uint8, device=dev)
+    K.bytes_kernel[(3,)](u, uo, n, BLOCK=1024)
+    out.append(("bytes", uo.cpu(), torch.clamp(u.int() * 2 + 10, max=255).to(torch.uint8).cpu(), 0))
+    return out
+
+
+def test_mixed_ops_on_host_stand_in():
+    with fake_device():
+        cases = _mixed_op_cases("cpu")
+    for name, got, exp, tol in cases:
+        if tol == 0:
+            assert torch.equal(got, exp), name
+        else:
+            assert torch.allclose(got, exp, rtol=tol, atol=tol), name

@@ -361,3 +361,14 @@ def test_block_programs(drv):
             assert torch.equal(got, exp), name
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
+
+
+def test_mixed_elementwise_ops(drv):
+    """where / exp / sqrt / log / trig / floor, integer division, remainder, shifts and bit ops,
+    int <-> float casts and uint8 I/O through the register VM, against torch."""
+    from test_cpu_host import _mixed_op_cases
+    for name, got, exp, tol in _mixed_op_cases("cuda"):
+        if tol == 0:
+            assert torch.equal(got, exp), name
+        else:
+            assert torch.allclose(got, exp, rtol=tol, atol=tol), name
