@@ -359,7 +359,7 @@ def main():
     torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ secondary workloads
-    names = {"vec_add", "layernorm", "strided_reduce", "matmul"}
+    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy"}
     # kernels of the widened rows (general engines rather than dedicated kernels); not part of "all"
     extra = {"gelu_bias", "rmsnorm", "wrap_rows"}
     chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names | extra}
@@ -508,9 +508,23 @@ def main():
                 K.wrap_rows_kernel[(1,)](A, Cc, M, N, 1, N, 1, START=4090, BM=64, BN=64, STEPS=N // 64)
             record("wrap_rows", step, 8 * 64 * N, 1e9, "hbm", "GB/s", launches=N // 64)
 
+        def wl_block_copy():
+            # masked strided 2-D block copy, fp32 16,000 x 16,000 (ragged against 64 x 128 tiles), row-major to row-major
+            M = N = 8000 if args.small else 16000
+            src = torch.randn(M, N, device="cuda")
+            dst = torch.empty(M, N, device="cuda")
+            grid2 = ((M + 63) // 64, (N + 127) // 128)
+
+            def step():
+                K.copy_2d_kernel[grid2](src, dst, M, N, N, 1, N, 1, BM=64, BN=128)
+            record("block_copy", step, 8 * M * N, 1e9, "hbm", "GB/s")
+            if "value" in wl["block_copy"]:
+                wl["block_copy"]["result_check"] = bool(torch.equal(src, dst))
+
         for name, fn in (("vec_add", wl_vec_add), ("layernorm", wl_layernorm),
                          ("strided_reduce", wl_strided_reduce), ("matmul", wl_matmul),
-                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("wrap_rows", wl_wrap_rows)):
+                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("wrap_rows", wl_wrap_rows),
+                         ("block_copy", wl_block_copy)):
             if name in chosen:
                 fn()
                 torch.cuda.empty_cache()

@@ -351,3 +351,14 @@ def bytes_kernel(x_ptr, o_ptr, n, BLOCK: tl.constexpr):
     m = offs < n
     x = tl.load(x_ptr + offs, mask=m, other=0).to(tl.int32)
     tl.store(o_ptr + offs, tl.minimum(x * 2 + 10, 255).to(tl.uint8), mask=m)
+
+
+@triton.jit
+def copy_2d_kernel(src_ptr, dst_ptr, M, N, s_sm, s_sn, d_sm, d_sn, BM: tl.constexpr, BN: tl.constexpr):
+    """Masked strided 2-D block copy (one tile per program, 2-D grid): the lowered form is exactly
+    reinterpret_cast + subview + memref.copy on both sides."""
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+    x = tl.load(src_ptr + offs_m[:, None] * s_sm + offs_n[None, :] * s_sn, mask=mask)
+    tl.store(dst_ptr + offs_m[:, None] * d_sm + offs_n[None, :] * d_sn, x, mask=mask)

@@ -372,3 +372,21 @@ def test_mixed_elementwise_ops(drv):
             assert torch.equal(got, exp), name
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.uint8])
+@pytest.mark.parametrize("M,N", [(1000, 1000), (130, 72), (64, 128)])
+def test_block_copy_2d(drv, dtype, M, N):
+    """Masked strided 2-D block copy: aligned rows take the lean 16-byte kernel, a transposed
+    destination and odd pitches the general one; nothing outside the mask is written."""
+    torch.manual_seed(9)
+    src = (torch.rand(M, N, device="cuda") * 200).to(dtype)
+    grid = ((M + 63) // 64, (N + 127) // 128)
+    # row-major -> row-major inside a padded buffer (guard columns must stay untouched)
+    pad = torch.full((M, N + 16), 7, dtype=dtype, device="cuda")
+    K.copy_2d_kernel[grid](src, pad, M, N, N, 1, N + 16, 1, BM=64, BN=128)
+    assert torch.equal(pad[:, :N], src) and torch.all(pad[:, N:] == 7)
+    # row-major -> column-major (transposing store: unit stride along rows)
+    dst_t = torch.zeros(N, M, dtype=dtype, device="cuda")
+    K.copy_2d_kernel[grid](src, dst_t, M, N, N, 1, 1, M, BM=64, BN=128)
+    assert torch.equal(dst_t.t(), src)

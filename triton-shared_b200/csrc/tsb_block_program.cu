@@ -27,6 +27,7 @@ struct BpParams {
   int size[3];
   int lg[3];  // log2 of size
   int grid[3];
+  int order[3];   // grid axes from fastest to slowest in the order programs are walked
   long long pid_lo, pid_hi;
   int reg_mask[BP_MAX_REGS];  // bit d set: the register extends along dim d
   int reg_off[BP_MAX_REGS];   // offset (32-bit words) in dynamic shared memory
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
     long long px, py, pz;
-    split_pid(P.grid, prog, px, py, pz);
+    split_pid(P.grid, P.order, prog, px, py, pz);
     for (int k = 0; k < P.n_ops; ++k) {
       __syncthreads();  // every op may read what other threads wrote in the previous one
       const tsb_op &op = P.ops[k];
@@ -312,6 +313,7 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
   P.n_acc = n_acc; P.n_ops = n_ops; P.n_regs = n_regs;
   for (int k = 0; k < 3; ++k) P.grid[k] = grid[k] > 0 ? grid[k] : 1;
   P.pid_lo = pid_lo; P.pid_hi = pid_hi;
+  choose_program_order(P.acc, n_acc, P.grid, pid_lo, pid_hi, P.order);
   if (pid_hi == pid_lo) return TSB_OK;
   static long long smem_set = 0;
   if (smem > 48 * 1024 && smem_set < smem) {

@@ -22,6 +22,7 @@ struct EwParams {
   int lg[3];      // log2 of sizes (Triton block shapes are powers of two)
   int lanes;      // size[0]*size[1]*size[2]
   int grid[3];
+  int order[3];   // grid axes from fastest to slowest in the order programs are walked
   long long pid_lo, pid_hi;
 };
 
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
   const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
     long long px, py, pz;
-    split_pid(P.grid, prog, px, py, pz);
+    split_pid(P.grid, P.order, prog, px, py, pz);
     __syncthreads();  // the previous program's state is no longer read
     if (threadIdx.x < P.n_acc) program_state(P.acc[threadIdx.x], P.size, px, py, pz, st[threadIdx.x]);
     __syncthreads();
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(256) ew_binary_f32_kernel(const __grid_constan
       long long prog = prog0 + u;
       if (prog >= P.pid_hi) prog = P.pid_hi - 1;  // duplicate work is skipped below
       long long px, py, pz;
-      split_pid(P.grid, prog, px, py, pz);
+      split_pid(P.grid, P.order, prog, px, py, pz);
       program_state(A0, P.size, px, py, pz, s0[u]);
       program_state(A1, P.size, px, py, pz, s1[u]);
       program_state(AS, P.size, px, py, pz, ss[u]);
@@ -204,6 +205,95 @@ __global__ void __launch_bounds__(256) ew_binary_f32_kernel(const __grid_constan
         for (int v = 0; v < VEC; ++v)
           r[v] = __float_as_uint(binf(opc, __uint_as_float(a[u][v]), __uint_as_float(b[u][v])));
         store_vec<VEC>(AS, ss[u], i0, i1, i2, r);
+      }
+    }
+  }
+}
+
+// ---- copy body: store(load) with one element type ------------------------------------------
+// The B200 counterpart of memrefCopy (CRunnerUtils.cpp:58-113) for masked strided blocks of any
+// rank <= 3: 16-byte (or 8 / 4-byte for narrow types) accesses along the unit-stride dim, four
+// independent vectors in flight per thread, no VM.
+template <int VEC>
+__global__ void __launch_bounds__(256) ew_copy_kernel(const __grid_constant__ EwParams P) {
+  const int items = P.lanes / VEC;
+  const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
+  const DAcc &AL = P.acc[P.ops[0].a];
+  const DAcc &AS = P.acc[P.ops[1].a];
+  constexpr int U = 4;
+  for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
+    long long px, py, pz;
+    split_pid(P.grid, P.order, prog, px, py, pz);
+    ProgState sl, ss;
+    program_state(AL, P.size, px, py, pz, sl);
+    program_state(AS, P.size, px, py, pz, ss);
+    for (int it0 = threadIdx.x; it0 < items; it0 += blockDim.x * U) {
+      unsigned v[U][VEC];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int it = it0 + u * (int)blockDim.x;
+        if (it < items) {
+          const int l = it * VEC;
+          load_vec<VEC>(AL, sl, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), v[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int it = it0 + u * (int)blockDim.x;
+        if (it < items) {
+          const int l = it * VEC;
+          store_vec<VEC>(AS, ss, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), v[u]);
+        }
+      }
+    }
+  }
+}
+
+// Lean form of the copy for rank <= 2 blocks whose rows are 16-byte aligned on both sides and
+// whose load and store masks are the same: raw 16-byte vectors, addresses by pointer arithmetic.
+__global__ void __launch_bounds__(256) ew_copy2d_kernel(const __grid_constant__ EwParams P) {
+  const DAcc &AL = P.acc[P.ops[0].a];
+  const DAcc &AS = P.acc[P.ops[1].a];
+  const int es = AL.esize;
+  const int epv_lg = es == 4 ? 2 : (es == 2 ? 3 : 4);  // elements per 16-byte vector
+  const int vr_lg = P.lg[2] - epv_lg;                  // vectors per row
+  const int n_vec = P.size[1] << vr_lg;
+  const long long pitch_l = AL.stride[1] * es, pitch_s = AS.stride[1] * es;
+  constexpr int U = 4;
+  for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
+    long long px, py, pz;
+    split_pid(P.grid, P.order, prog, px, py, pz);
+    ProgState sl, ss;
+    program_state(AL, P.size, px, py, pz, sl);
+    program_state(AS, P.size, px, py, pz, ss);
+    const char *lb = AL.base + sl.off * es;
+    char *sb = AS.base + ss.off * es;
+    const int rows = ss.dim[1], cols = ss.dim[2];
+    for (int v0 = threadIdx.x; v0 < n_vec; v0 += blockDim.x * U) {
+      uint4 q[U];
+      int row[U], col[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * (int)blockDim.x;
+        row[u] = v >> vr_lg;
+        col[u] = (v & ((1 << vr_lg) - 1)) << epv_lg;
+        if (v < n_vec && row[u] < rows && col[u] + (1 << epv_lg) <= cols)
+          q[u] = __ldcs(reinterpret_cast<const uint4 *>(lb + row[u] * pitch_l + (long long)col[u] * es));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * (int)blockDim.x;
+        if (v >= n_vec || row[u] >= rows) continue;
+        if (col[u] + (1 << epv_lg) <= cols) {
+          __stcs(reinterpret_cast<uint4 *>(sb + row[u] * pitch_s + (long long)col[u] * es), q[u]);
+        } else {
+          // ragged right edge: element by element
+          for (int e = col[u]; e < cols; ++e) {
+            const char *ps = lb + row[u] * pitch_l + (long long)e * es;
+            char *pd = sb + row[u] * pitch_s + (long long)e * es;
+            st_raw(pd, es, ld_raw(ps, es));
+          }
+        }
       }
     }
   }
@@ -443,6 +533,7 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
   P.n_acc = n_acc;
   P.n_ops = n_ops;
   for (int k = 0; k < 3; ++k) P.grid[k] = grid[k] > 0 ? grid[k] : 1;
+  choose_program_order(P.acc, n_acc, P.grid, pid_lo, pid_hi, P.order);
   P.pid_lo = pid_lo;
   P.pid_hi = pid_hi;
   return TSB_OK;
@@ -482,6 +573,35 @@ static int vm_regs_used(const tsb_op *ops, int n_ops) {
     if (o.opcode == TSB_OP_STORE && o.b > hi) hi = o.b;
   }
   return hi + 1;
+}
+
+static bool is_copy(const tsb_access *acc, const tsb_op *ops, int n_ops) {
+  return n_ops == 2 && ops[0].opcode == TSB_OP_LOAD && ops[1].opcode == TSB_OP_STORE && ops[1].b == ops[0].dst &&
+         acc[ops[0].a].is_store == 0 && acc[ops[0].a].dtype == acc[ops[1].a].dtype;
+}
+
+// ew_copy2d_kernel applies when both sides are plain memory accesses of rank <= 2 with unit inner
+// stride, every row start is 16-byte aligned and the two masks are the same descriptor.
+static bool copy2d_ok(const EwParams &P, const int32_t grid[3]) {
+  const DAcc &l = P.acc[P.ops[0].a], &st = P.acc[P.ops[1].a];
+  if (P.size[0] != 1 || l.kind != 0 || st.kind != 1 || l.n_wrap || st.n_wrap) return false;
+  if ((long long)P.size[2] * l.esize % 16 != 0) return false;
+  if (l.masked != st.masked) return false;
+  for (int d = 1; d < 3; ++d) {
+    if (!(l.masked & (1 << d))) continue;
+    if (l.mstart0[d] != st.mstart0[d] || l.bound[d] != st.bound[d]) return false;
+    for (int k = 0; k < 3; ++k)
+      if (l.mstart_pid[d][k] != st.mstart_pid[d][k]) return false;
+  }
+  const DAcc *both[2] = {&l, &st};
+  for (const DAcc *d : both) {
+    const long long es = d->esize;
+    if (d->stride[2] != 1 || ((uintptr_t)d->base + d->off0 * es) % 16 != 0) return false;
+    for (int k = 0; k < 3; ++k)
+      if (grid[k] > 1 && (d->off_pid[k] * es) % 16 != 0) return false;
+    if (P.size[1] > 1 && (d->stride[1] * es) % 16 != 0) return false;
+  }
+  return true;
 }
 
 static bool is_fast_binary(const tsb_access *acc, const tsb_op *ops, int n_ops) {
@@ -544,6 +664,18 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     if (vec == 4) ew_binary_f32_kernel<4><<<(unsigned)ctas, threads, 0, s>>>(P);
     else ew_binary_f32_kernel<1><<<(unsigned)ctas, threads, 0, s>>>(P);
     TSB_LAUNCH_OK("ew_binary_f32_kernel");
+    return TSB_OK;
+  }
+  if (is_copy(acc, ops, n_ops)) {
+    long long ctas = n_prog < max_ctas ? n_prog : max_ctas;
+    if (copy2d_ok(P, grid)) {
+      ew_copy2d_kernel<<<(unsigned)ctas, 256, 0, s>>>(P);
+      TSB_LAUNCH_OK("ew_copy2d_kernel");
+      return TSB_OK;
+    }
+    if (vec == 4) ew_copy_kernel<4><<<(unsigned)ctas, threads, 0, s>>>(P);
+    else ew_copy_kernel<1><<<(unsigned)ctas, threads, 0, s>>>(P);
+    TSB_LAUNCH_OK("ew_copy_kernel");
     return TSB_OK;
   }
   // four lane-vectors per thread when the block is large enough to keep at least a warp busy

@@ -438,17 +438,23 @@ __device__ __forceinline__ constexpr int alu_arity() {
   X(TSB_OP_SHRUI) X(TSB_OP_ABSI) X(TSB_OP_CMPF) X(TSB_OP_CMPI) X(TSB_OP_SELECT) X(TSB_OP_CAST)      \
   X(TSB_OP_FMA)
 
-__device__ __forceinline__ void split_pid(const int grid[3], long long prog, long long &px, long long &py,
-                                          long long &pz) {
+// Program id of the k-th program a kernel processes.  order[] lists the grid axes from fastest to
+// slowest varying; {0,1,2} is the linearisation of the launch (x fastest).  Programs are
+// independent, so when a launch covers the whole grid the kernels may walk them with the axis
+// of smallest address step fastest, which keeps concurrently running CTAs on neighbouring memory.
+__device__ __forceinline__ void split_pid(const int grid[3], const int order[3], long long k, long long &px,
+                                          long long &py, long long &pz) {
   if (grid[1] == 1 && grid[2] == 1) {
-    px = prog; py = 0; pz = 0;
+    px = k; py = 0; pz = 0;
     return;
   }
-  const unsigned long long gx = (unsigned long long)grid[0], gy = (unsigned long long)grid[1];
-  const unsigned long long q = (unsigned long long)prog / gx;
-  px = (long long)((unsigned long long)prog - q * gx);
-  py = (long long)(q % gy);
-  pz = (long long)(q / gy);
+  long long p[3];
+  const unsigned long long g0 = (unsigned long long)grid[order[0]], g1 = (unsigned long long)grid[order[1]];
+  const unsigned long long q = (unsigned long long)k / g0;
+  p[order[0]] = (long long)((unsigned long long)k - q * g0);
+  p[order[1]] = (long long)(q % g1);
+  p[order[2]] = (long long)(q / g1);
+  px = p[0]; py = p[1]; pz = p[2];
 }
 
 
@@ -476,6 +482,26 @@ inline int ilog2_exact(long long v) {
   return ((1ll << l) == v) ? l : -1;
 }
 
+
+// Order in which a kernel walks the programs of a launch: natural unless the launch covers the
+// whole grid, in which case the axis along which the first store moves least goes fastest.
+inline void choose_program_order(const DAcc *acc, int n_acc, const int grid[3], long long pid_lo,
+                                 long long pid_hi, int order[3]) {
+  order[0] = 0; order[1] = 1; order[2] = 2;
+  const long long total = (long long)grid[0] * grid[1] * grid[2];
+  if (pid_lo != 0 || pid_hi != total) return;
+  const DAcc *st = nullptr;
+  for (int a = 0; a < n_acc && !st; ++a)
+    if (acc[a].kind == 1) st = &acc[a];
+  if (!st) return;
+  auto step = [&](int a) {
+    long long v = st->off_pid[a] < 0 ? -st->off_pid[a] : st->off_pid[a];
+    return grid[a] > 1 ? v : 0x7fffffffffffffffll;  // unit axes last
+  };
+  for (int i = 0; i < 3; ++i)
+    for (int j = i + 1; j < 3; ++j)
+      if (step(order[j]) < step(order[i])) { int t = order[i]; order[i] = order[j]; order[j] = t; }
+}
 
 // Device form of one access of a launch: validates `s` and pads it to the rank-3 iteration space
 // `size` (leading unit dims). `vec` is the lane-vector width the kernel will use (4 or 1).
