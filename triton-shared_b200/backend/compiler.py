@@ -39,9 +39,7 @@ def ttir_to_plan(mod, metadata) -> bytes:
     """The `plan` stage: parse, analyse, select a kernel family."""
     text = mod.str_nodebug() if hasattr(mod, "str_nodebug") else str(mod)
     _dump("tt.mlir", text)
-    fn = ttir.parse_module(text)
-    kernel, an = structured.analyze(fn)
-    pl = _plan.make_plan(kernel, an)
+    pl, fn = _plan_of(text)
     metadata["name"] = fn.name
     metadata["shared"] = 0
     metadata["family"] = pl.family
@@ -50,11 +48,22 @@ def ttir_to_plan(mod, metadata) -> bytes:
     return blob
 
 
+def _plan_of(text: str):
+    """Parse, analyse, select a family.  Anything the parser or the analysis does not understand is
+    reported as UnsupportedTTIR (never as an internal error, and never by falling back)."""
+    try:
+        fn = ttir.parse_module(text)
+        kernel, an = structured.analyze(fn)
+    except ttir.UnsupportedTTIR:
+        raise
+    except (AttributeError, AssertionError, KeyError, IndexError, ValueError, TypeError) as e:
+        raise ttir.UnsupportedTTIR(f"TTIR construct outside the structured subset ({type(e).__name__}: {e})") from e
+    return _plan.make_plan(kernel, an), fn
+
+
 def compile_ttir_text(text: str) -> "_plan.Plan":
     """Plan for a TTIR module given as text (used by tests and tools)."""
-    fn = ttir.parse_module(text)
-    kernel, an = structured.analyze(fn)
-    return _plan.make_plan(kernel, an)
+    return _plan_of(text)[0]
 
 
 @dataclass(frozen=True)
