@@ -43,6 +43,7 @@ extern "C" {
 #define TSB_MAX_ACCESSES 16
 #define TSB_MAX_OPS 96
 #define TSB_NUM_REGS 16
+#define TSB_MAX_LOOPS 4
 
 /* element types (what !tt.ptr<T> / tensor<..xT> name) */
 enum tsb_dtype {
@@ -121,6 +122,12 @@ typedef struct tsb_access {
   int32_t n_wrap;      /* 0..2 wrap-around terms added to the address */
   int32_t pad2_;
   tsb_wrap wrap[2];
+  /* tsb_block_program only: per iteration of enclosing loop l (TSB_OP_LOOP_BEGIN slot l) the
+   * element offset advances by offset_loop[l] and the mask start of dim d by
+   * mask_start_loop[d][l] (loop-carried pointers and `for off in range(0, N, BLOCK)` offsets,
+   * PtrAnalysis.cpp:1536-1602).  Ignored by the other entry points. */
+  int64_t offset_loop[TSB_MAX_LOOPS];
+  int64_t mask_start_loop[TSB_MAX_RANK][TSB_MAX_LOOPS];
 } tsb_access;
 
 /* Opcodes of the elementwise body (one linalg.generic each in the reference,
@@ -149,7 +156,9 @@ enum tsb_opcode {
   TSB_OP_CAST = 90,
   TSB_OP_BITCAST = 91,
   TSB_OP_FMA = 92, /* math.fma: single rounding */
-  TSB_OP_REDUCE = 100 /* tsb_block_program only: dst <- fold of reg a along dim imm2 with combiner opcode imm */
+  TSB_OP_REDUCE = 100, /* tsb_block_program only: dst <- fold of reg a along dim imm2 with combiner opcode imm */
+  TSB_OP_LOOP_BEGIN = 101, /* tsb_block_program only: loop slot a runs imm iterations; b = index of the op after its LOOP_END */
+  TSB_OP_LOOP_END = 102    /* tsb_block_program only: closes loop slot a */
 };
 
 enum tsb_cmp {

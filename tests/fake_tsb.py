@@ -126,9 +126,9 @@ class FakeLib:
         return 0
 
     @staticmethod
-    def _acc_state(A, p, rank, sizes, idx, lanes):
-        """(element index, validity) of every lane of the iteration space for program p."""
-        off = A.offset0 + sum(A.offset_pid[k] * p[k] for k in range(3))
+    def _acc_state(A, p, rank, sizes, idx, lanes, it=(0, 0, 0, 0)):
+        """(element index, validity) of every lane of the iteration space for program p (and loop counters it)."""
+        off = A.offset0 + sum(A.offset_pid[k] * p[k] for k in range(3)) + sum(A.offset_loop[l] * it[l] for l in range(4))
         valid = np.ones(lanes, dtype=bool)
         elem = np.full(lanes, off, dtype=np.int64)
         for w in range(A.n_wrap):
@@ -140,7 +140,8 @@ class FakeLib:
         for d in range(rank):
             elem = elem + idx[d] * A.strides[d]
             if A.masked[d]:
-                st = A.mask_start0[d] + sum(A.mask_start_pid[d][k] * p[k] for k in range(3))
+                st = A.mask_start0[d] + sum(A.mask_start_pid[d][k] * p[k] for k in range(3)) + \
+                    sum(A.mask_start_loop[d][l] * it[l] for l in range(4))
                 dim = max(min(st + sizes[d], A.mask_bound[d]), st) - st
                 valid &= idx[d] < dim
         return elem, valid
@@ -161,12 +162,23 @@ class FakeLib:
         for prog in range(pid_lo, pid_hi):
             p = (prog % g[0], (prog // g[0]) % g[1], prog // (g[0] * g[1]))
             R = {}
-            for k in range(n_ops):
+            it, trip, begin = [0] * 4, [0] * 4, [0] * 4
+            k = 0
+            while k < n_ops:
                 o = ops[k]
                 name = _OPNAME[o.opcode]
+                if name == "loop_begin":
+                    it[o.a], trip[o.a], begin[o.a] = 0, int(o.imm), k + 1
+                    k = k + 1 if trip[o.a] > 0 else o.b
+                    continue
+                if name == "loop_end":
+                    it[o.a] += 1
+                    k = begin[o.a] if it[o.a] < trip[o.a] else k + 1
+                    continue
+                k += 1
                 if name == "load":
                     A = accs[o.a]
-                    elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes)
+                    elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes, it)
                     if A.is_store == 2:
                         full = valid.astype(np.uint32)
                     elif A.is_store == 3:
@@ -176,7 +188,7 @@ class FakeLib:
                     R[o.dst] = take(full, reg_masks[o.dst]).copy()
                 elif name == "store":
                     A = accs[o.a]
-                    elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes)
+                    elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes, it)
                     m = int(o.imm)
                     val = np.broadcast_to(R[o.b], shape_of(m))
                     sel = take(np.arange(lanes), m).reshape(-1)  # one lane per walked element

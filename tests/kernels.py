@@ -362,3 +362,41 @@ def copy_2d_kernel(src_ptr, dst_ptr, M, N, s_sm, s_sn, d_sm, d_sn, BM: tl.conste
     mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
     x = tl.load(src_ptr + offs_m[:, None] * s_sm + offs_n[None, :] * s_sn, mask=mask)
     tl.store(dst_ptr + offs_m[:, None] * d_sm + offs_n[None, :] * d_sn, x, mask=mask)
+
+
+# ---- loops that carry block values, outside the dedicated families -----------------------------
+
+@triton.jit
+def row_stats_kernel(x_ptr, sum_ptr, max_ptr, stride, N, BLOCK: tl.constexpr):
+    """Per row: sum and maximum over column chunks, two lane accumulators carried through the loop."""
+    row = tl.program_id(0)
+    s_acc = tl.zeros([BLOCK], dtype=tl.float32)
+    m_acc = tl.full([BLOCK], -float("inf"), dtype=tl.float32)
+    for off in range(0, N, BLOCK):
+        cols = off + tl.arange(0, BLOCK)
+        x = tl.load(x_ptr + row * stride + cols, mask=cols < N, other=0.0)
+        s_acc += x
+        m_acc = tl.maximum(m_acc, tl.where(cols < N, x, -float("inf")))
+    tl.store(sum_ptr + row, tl.sum(s_acc, axis=0))
+    tl.store(max_ptr + row, tl.max(m_acc, axis=0))
+
+
+@triton.jit
+def wide_softmax_kernel(out_ptr, in_ptr, stride, N, BLOCK: tl.constexpr):
+    """Softmax of rows wider than one block: three loops over column chunks (max, sum, write)."""
+    row = tl.program_id(0)
+    m_acc = tl.full([BLOCK], -float("inf"), dtype=tl.float32)
+    for off in range(0, N, BLOCK):
+        cols = off + tl.arange(0, BLOCK)
+        m_acc = tl.maximum(m_acc, tl.load(in_ptr + row * stride + cols, mask=cols < N, other=-float("inf")))
+    m = tl.max(m_acc, axis=0)
+    s_acc = tl.zeros([BLOCK], dtype=tl.float32)
+    for off in range(0, N, BLOCK):
+        cols = off + tl.arange(0, BLOCK)
+        x = tl.load(in_ptr + row * stride + cols, mask=cols < N, other=-float("inf"))
+        s_acc += tl.exp(x - m)
+    s = tl.sum(s_acc, axis=0)
+    for off in range(0, N, BLOCK):
+        cols = off + tl.arange(0, BLOCK)
+        x = tl.load(in_ptr + row * stride + cols, mask=cols < N, other=-float("inf"))
+        tl.store(out_ptr + row * stride + cols, tl.exp(x - m) / s, mask=cols < N)

@@ -360,6 +360,19 @@ def _block_program_cases(dev):
         blk[:rows.shape[0], :24] = rows
         exp_cmin[pid, :24] = blk.min(dim=0).values[:24]
     out.append(("tile_colmin", cmin.cpu().reshape(4, 32), exp_cmin, 0))
+    # loops that carry block values (device-side loops of the block-program kernel)
+    xr = torch.randn(7, 1000, device=dev)
+    rs = torch.zeros(7, device=dev)
+    rm = torch.zeros(7, device=dev)
+    K.row_stats_kernel[(7,)](xr, rs, rm, 1000, 900, BLOCK=256)
+    out.append(("row_stats_sum", rs.cpu(), xr[:, :900].sum(dim=1).cpu(), 1e-4))
+    out.append(("row_stats_max", rm.cpu(), xr[:, :900].max(dim=1).values.cpu(), 0))
+    xs = torch.randn(6, 2500, device=dev)
+    os_ = torch.full((6, 2500), -1.0, device=dev)
+    K.wide_softmax_kernel[(6,)](os_, xs, 2500, 2400, BLOCK=512)
+    exp = torch.full((6, 2500), -1.0)
+    exp[:, :2400] = torch.softmax(xs[:, :2400].cpu(), dim=1)
+    out.append(("wide_softmax", os_.cpu(), exp, 1e-5))
     return out
 
 
@@ -371,7 +384,7 @@ def test_block_programs_on_host_stand_in():
             assert torch.equal(got, exp), name
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
-    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 4
+    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 6
 
 
 # ------------------------------------------------------------------ a spread of elementwise ops

@@ -179,6 +179,20 @@ def is_affine_in_pid(p: Poly) -> bool:
     return True
 
 
+def _is_affine_in_its(p: Poly) -> bool:
+    """Every loop counter appears at most linearly, never multiplied by another counter or inside a function."""
+    for m in p.terms:
+        deg = 0
+        for a in m:
+            if a[0] == "it":
+                deg += 1
+            elif a[0] == "fn" and (a[2].depends_on(("it",)) or a[3].depends_on(("it",))):
+                return False
+        if deg > 1:
+            return False
+    return True
+
+
 def _float_bits(v: float, elem: str) -> int:
     if elem == "f32":
         return struct.unpack("<I", struct.pack("<f", v))[0]
@@ -453,7 +467,7 @@ class _EwLowering:
 
 def _reads(o):
     opc = o[0]
-    if opc in ("load", "const", "iota"):
+    if opc in ("load", "const", "iota", "loop_begin", "loop_end"):
         return []
     if opc == "store":
         return [o[4]]
@@ -577,7 +591,7 @@ class ElementwisePlan(Plan):
         run(self.p["tree"])
         return out
 
-    def _evaluate(self, seg, args, env):
+    def _evaluate(self, seg, args, env, trips=None):
         space = seg["space"]
         rank = len(space)
         n = len(seg["accs"])
@@ -627,6 +641,18 @@ class ElementwisePlan(Plan):
                 ww.scale = int(w["scale"].evaluate(e0))
                 if ww.modulus <= 0:
                     raise UnsupportedTTIR("wrap-around access with a non-positive modulus")
+            # block programs: advance per iteration of each enclosing loop (slot = nesting depth)
+            for lid, depth in (seg.get("loop_depth") or {}).items():
+                lid = int(lid)
+                if not (d["offset"].depends_on(("it",)) or any(m and m[0].depends_on(("it",)) for m in d["mask"])):
+                    continue
+                env.base[("it", lid)] = 1
+                a.offset_loop[depth] += int(d["offset"].evaluate(env.at())) - off0
+                for k in range(rank):
+                    m = d["mask"][k]
+                    if m is not None:
+                        a.mask_start_loop[k][depth] += int(m[0].evaluate(env.at())) - a.mask_start0[k]
+                env.base[("it", lid)] = 0
             arg_of.append(d.get("arg"))
         ops = (rt.Op * len(seg["ops"]))()
         for k, o in enumerate(seg["ops"]):
@@ -635,7 +661,10 @@ class ElementwisePlan(Plan):
             x.opcode = rt.OPCODES[opc]
             x.type = rt.DTYPES[dt]
             x.dst, x.a, x.b, x.c = max(dst, 0), ra, rb, rc
-            if isinstance(imm, str):
+            if isinstance(imm, (list, tuple)) and imm[0] == "trip":
+                q = trips[str(imm[1])]
+                x.imm = max(0, int(q.evaluate(e0)))
+            elif isinstance(imm, str):
                 x.imm = rt.OPCODES[imm]  # combiner of a reduction
             elif isinstance(imm, (list, tuple)):
                 if imm[0] == "poly":
@@ -677,14 +706,17 @@ class _DimUnion:
         self.parent[max(ra, rb)] = min(ra, rb)
 
 
-def _discover_space(stores: List[Access]):
+def _discover_space(stores: List[Access], loops: Dict[int, Loop] = None):
     """Symbolic dims of every node reachable from the stores.  A reduction introduces a dim its result
-    does not have; a node reached along two paths has one set of dims (they are unified).
-    Returns (ordered space dims, {node id: tuple of space positions})."""
+    does not have; a node reached along two paths has one set of dims (they are unified); a
+    loop-carried value, its initial value, its yielded value and the loop's result share their dims.
+    Returns (space sizes, {node id: tuple of space positions}, {reduce node id: reduced space position})."""
     uf = _DimUnion()
+    loops = loops or {}
     node_dims: Dict[int, tuple] = {}
     order: List[tuple] = []  # (a, b): dim a precedes dim b in some node
     red_dim: Dict[int, int] = {}
+    carried: Dict[tuple, tuple] = {}
 
     def visit(n: Node, dims: tuple):
         if n.id in node_dims:
@@ -705,8 +737,23 @@ def _discover_space(stores: List[Access]):
             src = n.args[0]
             d = red_dim.setdefault(n.id, uf.fresh(src.shape[ax]))
             visit(src, dims[:ax] + (d,) + dims[ax:])
-        elif n.op in ("dot", "iter_arg", "loop_result"):
-            raise UnsupportedTTIR(f"block program: operation {n.op}")
+        elif n.op in ("iter_arg", "loop_result"):
+            key = (n.attr("loop"), n.attr("k"))
+            if key in carried:
+                for a, b in zip(carried[key], dims):
+                    uf.union(a, b)
+                return
+            carried[key] = dims
+            loop = loops.get(key[0])
+            if loop is None:
+                raise UnsupportedTTIR("block program: loop-carried value of an unknown loop")
+            init, yld = loop.inits[key[1]], loop.yields[key[1]]
+            if not isinstance(init, TData) or not isinstance(yld, TData):
+                raise UnsupportedTTIR("block program: loop-carried value is not block data")
+            visit(init.node, dims)
+            visit(yld.node, dims)
+        elif n.op == "dot":
+            raise UnsupportedTTIR("block program: operation dot")
         else:
             for a in n.args:
                 if isinstance(a, Node):
@@ -749,8 +796,27 @@ class _BpLowering(_EwLowering):
         self.acc_mask: Dict[int, int] = {}
         self.red_pos = red_pos
 
-    def acc_for(self, kind, elem, shape, dimmap, *a, **kw):
-        ai = super().acc_for(kind, elem, shape, dimmap, *a, **kw)
+    def acc_for(self, kind, elem, shape, dimmap, offset, strides, mask, other, arg=None, wrapped=()):
+        # a mask bound that moves with a loop counter (`k < K - it*BLOCK`) is the same mask with the
+        # counter moved into the start (`it*BLOCK + k < K`): dims = max(min(s+size,b),s)-s is shift-invariant
+        if mask:
+            dims = []
+            for dd in mask["dims"]:
+                nd = []
+                for st, bnd in dd:
+                    var = Poly({m: c for m, c in bnd.terms.items() if any(a[0] == "it" for a in m)})
+                    nd.append([st - var, bnd - var])
+                dims.append(nd)
+            mask = {"dims": dims, "conds": mask["conds"]}
+        ai = super().acc_for(kind, elem, shape, dimmap, offset, strides, mask, other, arg, wrapped)
+        d = self.accs[ai]
+        for q in d["strides"] + [sb[1] for sb in d["mask"] if sb] + d["conds"] + \
+                [x for w in d["wrap"] for x in w.values() if isinstance(x, Poly)]:
+            if q.depends_on(("it",)):
+                raise UnsupportedTTIR("block program: stride, mask bound or wrap-around term depends on a loop counter")
+        for q in [d["offset"]] + [sb[0] for sb in d["mask"] if sb]:
+            if not _is_affine_in_its(q):
+                raise UnsupportedTTIR("block program: access offset is not affine in the loop counters")
         m = 0
         for d, it_d in enumerate(dimmap):
             if shape[d] > 1:
@@ -773,6 +839,11 @@ class _BpLowering(_EwLowering):
         return dst
 
     def _value(self, n: Node, dimmap):
+        if n.op in ("iter_arg", "loop_result"):
+            key = (n.attr("loop"), n.attr("k"))
+            if key not in self.carried_reg:
+                raise UnsupportedTTIR("block program: loop-carried value used outside its loop's scope")
+            return self.carried_reg[key]
         if n.op == "reduce":
             ax, comb = n.attr("axis"), n.attr("comb")
             if comb not in ("addf", "mulf", "maxnumf", "minnumf", "maximumf", "minimumf", "addi", "muli", "maxsi",
@@ -783,30 +854,99 @@ class _BpLowering(_EwLowering):
             return self.emit("reduce", n.dtype, a=src, imm=comb, imm2=d, mask=self.vmask[src] & ~(1 << d))
         return super()._value(n, dimmap)
 
-    def lower(self, stores, maps):
-        for acc in stores:
-            dimmap = maps[("store", id(acc))]
-            v = self.value(acc.value, dimmap)
-            ai = self.acc_for("store", acc.elem, acc.shape, dimmap, acc.offset, acc.strides,
-                              _mask_json(acc.mask, acc.shape), None, acc.arg, acc.wrapped)
-            self.ops.append(["store", acc.elem, -1, ai, v, 0, self.acc_mask[ai], 0])
+    def lower(self, effects, maps, loops):
+        self.carried_reg: Dict[tuple, int] = {}
+        self.loop_spans: List[tuple] = []   # (first op index, last op index) of every loop
+        self.loop_trips: Dict[int, Poly] = {}
+        self.loop_depth: Dict[int, int] = {}
+        self._walk(effects, maps, loops, 0)
         return self.allocate_masked()
+
+    def _walk(self, effects, maps, loops, depth):
+        for kind, e in effects:
+            if kind == "store":
+                dimmap = maps[("store", id(e))]
+                v = self.value(e.value, dimmap)
+                ai = self.acc_for("store", e.elem, e.shape, dimmap, e.offset, e.strides,
+                                  _mask_json(e.mask, e.shape), None, e.arg, e.wrapped)
+                self.ops.append(["store", e.elem, -1, ai, v, 0, self.acc_mask[ai], 0])
+                continue
+            loop: Loop = e
+            if depth >= 4:
+                raise UnsupportedTTIR("block program: loops nested more than four deep")
+            if loop.trip.depends_on(("pid", "it", "carry")):
+                raise UnsupportedTTIR("block program: loop trip count depends on program_id or on an outer loop")
+            # carried block values that something reads (dead ones have no dims and need no register)
+            data_k = [k for k, init in enumerate(loop.inits) if isinstance(init, TData) and init.node.id in maps
+                      and isinstance(loop.yields[k], TData) and loop.yields[k].node.id in maps]
+            # carried registers: written before the loop (initial value) and at the end of every iteration
+            for k in data_k:
+                init = loop.inits[k].node
+                dimmap = maps[init.id]
+                src = self.value(init, dimmap)
+                r = self.emit("mov", init.dtype, a=src, mask=self._mask_of(init, dimmap))
+                self.carried_reg[(loop.id, k)] = r
+            begin = len(self.ops)
+            self.ops.append(["loop_begin", "i32", -1, depth, 0, 0, ("trip", loop.id), 0])
+            self.loop_trips[loop.id] = loop.trip
+            self.loop_depth[loop.id] = depth
+            self._walk(loop.effects, maps, loops, depth + 1)
+            new_vals = []
+            for k in data_k:
+                y = loop.yields[k].node
+                v = self.value(y, maps[y.id])
+                # through a temporary, so that carried values that exchange places are not clobbered
+                new_vals.append(self.emit("mov", y.dtype, a=v, mask=self.vmask[self.carried_reg[(loop.id, k)]])
+                                if len(data_k) > 1 else v)
+            for k, v in zip(data_k, new_vals):
+                r = self.carried_reg[(loop.id, k)]
+                self.ops.append(["mov", loop.yields[k].node.dtype, r, v, 0, 0, 0, 0])
+            self.ops.append(["loop_end", "i32", -1, depth, 0, 0, 0, 0])
+            self.ops[begin][4] = len(self.ops)  # index of the op after the loop end
+            self.loop_spans.append((begin, len(self.ops) - 1))
+
+    def _mask_of(self, n: Node, dimmap):
+        m = 0
+        for d, it_d in enumerate(dimmap):
+            if n.shape[d] > 1:
+                m |= 1 << it_d
+        return m
 
     def allocate_masked(self):
         """Physical registers are shared-memory regions; a region is reused only by values of the same mask."""
         ops = self.ops
         last_use: Dict[int, int] = {}
+        first_def: Dict[int, int] = {}
         for i, o in enumerate(ops):
             for r in _reads(o):
                 last_use[r] = i
+            if o[0] not in ("store", "loop_begin", "loop_end"):
+                first_def.setdefault(o[2], i)
+        # a value defined before a loop and read inside it is read again in every iteration
+        for b, e in getattr(self, "loop_spans", []):
+            for r, d in first_def.items():
+                if d < b and b <= last_use.get(r, -1) <= e:
+                    last_use[r] = e
         free: Dict[int, List[int]] = {}
         masks: List[int] = []
         phys: Dict[int, int] = {}
         out = []
         for i, o in enumerate(ops):
             o = list(o)
+            if o[0] in ("loop_begin", "loop_end"):
+                out.append(o)
+                continue
             reads = _reads(o)
             mapped = {r: phys[r] for r in reads}
+            if o[0] != "store" and o[2] in phys:
+                # second definition of a loop-carried register: same region
+                o[2] = phys[o[2]]
+                _remap(o, mapped)
+                for r in set(reads):
+                    if last_use[r] == i and r in phys:
+                        free.setdefault(self.vmask[r], []).append(phys.pop(r))
+                out.append(o)
+                continue
             if o[0] != "store":
                 m = self.vmask[o[2]]
                 # an elementwise result may overwrite an operand of the same mask that dies here; a
@@ -846,28 +986,35 @@ class BlockProgramPlan(Plan):
 
     @staticmethod
     def build(kernel: Kernel, an: Analyzer) -> "BlockProgramPlan":
-        stores = []
-        for kind, e in kernel.effects:
-            if kind != "store":
-                raise UnsupportedTTIR("block_program family: kernel contains a loop")
-            stores.append(e)
+        stores: List[Access] = []
+
+        def collect(effects):
+            for kind, e in effects:
+                if kind == "store":
+                    stores.append(e)
+                else:
+                    collect(e.effects)
+        collect(kernel.effects)
         if not stores:
             raise UnsupportedTTIR("kernel stores nothing")
-        sizes, maps, red_pos = _discover_space(stores)
-        if not red_pos:
-            raise UnsupportedTTIR("block_program family: no reduction in the body")
+        sizes, maps, red_pos = _discover_space(stores, kernel.loops)
         if not sizes:
             sizes = [1]
         if len(sizes) > rt.TSB_MAX_RANK:
             raise UnsupportedTTIR(f"block program: iteration space of rank {len(sizes)}")
         low = _BpLowering(kernel, an, sizes, red_pos)
-        ops, masks = low.lower(stores, maps)
-        return BlockProgramPlan(kernel.name, {"seg": {"space": list(sizes), "accs": low.accs, "ops": ops},
-                                              "reg_masks": masks})
+        ops, masks = low.lower(kernel.effects, maps, kernel.loops)
+        return BlockProgramPlan(kernel.name, {"seg": {"space": list(sizes), "accs": low.accs, "ops": ops,
+                                                      "loops": sorted(low.loop_trips),
+                                                      "loop_depth": {str(k): v for k, v in low.loop_depth.items()}},
+                                              "reg_masks": masks, "trips": {str(k): v for k, v in low.loop_trips.items()}})
 
     def launch(self, args, grid, pid_lo, pid_hi, stream):
         def compute():
-            accs, ops, arg_of = ElementwisePlan._evaluate(self, self.p["seg"], args, LaunchEnv(args.scalars, grid))
+            env = LaunchEnv(args.scalars, grid)
+            for lid in self.p["seg"].get("loops", []):
+                env.base[("it", lid)] = 0
+            accs, ops, arg_of = ElementwisePlan._evaluate(self, self.p["seg"], args, env, self.p.get("trips"))
             masks = (ctypes.c_int32 * len(self.p["reg_masks"]))(*self.p["reg_masks"])
             return accs, ops, arg_of, masks
         accs, ops, arg_of, masks = self.memo(args, grid, compute)

@@ -116,13 +116,27 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
     long long px, py, pz;
     split_pid(P.grid, P.order, prog, px, py, pz);
-    for (int k = 0; k < P.n_ops; ++k) {
-      __syncthreads();  // every op may read what other threads wrote in the previous one
+    int it[TSB_MAX_LOOPS] = {0, 0, 0, 0}, trip[TSB_MAX_LOOPS] = {0, 0, 0, 0}, begin[TSB_MAX_LOOPS] = {0, 0, 0, 0};
+    for (int k = 0; k < P.n_ops;) {
       const tsb_op &op = P.ops[k];
+      // loops: uniform control flow, the same for every thread of the CTA
+      if (op.opcode == TSB_OP_LOOP_BEGIN) {
+        it[op.a] = 0;
+        trip[op.a] = (int)op.imm;
+        begin[op.a] = k + 1;
+        k = trip[op.a] > 0 ? k + 1 : op.b;
+        continue;
+      }
+      if (op.opcode == TSB_OP_LOOP_END) {
+        k = (++it[op.a] < trip[op.a]) ? begin[op.a] : k + 1;
+        continue;
+      }
+      ++k;
+      __syncthreads();  // every op may read what other threads wrote in the previous one
       if (op.opcode == TSB_OP_LOAD) {
         const DAcc &A = P.acc[op.a];
         ProgState st;
-        program_state(A, P.size, px, py, pz, st);
+        program_state_loops(A, P.size, px, py, pz, it, st);
         const int m = P.reg_mask[op.dst];
         unsigned *dst = bp_smem + P.reg_off[op.dst];
         if ((m & 4) && (P.size[2] & 3) == 0) {
@@ -157,7 +171,7 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
       } else if (op.opcode == TSB_OP_STORE) {
         const DAcc &A = P.acc[op.a];
         ProgState st;
-        program_state(A, P.size, px, py, pz, st);
+        program_state_loops(A, P.size, px, py, pz, it, st);
         const int m = (int)op.imm;  // dims the store extends along
         const int ms = P.reg_mask[op.b];
         const unsigned *src = bp_smem + P.reg_off[op.b];
@@ -303,6 +317,13 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
     if (o.opcode == TSB_OP_REDUCE) {
       if (o.imm2 >= (unsigned)rank) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d reduces dim %u of rank %d", k, o.imm2, rank);
       o.imm2 += 3 - rank;
+    }
+    if (o.opcode == TSB_OP_LOOP_BEGIN || o.opcode == TSB_OP_LOOP_END) {
+      if (o.a < 0 || o.a >= TSB_MAX_LOOPS) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d uses loop slot %d", k, o.a);
+      if (o.opcode == TSB_OP_LOOP_BEGIN && (o.b <= k || o.b > n_ops || ops[o.b - 1].opcode != TSB_OP_LOOP_END || ops[o.b - 1].a != o.a))
+        return fail(TSB_ERR_INVALID, "tsb_block_program: op %d does not name its matching loop end", k);
+      P.ops[k] = o;
+      continue;
     }
     const int regs[4] = {o.opcode == TSB_OP_STORE ? 0 : o.dst, mem || o.opcode == TSB_OP_CONST ? 0 : o.a,
                          o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_CONST ? 0 : o.b, o.c};

@@ -15,6 +15,8 @@ struct DAcc {
   long long stride[3];
   long long mstart0[3];
   long long mstart_pid[3][3];
+  long long off_loop[TSB_MAX_LOOPS];        // block programs: advance per iteration of loop slot l
+  long long mstart_loop[3][TSB_MAX_LOOPS];
   long long bound[3];
   int masked;     // bit d set: dim d carries a mask
   int dtype;
@@ -290,6 +292,34 @@ __device__ __forceinline__ void program_state(const DAcc &A, const int size[3], 
   }
 }
 
+// program_state inside loops: iteration it[l] of loop slot l shifts the offset and the mask starts
+__device__ __forceinline__ void program_state_loops(const DAcc &A, const int size[3], long long px, long long py,
+                                                    long long pz, const int it[TSB_MAX_LOOPS], ProgState &s) {
+  long long extra = 0, mextra[3] = {0, 0, 0};
+#pragma unroll
+  for (int l = 0; l < TSB_MAX_LOOPS; ++l) {
+    extra += A.off_loop[l] * it[l];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) mextra[d] += A.mstart_loop[d][l] * it[l];
+  }
+  s.off = A.off0 + A.off_pid[0] * px + A.off_pid[1] * py + A.off_pid[2] * pz + extra;
+  for (int w = 0; w < A.n_wrap; ++w)
+    s.woff[w] = A.wrap[w].off0 + A.wrap[w].off_pid[0] * px + A.wrap[w].off_pid[1] * py + A.wrap[w].off_pid[2] * pz;
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    int dim = size[d];
+    if (A.masked & (1 << d)) {
+      long long st = A.mstart0[d] + A.mstart_pid[d][0] * px + A.mstart_pid[d][1] * py +
+                     A.mstart_pid[d][2] * pz + mextra[d];
+      long long en = st + size[d];
+      long long m = en < A.bound[d] ? en : A.bound[d];
+      m = m > st ? m : st;
+      dim = (int)(m - st);
+    }
+    s.dim[d] = dim;
+  }
+}
+
 template <int VEC>
 __device__ __forceinline__ void load_vec(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
                                          unsigned (&out)[VEC]) {
@@ -522,6 +552,7 @@ inline int convert_access(const tsb_access *acc, int a, int rank, const int size
   d.esize = es;
   d.off0 = s.offset0;
   for (int k = 0; k < 3; ++k) d.off_pid[k] = s.offset_pid[k];
+  for (int l = 0; l < TSB_MAX_LOOPS; ++l) d.off_loop[l] = s.offset_loop[l];
   d.has_other = s.has_other;
   d.other = other_to_reg(s.other_bits, s.dtype);
   for (int k = 0; k < 3; ++k) { d.stride[k] = 0; d.bound[k] = 0; }
@@ -535,6 +566,7 @@ inline int convert_access(const tsb_access *acc, int a, int rank, const int size
       d.mstart0[o] = s.mask_start0[k];
       for (int j = 0; j < 3; ++j) d.mstart_pid[o][j] = s.mask_start_pid[k][j];
       d.bound[o] = s.mask_bound[k];
+      for (int l = 0; l < TSB_MAX_LOOPS; ++l) d.mstart_loop[o][l] = s.mask_start_loop[k][l];
     }
   }
   if (s.n_wrap < 0 || s.n_wrap > 2) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has %d wrap terms", a, s.n_wrap);
