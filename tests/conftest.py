@@ -23,7 +23,6 @@ def oracle_lib():
 @pytest.fixture(scope="session")
 def tsb_driver():
     """Activates the B200 driver for Triton (GPU tests)."""
-    import triton
     import triton_shared_b200
     drv = triton_shared_b200.activate()
     return drv

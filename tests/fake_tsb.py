@@ -10,15 +10,12 @@ oracle with the arguments they were given.  Nothing here is reachable from the
 product package.
 """
 import ctypes
-import struct
 
 import numpy as np
 
 import oracle
 from triton_shared_b200.backend import runtime as rt
 
-_NP = {0: np.float32, 1: np.float16, 2: np.uint16, 3: np.int32, 4: np.int16, 5: np.int8, 6: np.uint8,
-       9: np.uint32, 10: np.uint16, 11: np.uint8}
 _SIZE = {0: 4, 1: 2, 2: 2, 3: 4, 4: 2, 5: 1, 6: 1, 9: 4, 10: 2, 11: 1}
 _OPNAME = {v: k for k, v in rt.OPCODES.items()}
 _CMPF = {v: k for k, v in rt.CMPF.items()}

@@ -9,7 +9,6 @@ identical to tsb_reduce_rows given ordinary scratch; it also checks that an over
 refused rather than served by a hidden allocation.  It runs last so that a failure here cannot
 mask any other test.
 """
-import ctypes
 
 import pytest
 import torch

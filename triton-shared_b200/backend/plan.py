@@ -121,7 +121,6 @@ def dec(o):
 # --------------------------------------------------------------------------
 # launch-time helpers
 
-_PID = [("pid", 0), ("pid", 1), ("pid", 2)]
 
 
 class LaunchEnv:
