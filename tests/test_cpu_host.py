@@ -424,3 +424,23 @@ def test_mixed_ops_on_host_stand_in():
             assert torch.equal(got, exp), name
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
+
+
+def test_launch_hooks_are_called():
+    """launch_enter_hook / launch_exit_hook around every launch, as the reference launcher does
+    (backend/driver.py:197-218 there)."""
+    from triton import knobs
+    seen = []
+    old_enter, old_exit = knobs.runtime.launch_enter_hook, knobs.runtime.launch_exit_hook
+    knobs.runtime.launch_enter_hook = lambda md: seen.append(("enter", md.get()["name"] if hasattr(md, "get") else md))
+    knobs.runtime.launch_exit_hook = lambda md: seen.append(("exit", md.get()["name"] if hasattr(md, "get") else md))
+    try:
+        x = torch.arange(0, 64, dtype=torch.float32)
+        y = torch.ones(64)
+        out = torch.zeros(64)
+        with fake_device():
+            K.add_kernel[(1,)](x, y, out, 64, BLOCK_SIZE=64)
+    finally:
+        knobs.runtime.launch_enter_hook, knobs.runtime.launch_exit_hook = old_enter, old_exit
+    assert [s[0] for s in seen] == ["enter", "exit"] and seen[0][1] == "add_kernel"
+    assert torch.equal(out, x + 1)
