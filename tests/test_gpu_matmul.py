@@ -126,3 +126,14 @@ def test_partitioned_matmul(drv):
             K.matmul_kernel[grid](a, b, parts, 1024, 1024, 512, 512, 1, 1024, 1, 1024, 1,
                                   BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
     assert torch.equal(full, parts)
+
+
+@pytest.mark.parametrize("BN,BK", [(128, 128), (64, 64), (256, 128)])
+def test_matmul_other_block_shapes(drv, oracle_lib, BN, BK):
+    """BLOCK_K = 128 (two 64-wide pipeline stages per K step) and BLOCK_N = 64 (not splittable between
+    two CTAs for a [K,N] B: the paired entry point refuses and the one-CTA kernel takes the launch)."""
+    torch.manual_seed(3)
+    a = (2 * torch.rand(384, 512) - 1).bfloat16().cuda()
+    b = (2 * torch.rand(512, 640) - 1).bfloat16().cuda()
+    c = _run(K.matmul_kernel, a, b, 128, BN, BK)
+    _check(c, a, b, oracle_lib, 128, BN, BK)
