@@ -170,10 +170,20 @@ enum tsb_cmp {
   TSB_CMPI_ULT, TSB_CMPI_ULE, TSB_CMPI_UGT, TSB_CMPI_UGE
 };
 
+/*
+ * tsb_elementwise only: besides a register number, an operand (a, b, c, or the b of a store) may be
+ *   TSB_REG_ACC  the result of the op executed just before this one (kept in hardware registers), or
+ *   TSB_REG_IMM  the 32-bit pattern in imm2 (not for TSB_OP_CAST, which uses imm2 itself);
+ * and dst may be TSB_REG_ACC when the only consumer of the result is the next op.  Bodies written
+ * with plain register numbers only stay valid.
+ */
+#define TSB_REG_ACC (-1)
+#define TSB_REG_IMM (-2)
+
 typedef struct tsb_op {
   int32_t opcode; /* enum tsb_opcode */
   int32_t type;   /* enum tsb_dtype of the result (operand type for compares) */
-  int32_t dst, a, b, c; /* register numbers < TSB_NUM_REGS, or an access index */
+  int32_t dst, a, b, c; /* register numbers < TSB_NUM_REGS (or TSB_REG_ACC / TSB_REG_IMM), or an access index */
   uint32_t imm;
   uint32_t imm2;
 } tsb_op;

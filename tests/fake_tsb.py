@@ -74,6 +74,27 @@ class HostMemory:
         return self._status.tolist()
 
 
+class _Regs(dict):
+    """Register file of the elementwise VM: numbers, TSB_REG_ACC (-1, the previous result) and
+    TSB_REG_IMM (-2, the op's imm2)."""
+
+    def __init__(self, lanes):
+        super().__init__()
+        self.lanes, self.acc, self.imm = lanes, np.zeros(lanes, dtype=np.uint32), np.uint32(0)
+
+    def __getitem__(self, r):
+        if r == -1:
+            return self.acc
+        if r == -2:
+            return np.full(self.lanes, self.imm, dtype=np.uint32)
+        return dict.__getitem__(self, r)
+
+    def write(self, r, v):
+        self.acc = v
+        if r >= 0:
+            self[r] = v
+
+
 class FakeLib:
     """Same entry points as libtsb200.so, executing on host memory."""
 
@@ -101,25 +122,27 @@ class FakeLib:
         for prog in range(pid_lo, pid_hi):
             p = (prog % g[0], (prog // g[0]) % g[1], prog // (g[0] * g[1]))
             state = [self._acc_state(accs[a], p, rank, sizes, idx, lanes) for a in range(n_acc)]
-            regs = {}
+            regs = _Regs(lanes)
             for k in range(n_ops):
                 o = ops[k]
                 name = _OPNAME[o.opcode]
+                regs.imm = np.uint32(o.imm2)
                 if name == "load":
                     A = accs[o.a]
                     elem, valid = state[o.a]
                     if A.is_store == 2:
-                        regs[o.dst] = valid.astype(np.uint32)
+                        v = valid.astype(np.uint32)
                     elif A.is_store == 3:
-                        regs[o.dst] = elem.astype(np.int64).astype(np.uint32)
+                        v = elem.astype(np.int64).astype(np.uint32)
                     else:
-                        regs[o.dst] = self._load(A, elem, valid)
+                        v = self._load(A, elem, valid)
+                    regs.write(o.dst, v)
                 elif name == "store":
                     A = accs[o.a]
                     elem, valid = state[o.a]
                     self._store(A, elem, valid, regs[o.b])
                 else:
-                    regs[o.dst] = self._alu(name, o, regs, lanes)
+                    regs.write(o.dst, self._alu(name, o, regs, lanes))
         return 0
 
     @staticmethod

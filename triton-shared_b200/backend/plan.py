@@ -428,34 +428,69 @@ class _EwLowering:
         return self.allocate()
 
     def allocate(self):
-        """Hoist loads, then map virtual registers onto TSB_NUM_REGS physical ones."""
+        """Hoist loads; turn constants into immediate operands; keep a value that only the next op
+        reads in the accumulator; map what remains onto TSB_NUM_REGS shared-memory registers."""
+        ACC, IMM = rt.REG_ACC, rt.REG_IMM
         loads = [o for o in self.ops if o[0] == "load"]
         rest = [o for o in self.ops if o[0] != "load"]
-        ops = loads + rest
+        ops = [list(o) for o in loads + rest]
+        slots = {"store": (4,), "select": (3, 4, 5), "fma": (3, 4, 5)}
+
+        def read_slots(o):
+            if o[0] in ("load", "const"):
+                return ()
+            if o[0] in slots:
+                return slots[o[0]]
+            return (3,) if len(_reads(o)) == 1 else (3, 4)
+
+        # 1. constants become immediates (one per op; casts use imm2 themselves; stores need a value)
+        consts = {o[2]: o for o in ops if o[0] == "const"}
+        marks: Dict[tuple, int] = {}  # (op index, slot) -> ACC / IMM
+        for i, o in enumerate(ops):
+            if o[0] in ("store", "cast", "load", "const"):
+                continue
+            for sl in read_slots(o):
+                if o[sl] in consts and not any(marks.get((i, s2)) == IMM for s2 in read_slots(o)):
+                    marks[(i, sl)] = IMM
+                    o[7] = consts[o[sl]][6]
+        still_used = {o[sl] for i, o in enumerate(ops) for sl in read_slots(o) if (i, sl) not in marks}
+        keep = [i for i, o in enumerate(ops) if not (o[0] == "const" and o[2] not in still_used)]
+        remap_idx = {old: new for new, old in enumerate(keep)}
+        marks = {(remap_idx[i], sl): m for (i, sl), m in marks.items() if i in remap_idx}
+        ops = [ops[i] for i in keep]
+        # 2. the previous op's result is read from the accumulator
+        prev = None
+        for i, o in enumerate(ops):
+            for sl in read_slots(o):
+                if (i, sl) not in marks and prev is not None and o[sl] == prev:
+                    marks[(i, sl)] = ACC
+            prev = o[2] if o[0] != "store" else None
+        # 3. registers for every value that is read in some other way
         last_use: Dict[int, int] = {}
         for i, o in enumerate(ops):
-            for r in _reads(o):
-                last_use[r] = i
+            for sl in read_slots(o):
+                if (i, sl) not in marks:
+                    last_use[o[sl]] = i
         free = list(range(rt.TSB_NUM_REGS - 1, -1, -1))
         phys: Dict[int, int] = {}
         out = []
         for i, o in enumerate(ops):
-            o = list(o)
-            reads = _reads(o)
-            mapped = {r: phys[r] for r in reads}
-            for r in set(reads):
-                if last_use[r] == i:
-                    free.append(phys.pop(r))
+            reads = [(sl, o[sl]) for sl in read_slots(o) if (i, sl) not in marks]
+            mapped = {v: phys[v] for _, v in reads}
+            for v in {v for _, v in reads}:
+                if last_use[v] == i:
+                    free.append(phys.pop(v))
             if o[0] != "store":
-                if not free:
-                    raise UnsupportedTTIR(f"elementwise body needs more than {rt.TSB_NUM_REGS} live block values")
-                if o[2] not in last_use:
-                    dst_phys = free[-1]  # dead value: still needs a slot for this op
+                if o[2] in last_use:
+                    if not free:
+                        raise UnsupportedTTIR(f"elementwise body needs more than {rt.TSB_NUM_REGS} live block values")
+                    phys[o[2]] = free.pop()
+                    o[2] = phys[o[2]]
                 else:
-                    dst_phys = free.pop()
-                    phys[o[2]] = dst_phys
-                o[2] = dst_phys
-            _remap(o, mapped)
+                    o[2] = ACC  # only the next op (or nothing) reads it
+            for sl in read_slots(o):
+                m = marks.get((i, sl))
+                o[sl] = m if m is not None else mapped[o[sl]]
             out.append(o)
         if len(out) > rt.TSB_MAX_OPS:
             raise UnsupportedTTIR(f"elementwise body of {len(out)} ops exceeds {rt.TSB_MAX_OPS}")
@@ -659,7 +694,7 @@ class ElementwisePlan(Plan):
             x = ops[k]
             x.opcode = rt.OPCODES[opc]
             x.type = rt.DTYPES[dt]
-            x.dst, x.a, x.b, x.c = max(dst, 0), ra, rb, rc
+            x.dst, x.a, x.b, x.c = (dst if opc != "store" else 0), ra, rb, rc
             if isinstance(imm, (list, tuple)) and imm[0] == "trip":
                 q = trips[str(imm[1])]
                 x.imm = max(0, int(q.evaluate(e0)))
@@ -672,7 +707,13 @@ class ElementwisePlan(Plan):
                     x.imm = struct.unpack("<I", struct.pack("<f", float(args.floats[imm[1]])))[0]
             else:
                 x.imm = imm
-            x.imm2 = imm2
+            if isinstance(imm2, (list, tuple)):  # an immediate operand that is a launch-time scalar
+                if imm2[0] == "poly":
+                    x.imm2 = int(imm2[1].evaluate(e0)) & 0xffffffff
+                else:
+                    x.imm2 = struct.unpack("<I", struct.pack("<f", float(args.floats[imm2[1]])))[0]
+            else:
+                x.imm2 = imm2
         return accs, ops, arg_of
 
 

@@ -65,54 +65,89 @@ struct VmRegs {
   }
 };
 
-template <int OPC, int VEC, int U>
-__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R) {
+// All sub-items of one operand: a shared-memory register, the accumulator (the previous op's
+// result, held in hardware registers), or an immediate.  The source is decoded once per op.
+template <int VEC, int U>
+__device__ __forceinline__ void vm_fetch(const tsb_op &op, int which, const VmRegs<VEC, U> &R,
+                                         const unsigned (&acc)[U][VEC], unsigned (&v)[U][VEC]) {
+  if (which == TSB_REG_ACC) {
 #pragma unroll
-  for (int u = 0; u < U; ++u) {
-    unsigned a[VEC], b[VEC], c[VEC], r[VEC];
-    R.get(op.a, u, a);
-    if (alu_arity<OPC>() >= 2) R.get(op.b, u, b);
-    if (alu_arity<OPC>() >= 3) R.get(op.c, u, c);
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[u][k] = acc[u][k];
+  } else if (which == TSB_REG_IMM) {
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[u][k] = op.imm2;
+  } else {
+#pragma unroll
+    for (int u = 0; u < U; ++u) R.get(which, u, v[u]);
+  }
+}
+
+template <int OPC, int VEC, int U>
+__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R, unsigned (&acc)[U][VEC]) {
+  unsigned a[U][VEC], b[U][VEC], c[U][VEC];
+  vm_fetch<VEC, U>(op, op.a, R, acc, a);
+  if (alu_arity<OPC>() >= 2) vm_fetch<VEC, U>(op, op.b, R, acc, b);
+  if (alu_arity<OPC>() >= 3) vm_fetch<VEC, U>(op, op.c, R, acc, c);
+#pragma unroll
+  for (int u = 0; u < U; ++u)
 #pragma unroll
     for (int v = 0; v < VEC; ++v)
-      r[v] = alu_op<OPC>(op, a[v], alu_arity<OPC>() >= 2 ? b[v] : 0u, alu_arity<OPC>() >= 3 ? c[v] : 0u);
-    R.put(op.dst, u, r);
+      acc[u][v] = alu_op<OPC, false>(op, a[u][v], alu_arity<OPC>() >= 2 ? b[u][v] : 0u,
+                                     alu_arity<OPC>() >= 3 ? c[u][v] : 0u);
+  if (alu_rounds<OPC>() && op.type != TSB_F32) {  // 16-bit float ops: one decision per op, not per lane
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[u][v] = __float_as_uint(round_to(__uint_as_float(acc[u][v]), op.type));
+  }
+  if (op.dst >= 0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) R.put(op.dst, u, acc[u]);
   }
 }
 
 // ld(access, u, regs) / st(access, u, regs) address sub-item u; inactive sub-items load zeros and store nothing
 template <int VEC, int U, typename LoadFn, typename StoreFn>
 __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC, U> R, LoadFn ld, StoreFn st) {
+  unsigned acc[U][VEC];
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[u][v] = 0u;
   for (int k = 0; k < n_ops; ++k) {
     const tsb_op &op = ops[k];
     switch (op.opcode) {
-      case TSB_OP_LOAD: {
-        unsigned t[U][VEC];
+      case TSB_OP_LOAD:
 #pragma unroll
-        for (int u = 0; u < U; ++u) ld(op.a, u, t[u]);  // all loads issued before the first use
+        for (int u = 0; u < U; ++u) ld(op.a, u, acc[u]);  // all loads issued before the first use
+        if (op.dst >= 0) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) R.put(op.dst, u, t[u]);
+          for (int u = 0; u < U; ++u) R.put(op.dst, u, acc[u]);
+        }
         break;
-      }
       case TSB_OP_STORE:
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          unsigned t[VEC];
-          R.get(op.b, u, t);
-          st(op.a, u, t);
+        {
+          unsigned t[U][VEC];
+          vm_fetch<VEC, U>(op, op.b, R, acc, t);
+#pragma unroll
+          for (int u = 0; u < U; ++u) st(op.a, u, t[u]);
         }
         break;
       case TSB_OP_CONST:
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          unsigned t[VEC];
 #pragma unroll
-          for (int v = 0; v < VEC; ++v) t[v] = op.imm;
-          R.put(op.dst, u, t);
+          for (int v = 0; v < VEC; ++v) acc[u][v] = op.imm;
+          if (op.dst >= 0) R.put(op.dst, u, acc[u]);
         }
         break;
 #define TSB_VM_CASE(O) \
-  case O: vm_alu<O, VEC, U>(op, R); break;
+  case O: vm_alu<O, VEC, U>(op, R, acc); break;
         TSB_ALU_OPCODES(TSB_VM_CASE)
 #undef TSB_VM_CASE
       default: break;
@@ -521,14 +556,19 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d loads from a store access", k);
     if (o.opcode == TSB_OP_STORE && acc[o.a].is_store != 1)
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d stores to a load access", k);
-    if (o.opcode != TSB_OP_STORE && (o.dst < 0 || o.dst >= TSB_NUM_REGS))
+    if (o.opcode != TSB_OP_STORE && (o.dst < TSB_REG_ACC || o.dst >= TSB_NUM_REGS))
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, o.dst);
     const int regs[3] = {is_mem || o.opcode == TSB_OP_CONST ? 0 : o.a,
                          o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_CONST ? 0 : o.b,
                          (o.opcode == TSB_OP_SELECT || o.opcode == TSB_OP_FMA) ? o.c : 0};
-    for (int r = 0; r < 3; ++r)
-      if (regs[r] < 0 || regs[r] >= TSB_NUM_REGS)
+    for (int r = 0; r < 3; ++r) {
+      if (regs[r] < TSB_REG_IMM || regs[r] >= TSB_NUM_REGS)
         return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, regs[r]);
+      if (regs[r] == TSB_REG_IMM && o.opcode == TSB_OP_CAST)
+        return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d: a cast cannot take an immediate operand", k);
+      if (regs[r] == TSB_REG_ACC && k == 0)
+        return fail(TSB_ERR_INVALID, "tsb_elementwise: op 0 reads the accumulator");
+    }
   }
   P.n_acc = n_acc;
   P.n_ops = n_ops;
@@ -571,13 +611,19 @@ static int vm_regs_used(const tsb_op *ops, int n_ops) {
     const tsb_op &o = ops[k];
     if (o.opcode != TSB_OP_STORE && o.dst > hi) hi = o.dst;
     if (o.opcode == TSB_OP_STORE && o.b > hi) hi = o.b;
+    if (o.opcode != TSB_OP_LOAD && o.opcode != TSB_OP_STORE && o.opcode != TSB_OP_CONST) {
+      if (o.a > hi) hi = o.a;
+      if (o.b > hi) hi = o.b;
+      if (o.c > hi) hi = o.c;
+    }
   }
   return hi + 1;
 }
 
 static bool is_copy(const tsb_access *acc, const tsb_op *ops, int n_ops) {
-  return n_ops == 2 && ops[0].opcode == TSB_OP_LOAD && ops[1].opcode == TSB_OP_STORE && ops[1].b == ops[0].dst &&
-         acc[ops[0].a].is_store == 0 && acc[ops[0].a].dtype == acc[ops[1].a].dtype;
+  return n_ops == 2 && ops[0].opcode == TSB_OP_LOAD && ops[1].opcode == TSB_OP_STORE &&
+         (ops[1].b == TSB_REG_ACC || ops[1].b == ops[0].dst) && acc[ops[0].a].is_store == 0 &&
+         acc[ops[0].a].dtype == acc[ops[1].a].dtype;
 }
 
 // ew_copy2d_kernel applies when both sides are plain memory accesses of rank <= 2 with unit inner
@@ -604,14 +650,25 @@ static bool copy2d_ok(const EwParams &P, const int32_t grid[3]) {
   return true;
 }
 
-static bool is_fast_binary(const tsb_access *acc, const tsb_op *ops, int n_ops) {
+// out = binop(load, load) on fp32, written with registers or with the accumulator forms.
+// swapped: operand a of the binop comes from the second load.
+static bool is_fast_binary(const tsb_access *acc, const tsb_op *ops, int n_ops, bool &swapped) {
+  swapped = false;
   if (n_ops != 4) return false;
   if (ops[0].opcode != TSB_OP_LOAD || ops[1].opcode != TSB_OP_LOAD || ops[3].opcode != TSB_OP_STORE)
     return false;
   const int o = ops[2].opcode;
   if (o < TSB_OP_ADDF || o > TSB_OP_MINIMUMF || ops[2].type != TSB_F32) return false;
-  if (ops[2].a != ops[0].dst || ops[2].b != ops[1].dst || ops[3].b != ops[2].dst) return false;
-  if (ops[0].dst == ops[1].dst) return false;
+  auto source = [&](int x) {  // which load produced operand x of ops[2]
+    if (x == TSB_REG_ACC) return 1;
+    if (x >= 0 && x == ops[1].dst) return 1;
+    if (x >= 0 && x == ops[0].dst) return 0;
+    return -1;
+  };
+  const int sa = source(ops[2].a), sb = source(ops[2].b);
+  if (sa < 0 || sb < 0 || sa == sb) return false;
+  if (!(ops[3].b == TSB_REG_ACC || (ops[3].b >= 0 && ops[3].b == ops[2].dst))) return false;
+  swapped = sa == 1;
   return acc[ops[0].a].dtype == TSB_F32 && acc[ops[1].a].dtype == TSB_F32 &&
          acc[ops[3].a].dtype == TSB_F32;
 }
@@ -632,10 +689,17 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
   int threads = items >= 256 ? 256 : (items >= 128 ? 128 : (items >= 64 ? 64 : 32));
   const long long max_ctas = (long long)sm_count() * (2048 / threads) * 4;
   cudaStream_t s = (cudaStream_t)stream;
+  bool swapped = false;
+  const bool fast_binary = is_fast_binary(acc, ops, n_ops, swapped);
+  if (fast_binary && swapped) {  // the fast kernels take ops[0] as the load of operand a
+    const int t = P.ops[0].a;
+    P.ops[0].a = P.ops[1].a;
+    P.ops[1].a = t;
+  }
   static thread_local FlatParams F;
   if (build_flat(P, vec, F)) {
     const long long n_vec = (F.g_hi - F.g_lo) / 4;
-    const bool fast = is_fast_binary(acc, ops, n_ops);
+    const bool fast = fast_binary;
     // the VM's register file lives in shared memory: fewer threads per CTA when the body uses many registers
     int flat_threads = 256;
     const size_t regs_bytes = (size_t)vm_regs_used(ops, n_ops) * FLAT_VM_U * 4 * sizeof(unsigned);
@@ -658,7 +722,7 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     TSB_LAUNCH_OK("ew_flat_kernel");
     return TSB_OK;
   }
-  if (is_fast_binary(acc, ops, n_ops)) {
+  if (fast_binary) {
     long long ctas = (n_prog + 1) / 2;
     if (ctas > max_ctas) ctas = max_ctas;
     if (vec == 4) ew_binary_f32_kernel<4><<<(unsigned)ctas, threads, 0, s>>>(P);

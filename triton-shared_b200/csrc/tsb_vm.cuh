@@ -427,23 +427,32 @@ __device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int
 
 
 // One ALU op on one lane with the opcode known at compile time: the per-op switch is taken
-// once per thread (see TSB_ALU_OPCODES), not once per lane.
-template <int OPC>
+// once per thread (see TSB_ALU_OPCODES), not once per lane.  ROUND = false leaves a float result
+// unrounded (the caller rounds all lanes of the op at once when the op's type is 16-bit).
+template <int OPC, bool ROUND = true>
 __device__ __forceinline__ unsigned alu_op(const tsb_op &op, unsigned a, unsigned b, unsigned c) {
   if constexpr (OPC == TSB_OP_MOV || OPC == TSB_OP_BITCAST) return a;  // 32-bit <-> 32-bit bitcasts keep their bits
-  else if constexpr (OPC >= TSB_OP_ADDF && OPC < TSB_OP_EXP)
-    return __float_as_uint(round_to(binf(OPC, __uint_as_float(a), __uint_as_float(b)), op.type));
-  else if constexpr (OPC >= TSB_OP_EXP && OPC < TSB_OP_ADDI)
-    return __float_as_uint(round_to(unf(OPC, __uint_as_float(a)), op.type));
-  else if constexpr (OPC == TSB_OP_ABSI) return wrap_to((unsigned)abs((int)a), op.type);
+  else if constexpr (OPC >= TSB_OP_ADDF && OPC < TSB_OP_EXP) {
+    const float r = binf(OPC, __uint_as_float(a), __uint_as_float(b));
+    return __float_as_uint(ROUND ? round_to(r, op.type) : r);
+  } else if constexpr (OPC >= TSB_OP_EXP && OPC < TSB_OP_ADDI) {
+    const float r = unf(OPC, __uint_as_float(a));
+    return __float_as_uint(ROUND ? round_to(r, op.type) : r);
+  } else if constexpr (OPC == TSB_OP_ABSI) return wrap_to((unsigned)abs((int)a), op.type);
   else if constexpr (OPC >= TSB_OP_ADDI && OPC < TSB_OP_CMPF) return wrap_to(bini(OPC, a, b), op.type);
   else if constexpr (OPC == TSB_OP_CMPF) return cmpf_(op.imm, __uint_as_float(a), __uint_as_float(b));
   else if constexpr (OPC == TSB_OP_CMPI) return cmpi_(op.imm, a, b);
   else if constexpr (OPC == TSB_OP_SELECT) return (a & 1u) ? b : c;
   else if constexpr (OPC == TSB_OP_CAST) return cast_(a, (int)op.imm, op.type, op.imm2);
-  else if constexpr (OPC == TSB_OP_FMA)
-    return __float_as_uint(round_to(fmaf(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c)), op.type));
-  else return 0u;
+  else if constexpr (OPC == TSB_OP_FMA) {
+    const float r = fmaf(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c));
+    return __float_as_uint(ROUND ? round_to(r, op.type) : r);
+  } else return 0u;
+}
+// float-result ops whose result must be re-rounded when the op's type is f16 / bf16
+template <int OPC>
+__device__ __forceinline__ constexpr bool alu_rounds() {
+  return (OPC >= TSB_OP_ADDF && OPC < TSB_OP_ADDI) || OPC == TSB_OP_FMA;
 }
 
 // Operands an ALU opcode reads (1, 2 or 3), known at compile time.
