@@ -68,10 +68,16 @@ __device__ __forceinline__ void ew_loop(const tsb_op &op, const int lg[3], unsig
       const uint4 B = (AR >= 2 && mb == md) ? pb[e] : make_uint4(b0, b0, b0, b0);
       const uint4 C = (AR >= 3 && mc == md) ? pc[e] : make_uint4(c0, c0, c0, c0);
       uint4 r;
-      r.x = alu_op<OPC>(op, A.x, B.x, C.x);
-      r.y = alu_op<OPC>(op, A.y, B.y, C.y);
-      r.z = alu_op<OPC>(op, A.z, B.z, C.z);
-      r.w = alu_op<OPC>(op, A.w, B.w, C.w);
+      r.x = alu_op<OPC, false>(op, A.x, B.x, C.x);
+      r.y = alu_op<OPC, false>(op, A.y, B.y, C.y);
+      r.z = alu_op<OPC, false>(op, A.z, B.z, C.z);
+      r.w = alu_op<OPC, false>(op, A.w, B.w, C.w);
+      if (alu_rounds<OPC>() && op.type != TSB_F32) {  // 16-bit float op: re-round, decided once per vector
+        r.x = __float_as_uint(round_to(__uint_as_float(r.x), op.type));
+        r.y = __float_as_uint(round_to(__uint_as_float(r.y), op.type));
+        r.z = __float_as_uint(round_to(__uint_as_float(r.z), op.type));
+        r.w = __float_as_uint(round_to(__uint_as_float(r.w), op.type));
+      }
       reinterpret_cast<uint4 *>(dst)[e] = r;
     }
   } else if (sa && sb && sc) {
