@@ -158,7 +158,9 @@ enum tsb_opcode {
   TSB_OP_FMA = 92, /* math.fma: single rounding */
   TSB_OP_REDUCE = 100, /* tsb_block_program only: dst <- fold of reg a along dim imm2 with combiner opcode imm */
   TSB_OP_LOOP_BEGIN = 101, /* tsb_block_program only: loop slot a runs imm iterations; b = index of the op after its LOOP_END */
-  TSB_OP_LOOP_END = 102    /* tsb_block_program only: closes loop slot a */
+  TSB_OP_LOOP_END = 102,   /* tsb_block_program only: closes loop slot a */
+  TSB_OP_ARGREDUCE = 103   /* tsb_block_program only: (dst, c) <- (value, index) of the largest (imm = 1) or smallest
+                              (imm = 0) element of reg a along dim imm2, indices from reg b, ties to the smaller index */
 };
 
 enum tsb_cmp {

@@ -400,3 +400,22 @@ def wide_softmax_kernel(out_ptr, in_ptr, stride, N, BLOCK: tl.constexpr):
         cols = off + tl.arange(0, BLOCK)
         x = tl.load(in_ptr + row * stride + cols, mask=cols < N, other=-float("inf"))
         tl.store(out_ptr + row * stride + cols, tl.exp(x - m) / s, mask=cols < N)
+
+
+@triton.jit
+def row_argmax_kernel(x_ptr, val_ptr, idx_ptr, stride, n, BLOCK: tl.constexpr):
+    """Per row: the maximum and the index of its first occurrence."""
+    row = tl.program_id(0)
+    offs = tl.arange(0, BLOCK)
+    x = tl.load(x_ptr + row * stride + offs, mask=offs < n, other=-float("inf"))
+    tl.store(val_ptr + row, tl.max(x, axis=0))
+    tl.store(idx_ptr + row, tl.argmax(x, axis=0))
+
+
+@triton.jit
+def tile_argmin_kernel(x_ptr, idx_ptr, stride_m, BM: tl.constexpr, BN: tl.constexpr):
+    """Index of the smallest element of every row of a BM x BN tile (argmin along axis 1)."""
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.arange(0, BN)
+    x = tl.load(x_ptr + offs_m[:, None] * stride_m + offs_n[None, :])
+    tl.store(idx_ptr + offs_m, tl.argmin(x, axis=1))

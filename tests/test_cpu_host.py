@@ -360,6 +360,18 @@ def _block_program_cases(dev):
         blk[:rows.shape[0], :24] = rows
         exp_cmin[pid, :24] = blk.min(dim=0).values[:24]
     out.append(("tile_colmin", cmin.cpu().reshape(4, 32), exp_cmin, 0))
+    # argmax / argmin: ties go to the smaller index
+    xa = torch.randint(0, 5, (6, 100), device=dev).float()  # many ties
+    av = torch.zeros(6, device=dev)
+    ai = torch.zeros(6, dtype=torch.int32, device=dev)
+    K.row_argmax_kernel[(6,)](xa, av, ai, 100, 90, BLOCK=128)
+    firsts = torch.tensor([int((r[:90] == r[:90].max()).nonzero()[0]) for r in xa.cpu()], dtype=torch.int32)
+    out.append(("argmax_val", av.cpu(), xa[:, :90].max(dim=1).values.cpu(), 0))
+    out.append(("argmax_idx", ai.cpu(), firsts, 0))
+    xt = torch.randn(32, 16, device=dev)
+    ti = torch.zeros(32, dtype=torch.int32, device=dev)
+    K.tile_argmin_kernel[(4,)](xt, ti, 16, BM=8, BN=16)
+    out.append(("argmin_axis1", ti.cpu(), xt.argmin(dim=1).to(torch.int32).cpu(), 0))
     # loops that carry block values (device-side loops of the block-program kernel)
     xr = torch.randn(7, 1000, device=dev)
     rs = torch.zeros(7, device=dev)
@@ -384,7 +396,7 @@ def test_block_programs_on_host_stand_in():
             assert torch.equal(got, exp), name
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
-    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 6
+    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 8
 
 
 # ------------------------------------------------------------------ a spread of elementwise ops

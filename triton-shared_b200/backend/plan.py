@@ -777,6 +777,14 @@ def _discover_space(stores: List[Access], loops: Dict[int, Loop] = None):
             src = n.args[0]
             d = red_dim.setdefault(n.id, uf.fresh(src.shape[ax]))
             visit(src, dims[:ax] + (d,) + dims[ax:])
+        elif n.op == "argreduce":
+            ax = n.attr("axis")
+            # both results of one tt.reduce share the reduced dim
+            key = ("arg", n.args[0].id, n.args[1].id, ax)
+            d = red_dim.setdefault(key, uf.fresh(n.args[0].shape[ax]))
+            red_dim[n.id] = d
+            for a in n.args:
+                visit(a, dims[:ax] + (d,) + dims[ax:])
         elif n.op in ("iter_arg", "loop_result"):
             key = (n.attr("loop"), n.attr("k"))
             if key in carried:
@@ -823,7 +831,7 @@ def _discover_space(stores: List[Access], loops: Dict[int, Loop] = None):
     pos = {d: i for i, d in enumerate(space)}
     maps = {k: tuple(pos[uf.find(d)] for d in dims) for k, dims in node_dims.items()}
     sizes = [uf.size[d] for d in space]
-    red_pos = {nid: pos[uf.find(d)] for nid, d in red_dim.items()}
+    red_pos = {nid: pos[uf.find(d)] for nid, d in red_dim.items() if isinstance(nid, int)}
     return sizes, maps, red_pos
 
 
@@ -835,6 +843,7 @@ class _BpLowering(_EwLowering):
         self.vmask: Dict[int, int] = {}
         self.acc_mask: Dict[int, int] = {}
         self.red_pos = red_pos
+        self.arg_pairs: Dict[tuple, tuple] = {}
 
     def acc_for(self, kind, elem, shape, dimmap, offset, strides, mask, other, arg=None, wrapped=()):
         # a mask bound that moves with a loop counter (`k < K - it*BLOCK`) is the same mask with the
@@ -884,6 +893,22 @@ class _BpLowering(_EwLowering):
             if key not in self.carried_reg:
                 raise UnsupportedTTIR("block program: loop-carried value used outside its loop's scope")
             return self.carried_reg[key]
+        if n.op == "argreduce":
+            ax, d = n.attr("axis"), self.red_pos[n.id]
+            sub = dimmap[:ax] + (d,) + dimmap[ax:]
+            key = ("arg", n.args[0].id, n.args[1].id, dimmap)
+            pair = self.arg_pairs.get(key)
+            if pair is None:
+                val = self.value(n.args[0], sub)
+                idx = self.value(n.args[1], sub)
+                m = (self.vmask[val] | self.vmask[idx]) & ~(1 << d)
+                rv = self.emit("argreduce", n.args[0].dtype, a=val, b=idx, imm=1 if n.attr("comb") == "argmax" else 0,
+                               imm2=d, mask=m)
+                ri = self.new()  # the op writes a second register: the winning index
+                self.vmask[ri] = m
+                self.ops[-1][5] = ri
+                pair = self.arg_pairs[key] = (rv, ri)
+            return pair[n.attr("out")]
         if n.op == "reduce":
             ax, comb = n.attr("axis"), n.attr("comb")
             if comb not in ("addf", "mulf", "maxnumf", "minnumf", "maximumf", "minimumf", "addi", "muli", "maxsi",
@@ -991,7 +1016,7 @@ class _BpLowering(_EwLowering):
                 m = self.vmask[o[2]]
                 # an elementwise result may overwrite an operand of the same mask that dies here; a
                 # reduction never writes into its own source
-                if o[0] != "reduce":
+                if o[0] not in ("reduce", "argreduce"):
                     for r in set(reads):
                         if last_use[r] == i and r in phys:
                             free.setdefault(self.vmask[r], []).append(phys.pop(r))
@@ -1000,12 +1025,27 @@ class _BpLowering(_EwLowering):
                 else:
                     dst = len(masks)
                     masks.append(m)
+                second = None
+                if o[0] == "argreduce":  # writes two registers: the winning value and its index
+                    if free.get(m):
+                        second = free[m].pop()
+                    else:
+                        second = len(masks)
+                        masks.append(m)
                 if o[2] in last_use:
                     phys[o[2]] = dst
                 else:
                     free.setdefault(m, []).append(dst)
                 o[2] = dst
+                if second is not None:
+                    v2 = o[5]
+                    if v2 in last_use:
+                        phys[v2] = second
+                    else:
+                        free.setdefault(m, []).append(second)
             _remap(o, mapped)
+            if o[0] == "argreduce":
+                o[5] = second
             for r in set(reads):
                 if last_use[r] == i and r in phys:
                     free.setdefault(self.vmask[r], []).append(phys.pop(r))

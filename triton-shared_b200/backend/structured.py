@@ -714,6 +714,8 @@ class Analyzer:
     def _reduce(self, op: Op, env):
         blk = op.regions[0]
         body = [o for o in blk.ops if o.name != "tt.reduce.return"]
+        if len(op.operands) == 2 and len(op.results) == 2:
+            return self._arg_reduce(op, env, blk, body)
         if len(op.operands) != 1 or len(body) != 1 or len(body[0].operands) != 2:
             raise UnsupportedTTIR("tt.reduce with more than one input or a multi-op body")
         comb = body[0].name.split(".")[1]
@@ -724,6 +726,28 @@ class Analyzer:
         rty = op.results[0][1]
         env[op.results[0][0]] = TData(self.node("reduce", (src,), {"axis": op.attrs["axis"], "comb": comb},
                                                 rty.shape, rty.elem))
+
+    def _arg_reduce(self, op: Op, env, blk: Block, body):
+        """tl.argmax / tl.argmin: a reduction over (value, index) pairs that keeps the larger
+        (smaller) value and, among equal values, the smaller index (the reference lowers the same
+        region, ConversionPatterns.hpp:1442-1769)."""
+        names = [o.name for o in body]
+        preds = [o.attrs.get("predicate") for o in body if o.name == "arith.cmpf"]
+        shape_ok = sorted(names) == sorted(["arith.cmpf", "arith.cmpi", "arith.andi", "arith.cmpf", "arith.ori",
+                                            "arith.select", "arith.select"])
+        if not shape_ok or "oeq" not in preds or not ({"ogt", "olt"} & set(preds)):
+            raise UnsupportedTTIR("two-input tt.reduce that is not the argmax / argmin pattern")
+        cmpi = [o for o in body if o.name == "arith.cmpi"][0]
+        if cmpi.attrs.get("predicate") != "slt":
+            raise UnsupportedTTIR("argmax / argmin with an unexpected tie-break")
+        kind = "argmax" if "ogt" in preds else "argmin"
+        val = self.as_data(env[op.operands[0]])
+        idx = self.as_data(env[op.operands[1]])
+        for k in range(2):
+            rty = op.results[k][1]
+            env[op.results[k][0]] = TData(self.node("argreduce", (val, idx),
+                                                    {"axis": op.attrs["axis"], "comb": kind, "out": k},
+                                                    rty.shape, rty.elem))
 
     def _for(self, op: Op, env, effects, loop_stack, record):
         lb, ub, step = (env[o] for o in op.operands[:3])

@@ -198,6 +198,43 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
             store_vec<1>(A, st, i0, i1, i2, v);
           }
         }
+      } else if (op.opcode == TSB_OP_ARGREDUCE) {
+        // (dst, c) = (value, index) of the extreme element along dim imm2; one warp per output
+        const int d = (int)op.imm2;
+        const bool want_max = op.imm != 0;
+        const int mv = P.reg_mask[op.a], mi = P.reg_mask[op.b], md = P.reg_mask[op.dst];
+        const unsigned *vsrc = bp_smem + P.reg_off[op.a], *isrc = bp_smem + P.reg_off[op.b];
+        unsigned *vdst = bp_smem + P.reg_off[op.dst], *idst = bp_smem + P.reg_off[op.c];
+        const int len = P.size[d];
+        // a over b iff a is strictly better, or equal with the smaller index (the region of tl.argmax / tl.argmin)
+        auto better = [&](float va, int ia, float vb, int ib) {
+          return (want_max ? va > vb : va < vb) || (va == vb && ia < ib);
+        };
+        for (int o = warp; o < P.reg_n[op.dst]; o += BP_THREADS / 32) {
+          int c[3];
+          reg_coords(P.lg, md, o, c[0], c[1], c[2]);
+          bool have = false;
+          float bv = 0.f;
+          int bi = 0;
+          for (int j = lane; j < len; j += 32) {
+            c[d] = j;
+            const float v = __uint_as_float(vsrc[reg_index(P.lg, mv, c[0], c[1], c[2])]);
+            const int ix = (int)isrc[reg_index(P.lg, mi, c[0], c[1], c[2])];
+            // fold order of the reference: acc = combine(element, acc)
+            if (!have || better(v, ix, bv, bi)) { bv = v; bi = ix; have = true; }
+          }
+#pragma unroll
+          for (int s = 16; s > 0; s >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, s);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, s);
+            const bool oh = __shfl_xor_sync(0xffffffffu, have ? 1 : 0, s) != 0;
+            if (oh && (!have || better(ov, oi, bv, bi))) { bv = ov; bi = oi; have = true; }
+          }
+          if (lane == 0) {
+            vdst[o] = __float_as_uint(bv);
+            idst[o] = (unsigned)bi;
+          }
+        }
       } else if (op.opcode == TSB_OP_REDUCE) {
         // dst = fold of src along dim imm2 with combiner imm; one warp per output element
         const int d = (int)op.imm2, comb = (int)op.imm;
@@ -320,7 +357,7 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
     if (o.opcode == TSB_OP_LOAD && acc[o.a].is_store == 1) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d loads from a store access", k);
     if (o.opcode == TSB_OP_STORE && acc[o.a].is_store != 1) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d stores to a load access", k);
     if (o.opcode == TSB_OP_STORE) o.imm = o.imm << (3 - rank);
-    if (o.opcode == TSB_OP_REDUCE) {
+    if (o.opcode == TSB_OP_REDUCE || o.opcode == TSB_OP_ARGREDUCE) {
       if (o.imm2 >= (unsigned)rank) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d reduces dim %u of rank %d", k, o.imm2, rank);
       o.imm2 += 3 - rank;
     }
