@@ -217,12 +217,12 @@ class FakeLib:
                     d, want_max = int(o.imm2), int(o.imm) != 0
                     shp = tuple(max(a, b) for a, b in zip(R[o.a].shape, R[o.b].shape))
                     val = np.broadcast_to(R[o.a], shp).view(np.float32)
-                    idx = np.broadcast_to(R[o.b], shp).view(np.int32)
+                    ind = np.broadcast_to(R[o.b], shp).view(np.int32)
                     key = np.where(np.isnan(val), -np.inf if want_max else np.inf, val)
                     best = key.max(axis=d, keepdims=True) if want_max else key.min(axis=d, keepdims=True)
-                    cand = np.where(key == best, idx, np.iinfo(np.int32).max)
+                    cand = np.where(key == best, ind, np.iinfo(np.int32).max)
                     bi = cand.min(axis=d, keepdims=True)
-                    pick = np.argmax((key == best) & (idx == bi), axis=d)
+                    pick = np.argmax((key == best) & (ind == bi), axis=d)
                     R[o.dst] = np.take_along_axis(val, np.expand_dims(pick, d), axis=d).view(np.uint32).copy()
                     R[o.c] = bi.astype(np.int32).view(np.uint32)
                 elif name == "reduce":
