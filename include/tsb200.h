@@ -281,7 +281,10 @@ int tsb_layernorm_fwd(const void *x, void *y, const void *w, const void *b, floa
  *
  * `scratch` is caller-provided device memory of at least
  * tsb_reduce_rows_scratch_bytes(row_hi-row_lo, n_valid, stride_m, stride_n) bytes
- * holding per-split partial sums; it may be NULL when that size is 0.
+ * holding per-split partial sums; it may be NULL when that size is 0.  With stride_m == 1 and
+ * enough rows to fill the GPU with at most 16 column splits per 128-row tile the splits are
+ * combined inside a thread-block cluster (one launch, no scratch); matrices of few rows and
+ * very many columns use the scratch partial sums and a second, combining launch.
  */
 int64_t tsb_reduce_rows_scratch_bytes(int64_t n_rows, int64_t n_valid, int64_t stride_m,
                                       int64_t stride_n);
@@ -303,7 +306,7 @@ int tsb_reduce_rows(const float *x, float *out, int64_t stride_m, int64_t stride
  * keep them on one stream or order them with events.  The first call on a device
  * looks the array's address up and should precede any stream capture.
  */
-#define TSB_REDUCE_STATIC_SCRATCH_BYTES (2u << 20)
+#define TSB_REDUCE_STATIC_SCRATCH_BYTES (1u << 20)
 int tsb_reduce_rows_static(const float *x, float *out, int64_t stride_m, int64_t stride_n,
                            int64_t out_stride, int64_t n_valid, int64_t row_lo, int64_t row_hi,
                            void *stream);

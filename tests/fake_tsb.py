@@ -56,12 +56,12 @@ class HostMemory:
         self._tables = {}
         self._status = np.zeros(4, dtype=np.int32)
 
-    def scratch(self, nbytes):
+    def scratch(self, nbytes, stream=0):
         if self._scratch is None or self._scratch.size < nbytes:
             self._scratch = np.zeros(max(nbytes, 1024), dtype=np.uint8)
         return self._scratch.ctypes.data
 
-    def table(self, key, host):
+    def table(self, key, host, stream=0):
         t = self._tables.get(key)
         if t is None:
             t = self._tables[key] = np.ascontiguousarray(host)
@@ -72,6 +72,9 @@ class HostMemory:
 
     def read_status(self):
         return self._status.tolist()
+
+    def clear_status(self):
+        self._status[:] = 0
 
 
 class _Regs(dict):
@@ -119,30 +122,46 @@ class FakeLib:
         sizes = [int(accs[0].sizes[d]) for d in range(rank)]
         lanes = int(np.prod(sizes))
         idx = np.unravel_index(np.arange(lanes), sizes)
+        import itertools
+        body = [ops[k] for k in range(n_ops)]
+        trips = []
+        while body and _OPNAME[body[0].opcode] == "loop_begin":  # a perfect nest around the whole body
+            assert _OPNAME[body[-1].opcode] == "loop_end" and body[-1].a == body[0].a == len(trips)
+            trips.append(int(body[0].imm))
+            body = body[1:-1]
         for prog in range(pid_lo, pid_hi):
             p = (prog % g[0], (prog // g[0]) % g[1], prog // (g[0] * g[1]))
-            state = [self._acc_state(accs[a], p, rank, sizes, idx, lanes) for a in range(n_acc)]
-            regs = _Regs(lanes)
-            for k in range(n_ops):
-                o = ops[k]
-                name = _OPNAME[o.opcode]
-                regs.imm = np.uint32(o.imm2)
-                if name == "load":
-                    A = accs[o.a]
-                    elem, valid = state[o.a]
-                    if A.is_store == 2:
-                        v = valid.astype(np.uint32)
-                    elif A.is_store == 3:
-                        v = elem.astype(np.int64).astype(np.uint32)
+            for its in itertools.product(*[range(t) for t in trips]):
+                it = tuple(its) + (0,) * (4 - len(its))
+                state = [self._acc_state(accs[a], p, rank, sizes, idx, lanes, it) for a in range(n_acc)]
+                regs = _Regs(lanes)
+                for o in body:
+                    name = _OPNAME[o.opcode]
+                    regs.imm = np.uint32(o.imm2)
+                    if name == "load":
+                        A = accs[o.a]
+                        elem, valid = state[o.a]
+                        if o.imm & rt.MEM_INDEX:
+                            elem = elem + regs[o.b].view(np.int32).astype(np.int64)
+                        if o.imm & rt.MEM_MASK:
+                            valid = valid & ((regs[o.c] & 1) != 0)
+                        if A.is_store == 2:
+                            v = valid.astype(np.uint32)
+                        elif A.is_store == 3:
+                            v = elem.astype(np.int64).astype(np.uint32)
+                        else:
+                            v = self._load(A, elem, valid)
+                        regs.write(o.dst, v)
+                    elif name == "store":
+                        A = accs[o.a]
+                        elem, valid = state[o.a]
+                        if o.imm & rt.MEM_INDEX:
+                            elem = elem + regs[o.c].view(np.int32).astype(np.int64)
+                        if o.imm & rt.MEM_MASK:
+                            valid = valid & ((regs[o.dst] & 1) != 0)
+                        self._store(A, elem, valid, regs[o.b])
                     else:
-                        v = self._load(A, elem, valid)
-                    regs.write(o.dst, v)
-                elif name == "store":
-                    A = accs[o.a]
-                    elem, valid = state[o.a]
-                    self._store(A, elem, valid, regs[o.b])
-                else:
-                    regs.write(o.dst, self._alu(name, o, regs, lanes))
+                        regs.write(o.dst, self._alu(name, o, regs, lanes))
         return 0
 
     @staticmethod

@@ -323,8 +323,8 @@ def test_loops_and_wraparound_on_host_stand_in():
         cases = _loop_and_wrap_cases("cpu")
     for name, got, exp in cases:
         assert torch.equal(got, exp), name
-    # 5 loop iterations, 3*5 tile steps, 2 wrap steps, 1 single launch
-    assert len(lib.calls) == 5 + 15 + 2 + 1
+    # every loop nest here is perfect, so each kernel is one launch with the loops run on the device
+    assert len(lib.calls) == 4
 
 
 # ------------------------------------------------------------------ block programs (reductions in the body)

@@ -66,7 +66,15 @@ class DevicePtr:
 
 class TorchDeviceMemory:
     """Device memory the kernels need beyond inputs and outputs, owned by the host side
-    (the C library never allocates).  One instance per process; state is kept per device."""
+    (the C library never allocates).  One instance per process; state is kept per device.
+
+    Scratch is one grow-only buffer per (device, stream): launches on different streams never share
+    partial sums, and a buffer that is replaced by a larger one is handed back to torch's caching
+    allocator only after the work already queued on its stream (``record_stream``).  Uploaded tile
+    tables are keyed by content and are evicted oldest first, after a device synchronisation, so a
+    table is never released under a launch that still reads it."""
+
+    MAX_TABLES = 256
 
     def __init__(self):
         self._state = {}
@@ -76,23 +84,28 @@ class TorchDeviceMemory:
         d = torch.cuda.current_device()
         st = self._state.get(d)
         if st is None:
-            st = self._state[d] = {"scratch": None, "tables": {}, "status": None}
+            st = self._state[d] = {"scratch": {}, "tables": {}, "status": None}
         return st
 
-    def scratch(self, nbytes: int) -> int:
+    def scratch(self, nbytes: int, stream: int = 0) -> int:
         import torch
         st = self._dev()
-        if st["scratch"] is None or st["scratch"].numel() < nbytes:
-            st["scratch"] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device="cuda")
-        return st["scratch"].data_ptr()
+        buf = st["scratch"].get(stream)
+        if buf is None or buf.numel() < nbytes:
+            if buf is not None:
+                buf.record_stream(torch.cuda.ExternalStream(stream) if stream else torch.cuda.default_stream())
+            buf = st["scratch"][stream] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device="cuda")
+        return buf.data_ptr()
 
-    def table(self, key, host: np.ndarray) -> int:
+    def table(self, key, host: np.ndarray, stream: int = 0) -> int:
         import torch
         st = self._dev()
         t = st["tables"].get(key)
         if t is None:
-            if len(st["tables"]) > 32:
-                st["tables"].clear()
+            if len(st["tables"]) >= self.MAX_TABLES:
+                torch.cuda.synchronize()  # nothing in flight reads the tables that go
+                for old in list(st["tables"])[: self.MAX_TABLES // 2]:
+                    del st["tables"][old]
             t = torch.from_numpy(np.ascontiguousarray(host)).to("cuda")
             st["tables"][key] = t
         return t.data_ptr()
@@ -107,6 +120,11 @@ class TorchDeviceMemory:
     def read_status(self):
         st = self._dev()
         return None if st["status"] is None else st["status"].cpu().tolist()
+
+    def clear_status(self):
+        st = self._dev()
+        if st["status"] is not None:
+            st["status"].zero_()
 
 
 class LaunchArgs:
@@ -140,10 +158,10 @@ class LaunchArgs:
         return p
 
     def scratch(self, nbytes: int, stream) -> int:
-        return self._mem.scratch(nbytes)
+        return self._mem.scratch(nbytes, int(stream or 0))
 
     def device_table(self, key, host: np.ndarray, stream) -> int:
-        return self._mem.table(key, host)
+        return self._mem.table(key, host, int(stream or 0))
 
     def status_word(self, stream) -> int:
         return self._mem.status()
@@ -256,6 +274,24 @@ class B200Driver(DriverBase):
             yield self
         finally:
             self._range = old
+
+    def check(self):
+        """Raise if a device-side bounded wait of an earlier launch gave up.
+
+        The tcgen05 matmul kernels wait on mbarriers with a time limit; a wait that expires records
+        (code, role, tile, k step) in a per-device status word and the kernel returns, leaving its
+        output invalid.  Launches are asynchronous, so the launcher cannot see this: call check()
+        after the work has been synchronised (it synchronises the device itself) wherever a silent
+        failure is not acceptable.  The word is cleared by the call."""
+        import torch
+        mem = B200Launcher.memory
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        st = mem.read_status()
+        if st and st[0] != 0:
+            mem.clear_status()
+            raise rt.TsbError(f"a device-side wait timed out (code {st[0]}: role {st[1]}, tile {st[2]}, k step {st[3]}); "
+                              "the output of that matmul launch is invalid")
 
     def get_benchmarker(self):
         from triton.testing import do_bench

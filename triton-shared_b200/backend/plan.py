@@ -342,6 +342,32 @@ class _EwLowering:
         self.ops.append([opcode, dtype, dst, a, b, c, imm, imm2])
         return dst
 
+    def weight(self, n) -> int:
+        """Ops a value costs to compute (its distinct non-leaf nodes): the operand with the larger
+        weight is evaluated first, so that the lighter one (often a leaf, which emits nothing) is
+        what separates it from its consumer and the result stays in the accumulator."""
+        memo = self.__dict__.setdefault("_weights", {})
+
+        def nodes(m, seen):
+            if not isinstance(m, Node) or m.id in seen or m.op in ("const", "sint", "farg", "load", "index", "maskval"):
+                return
+            seen.add(m.id)
+            for a in m.args:
+                nodes(a, seen)
+        if n.id not in memo:
+            seen = set()
+            nodes(n, seen)
+            memo[n.id] = len(seen)
+        return memo[n.id]
+
+    def values(self, nodes, dimmap):
+        """Registers of several operands, evaluated heaviest first."""
+        order = sorted(range(len(nodes)), key=lambda i: -self.weight(nodes[i]))
+        out = [None] * len(nodes)
+        for i in order:
+            out[i] = self.value(nodes[i], dimmap)
+        return out
+
     def value(self, n: Node, dimmap: Tuple[int, ...]) -> int:
         key = (n.id, dimmap)
         if key in self.memo:
@@ -387,23 +413,22 @@ class _EwLowering:
         if op in ("addf", "subf", "mulf", "divf", "maxnumf", "minnumf", "maximumf", "minimumf", "remf",
                   "addi", "subi", "muli", "divsi", "remsi", "divui", "remui", "minsi", "maxsi", "minui",
                   "maxui", "andi", "ori", "xori", "shli", "shrsi", "shrui"):
-            a = self.value(n.args[0], dimmap)
-            b = self.value(n.args[1], dimmap)
+            a, b = self.values(n.args, dimmap)
             return self.emit(op, n.dtype, a=a, b=b)
         if op in ("exp", "exp2", "log", "log2", "sqrt", "rsqrt", "sin", "cos", "tanh", "erf", "absf",
                   "negf", "floor", "ceil", "absi"):
             return self.emit(op, n.dtype, a=self.value(n.args[0], dimmap))
         if op == "fma":
-            a, b, c = (self.value(x, dimmap) for x in n.args)
+            a, b, c = self.values(n.args, dimmap)
             return self.emit("fma", n.dtype, a=a, b=b, c=c)
         if op == "cmpf":
-            a, b = self.value(n.args[0], dimmap), self.value(n.args[1], dimmap)
+            a, b = self.values(n.args, dimmap)
             return self.emit("cmpf", n.args[0].dtype, a=a, b=b, imm=rt.CMPF[n.attr("pred")])
         if op == "cmpi":
-            a, b = self.value(n.args[0], dimmap), self.value(n.args[1], dimmap)
+            a, b = self.values(n.args, dimmap)
             return self.emit("cmpi", n.args[0].dtype, a=a, b=b, imm=rt.CMPI[n.attr("pred")])
         if op == "select":
-            c, a, b = (self.value(x, dimmap) for x in n.args)
+            c, a, b = self.values(n.args, dimmap)
             return self.emit("select", n.dtype, a=c, b=a, c=b)
         if op == "cast":
             kind = n.attr("kind")
@@ -414,6 +439,11 @@ class _EwLowering:
                     raise UnsupportedTTIR("bitcast between types that are not 32 bits wide")
                 return self.emit("bitcast", n.dtype, a=a)
             mode = 1 if kind in ("uitofp", "fptoui", "extui") else 0
+            # registers hold f16 / bf16 values exactly widened to f32 and i8 / i16 sign-extended:
+            # widening to f32 and signed widening to i32 change nothing
+            if (kind in ("extf", "fp_to_fp") and n.dtype == "f32" and src.dtype in ("f16", "bf16")) or \
+                    (kind == "extsi" and n.dtype == "i32" and src.dtype in ("i8", "i16")):
+                return a
             return self.emit("cast", n.dtype, a=a, imm=rt.DTYPES[src.dtype], imm2=mode)
         raise UnsupportedTTIR(f"operation {op} has no elementwise lowering")
 
@@ -430,10 +460,23 @@ class _EwLowering:
     def allocate(self):
         """Hoist loads; turn constants into immediate operands; keep a value that only the next op
         reads in the accumulator; map what remains onto TSB_NUM_REGS shared-memory registers."""
+        hoisted = self._allocate(True)
+        if _regs_used(hoisted) > rt.RVM_REGS:
+            # loads at their point of use keep fewer values alive: take that order when it lets the
+            # body run on the hardware-register VM (rt.RVM_REGS registers besides the accumulator)
+            try:
+                inplace = self._allocate(False)
+            except UnsupportedTTIR:
+                return hoisted
+            if _regs_used(inplace) <= rt.RVM_REGS:
+                return inplace
+        return hoisted
+
+    def _allocate(self, hoist_loads: bool):
         ACC, IMM = rt.REG_ACC, rt.REG_IMM
         loads = [o for o in self.ops if o[0] == "load"]
         rest = [o for o in self.ops if o[0] != "load"]
-        ops = [list(o) for o in loads + rest]
+        ops = [list(o) for o in (loads + rest if hoist_loads else self.ops)]
         slots = {"store": (4,), "select": (3, 4, 5), "fma": (3, 4, 5)}
 
         def read_slots(o):
@@ -497,6 +540,21 @@ class _EwLowering:
         if len(self.accs) > rt.TSB_MAX_ACCESSES:
             raise UnsupportedTTIR(f"{len(self.accs)} block accesses exceed {rt.TSB_MAX_ACCESSES}")
         return out
+
+
+def _regs_used(ops) -> int:
+    """Highest register number an allocated body names, plus one (accumulator and immediate forms are negative)."""
+    hi = -1
+    for o in ops:
+        named = [] if o[0] == "store" else [o[2]]
+        if o[0] == "store":
+            named.append(o[4])
+        elif o[0] in ("select", "fma"):
+            named += [o[3], o[4], o[5]]
+        elif o[0] not in ("load", "const"):
+            named += [o[3]] if len(_reads(o)) == 1 else [o[3], o[4]]
+        hi = max([hi] + [r for r in named if isinstance(r, int)])
+    return hi + 1
 
 
 def _reads(o):
@@ -600,10 +658,54 @@ class ElementwisePlan(Plan):
             if rc:
                 rt.check(rc, f"tsb_elementwise[{self.name}]")
 
+    def _perfect_nest(self):
+        """(segment index, [(loop id, lb, ub, step)] outermost first) when the kernel is one segment
+        inside a perfect loop nest whose iterations only shift offsets and mask starts; else None.
+        Such a nest runs on the device, inside one launch (TSB_OP_LOOP_BEGIN / END around the body)."""
+        node, loops = self.p["tree"], []
+        while len(node) == 1 and node[0][0] == "loop":
+            _, lid, lb, ub, step, children = node[0]
+            loops.append((lid, lb, ub, step))
+            node = children
+        if not loops or len(loops) > rt.TSB_MAX_LOOPS or len(node) != 1 or node[0][0] != "seg":
+            return None
+        for _, lb, ub, step in loops:
+            if any(q.depends_on(("it",)) for q in (lb, ub, step)):
+                return None
+        seg = self.p["segments"][node[0][1]]
+        for d in seg["accs"]:
+            fixed = d["strides"] + [m[1] for m in d["mask"] if m] + d["conds"] + \
+                [x for w in d["wrap"] for x in w.values() if isinstance(x, Poly)]
+            if any(q.depends_on(("it",)) for q in fixed):
+                return None
+            if not all(_is_affine_in_its(q) for q in [d["offset"]] + [m[0] for m in d["mask"] if m]):
+                return None
+        for o in seg["ops"]:
+            for imm in (o[6], o[7]):
+                if isinstance(imm, (list, tuple)) and imm[0] == "poly" and imm[1].depends_on(("it",)):
+                    return None
+        return node[0][1], loops
+
     def _schedule(self, args, grid):
-        """Flatten the loop tree into the ordered list of launches for these scalar arguments."""
+        """The ordered list of launches for these scalar arguments: one launch with device-side loops
+        for a perfect nest, else the loop tree flattened on the host (one launch per iteration)."""
         out = []
         env = LaunchEnv(args.scalars, grid)
+        nest = self._perfect_nest()
+        if nest is not None:
+            si, loops = nest
+            seg = dict(self.p["segments"][si])
+            seg["loop_depth"] = {str(lid): depth for depth, (lid, _, _, _) in enumerate(loops)}
+            head = [["loop_begin", "i32", -1, depth, 0, 0, ("trip", lid), 0] for depth, (lid, _, _, _) in enumerate(loops)]
+            tail = [["loop_end", "i32", -1, depth, 0, 0, 0, 0] for depth in reversed(range(len(loops)))]
+            seg["ops"] = head + list(seg["ops"]) + tail
+            trips = {str(lid): Poly.fn("ceildivsi", ub - lb, step) for lid, lb, ub, step in loops}
+            e = env.at()
+            if any(int(step.evaluate(e)) <= 0 for _, _, _, step in loops):
+                raise UnsupportedTTIR("loop with a non-positive step")
+            for lid, _, _, _ in loops:
+                env.base[("it", lid)] = 0
+            return [self._evaluate(seg, args, env, trips)]
 
         def run(tree):
             for node in tree:
@@ -1362,7 +1464,8 @@ class ReduceRowsPlan(Plan):
         return ReduceRowsPlan(kernel.name, {
             "x": ld.arg, "out": st.arg, "block_rows": ld.shape[keep], "stride_keep": ld.strides[keep],
             "stride_red": ld.strides[axis], "x_off": off, "out_off": st.offset,
-            "n_valid": Poly.fn("minsi", mr[1], loop.ub), "row_start": mk[0] if mk is not None else None,
+            # columns the loop reaches: whole blocks, so a bound beyond `ub` still admits the last partial block
+            "n_valid": Poly.fn("minsi", mr[1], loop.trip * loop.step), "row_start": mk[0] if mk is not None else None,
             "row_bound": mk[1] if mk is not None else None})
 
     def __init__(self, name, params):
@@ -1429,7 +1532,7 @@ class ReduceAllPlan(Plan):
         if m is None or m[0] != loop.step * itp or other_bits(ld.other, "f32") != 0:
             raise UnsupportedTTIR("reduce_all family: load needs mask offs < n and other=0")
         return ReduceAllPlan(kernel.name, {"x": ld.arg, "out": st.arg, "x_off": off, "out_off": st.offset,
-                                           "stride": ld.strides[0], "n": Poly.fn("minsi", m[1], loop.ub)})
+                                           "stride": ld.strides[0], "n": Poly.fn("minsi", m[1], loop.trip * loop.step)})
 
     def launch(self, args, grid, pid_lo, pid_hi, stream):
         p = self.p
@@ -1641,10 +1744,11 @@ class GemmPlan(Plan):
             pk = ("split", pid_lo, pid_hi)
             sp = r.get(pk)
             if sp is None:
-                sp = r[pk] = self.pair_tiles(r["tiles"][pid_lo:pid_hi])
-            pairs, singles = sp
+                pr, sg = self.pair_tiles(r["tiles"][pid_lo:pid_hi])
+                sp = r[pk] = (pr, sg, _digest(pr), _digest(sg))
+            pairs, singles, key_pairs, key_singles = sp
             if len(pairs):
-                dev = args.device_table(("gemm_pairs", self.name, pid_lo, pid_hi) + key, pairs, stream)
+                dev = args.device_table(("gemm_pairs", key_pairs), pairs, stream)
                 rc = L.tsb_gemm_paired(*common, dev, len(pairs), status, stream)
                 if rc == -2:
                     r["no_pairs"] = True  # operands not eligible: the one-CTA entry decides (tensor or SIMT)
@@ -1652,15 +1756,25 @@ class GemmPlan(Plan):
                     if rc:
                         rt.check(rc, f"tsb_gemm_paired[{self.name}]")
                     if len(singles):
-                        dev1 = args.device_table(("gemm_singles", self.name, pid_lo, pid_hi) + key, singles, stream)
+                        dev1 = args.device_table(("gemm_singles", key_singles), singles, stream)
                         rc = L.tsb_gemm(*common, dev1, len(singles), 0, len(singles), status, stream)
                         if rc:
                             rt.check(rc, f"tsb_gemm[{self.name}]")
                     return
-        tiles_dev = args.device_table(("gemm_tiles", self.name) + key, r["tiles"], stream)
+        if "tiles_key" not in r:
+            r["tiles_key"] = _digest(r["tiles"])
+        tiles_dev = args.device_table(("gemm_tiles", r["tiles_key"]), r["tiles"], stream)
         rc = L.tsb_gemm(*common, tiles_dev, r["n_prog"], pid_lo, pid_hi, status, stream)
         if rc:
             rt.check(rc, f"tsb_gemm[{self.name}]")
+
+
+def _digest(table: np.ndarray):
+    """Key of a device-resident table: its shape and content (two plans, or two specialisations of
+    one kernel, share a table only when they would upload the same bytes)."""
+    import hashlib
+    a = np.ascontiguousarray(table)
+    return (a.shape, hashlib.sha1(a.tobytes()).digest())
 
 
 _FAMILIES = {c.family: c for c in (GemmPlan, LayerNormPlan, SoftmaxPlan, ReduceRowsPlan, ReduceAllPlan,

@@ -1,6 +1,7 @@
 // Library state shared by all entry points: error text, device properties.
 #include "tsb_common.cuh"
 #include <string.h>
+#include <stdlib.h>
 
 namespace tsb {
 
@@ -33,6 +34,21 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+int device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  return dev;
+}
+
+bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("TSB_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 }  // namespace tsb

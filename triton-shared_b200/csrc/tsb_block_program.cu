@@ -379,11 +379,8 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
   P.pid_lo = pid_lo; P.pid_hi = pid_hi;
   choose_program_order(P.acc, n_acc, P.grid, pid_lo, pid_hi, P.order);
   if (pid_hi == pid_lo) return TSB_OK;
-  static long long smem_set = 0;
-  if (smem > 48 * 1024 && smem_set < smem) {
-    TSB_CUDA_OK(cudaFuncSetAttribute(block_program_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    smem_set = 200 * 1024;
-  }
+  static SmemLimit smem_limit;
+  if (smem > 48 * 1024) TSB_CUDA_OK(allow_dynamic_smem(block_program_kernel, 200 * 1024, smem_limit));
   long long per_sm = smem > 0 ? (220 * 1024) / (smem + 1024) : 8;
   if (per_sm > 8) per_sm = 8;
   if (per_sm < 1) per_sm = 1;

@@ -31,6 +31,52 @@ int fail(int code, const char *fmt, ...);
   } while (0)
 
 int sm_count();
+// Current device ordinal clamped to [0, 64): index for per-device host-side caches.
+int device_slot();
+// Whether kernels are launched with programmatic stream serialization (default on; the
+// environment variable TSB_PDL=0 turns it off).
+bool pdl_enabled();
+
+// Raise a kernel's dynamic shared-memory limit.  The attribute belongs to the (function, device)
+// pair, so the high-water mark already set is remembered per device ordinal: a second device
+// used by the same process gets its own call.  A race between host threads at worst repeats it.
+struct SmemLimit {
+  int set[64];
+};
+template <typename K>
+inline cudaError_t allow_dynamic_smem(K kernel, size_t bytes, SmemLimit &st) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  const int d = device_slot();
+  if (st.set[d] >= (int)bytes) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) st.set[d] = (int)bytes;
+  return e;
+}
+
+// Programmatic dependent launch: a kernel launched through launch_pdl may become resident while
+// the kernel before it on the stream is still draining.  It must call grid_dependency_wait()
+// before its first access to global memory (the wait returns once the preceding kernel has
+// completed and its writes are visible) and calls grid_launch_dependents() once its own CTAs
+// no longer compete for SM slots.  Both are no-ops for a kernel launched the ordinary way, and a
+// preceding kernel that never signals simply releases its dependents when it completes.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __host__ __device__ inline int dtype_size(int dt) {
   switch (dt) {

@@ -11,6 +11,7 @@
 // The CPU backend materialises every block in a malloc'ed buffer and runs one
 // scalar loop per op; here a lane's values stay in registers from load to store.
 #include "tsb_vm.cuh"
+#include <stdlib.h>
 
 namespace tsb {
 
@@ -24,7 +25,14 @@ struct EwParams {
   int grid[3];
   int order[3];   // grid axes from fastest to slowest in the order programs are walked
   long long pid_lo, pid_hi;
+  int n_loops;               // perfect loop nest around the whole body (outermost first)
+  int trip[TSB_MAX_LOOPS];
+  long long total_trips;     // product of the trip counts
+  int indirect;              // some load/store takes a per-lane index or mask operand
 };
+
+// flags in the imm field of TSB_OP_LOAD / TSB_OP_STORE
+constexpr unsigned MEM_INDEX = 1u, MEM_MASK = 2u;
 
 // ---- general body: a small register VM ----------------------------------------
 // One pass over the op list for VEC lanes; `ld(access, regs)` and `st(access, regs)`
@@ -111,8 +119,11 @@ __device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R
 }
 
 // ld(access, u, regs) / st(access, u, regs) address sub-item u; inactive sub-items load zeros and store nothing
-template <int VEC, int U, typename LoadFn, typename StoreFn>
-__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC, U> R, LoadFn ld, StoreFn st) {
+// ldx / stx: the same with a per-lane element index added to the address and / or a per-lane
+// mask bit (flags MEM_INDEX, MEM_MASK): the data-dependent accesses of gather / scatter kernels.
+template <int VEC, int U, typename LoadFn, typename StoreFn, typename LoadXFn, typename StoreXFn>
+__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC, U> R, LoadFn ld, StoreFn st,
+                                        LoadXFn ldx, StoreXFn stx) {
   unsigned acc[U][VEC];
 #pragma unroll
   for (int u = 0; u < U; ++u)
@@ -122,8 +133,16 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRe
     const tsb_op &op = ops[k];
     switch (op.opcode) {
       case TSB_OP_LOAD:
+        if (op.imm & (MEM_INDEX | MEM_MASK)) {
+          unsigned ix[U][VEC], mk[U][VEC];
+          if (op.imm & MEM_INDEX) vm_fetch<VEC, U>(op, op.b, R, acc, ix);
+          if (op.imm & MEM_MASK) vm_fetch<VEC, U>(op, op.c, R, acc, mk);
 #pragma unroll
-        for (int u = 0; u < U; ++u) ld(op.a, u, acc[u]);  // all loads issued before the first use
+          for (int u = 0; u < U; ++u) ldx(op.a, u, op.imm, ix[u], mk[u], acc[u]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < U; ++u) ld(op.a, u, acc[u]);  // all loads issued before the first use
+        }
         if (op.dst >= 0) {
 #pragma unroll
           for (int u = 0; u < U; ++u) R.put(op.dst, u, acc[u]);
@@ -134,8 +153,16 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRe
         {
           unsigned t[U][VEC];
           vm_fetch<VEC, U>(op, op.b, R, acc, t);
+          if (op.imm & (MEM_INDEX | MEM_MASK)) {
+            unsigned ix[U][VEC], mk[U][VEC];
+            if (op.imm & MEM_INDEX) vm_fetch<VEC, U>(op, op.c, R, acc, ix);
+            if (op.imm & MEM_MASK) vm_fetch<VEC, U>(op, op.dst, R, acc, mk);
 #pragma unroll
-          for (int u = 0; u < U; ++u) st(op.a, u, t[u]);
+            for (int u = 0; u < U; ++u) stx(op.a, u, op.imm, ix[u], mk[u], t[u]);
+          } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) st(op.a, u, t[u]);
+          }
         }
         break;
       case TSB_OP_CONST:
@@ -155,6 +182,156 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRe
   }
 }
 
+// ---- register-resident VM ------------------------------------------------------------------
+// Bodies that need at most NR registers besides the accumulator run with the whole register file
+// in hardware registers: register r of a thread is U lane-vectors of VEC words held in an array
+// that is only ever indexed by compile-time constants (a run-time register number selects a
+// `case` of a switch, never an array slot), so nothing touches shared or local memory.  Operand
+// a of an op is brought into the accumulator (no work when it already is the accumulator, the
+// usual case), operand b into a scratch vector, and the result replaces the accumulator: about
+// two instructions per lane and op plus the decode shared by U*VEC lanes.
+template <int VEC, int U, int NR>
+struct RegFile {
+  unsigned r[NR][U][VEC];
+};
+
+#define TSB_RVM_WITH_REG(idx, F)                  \
+  switch (idx) {                                  \
+    case 0: F(0); break;                          \
+    case 1: if (NR > 1) { F(1 % NR); } break;     \
+    default: if (NR > 2) { F(2 % NR); } break;    \
+  }
+
+// v <- operand `which`: a register, the accumulator or the op's immediate
+template <int VEC, int U, int NR>
+__device__ __forceinline__ void rvm_fetch(const tsb_op &op, int which, const RegFile<VEC, U, NR> &R,
+                                          const unsigned (&acc)[U][VEC], unsigned (&v)[U][VEC]) {
+  if (which == TSB_REG_ACC) {
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[u][k] = acc[u][k];
+  } else if (which == TSB_REG_IMM) {
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[u][k] = op.imm2;
+  } else {
+#define TSB_F(I) _Pragma("unroll") for (int u = 0; u < U; ++u) _Pragma("unroll") for (int k = 0; k < VEC; ++k) v[u][k] = R.r[I][u][k]
+    TSB_RVM_WITH_REG(which, TSB_F)
+#undef TSB_F
+  }
+}
+
+template <int VEC, int U, int NR>
+__device__ __forceinline__ void rvm_put(int dst, RegFile<VEC, U, NR> &R, const unsigned (&acc)[U][VEC]) {
+  if (dst < 0) return;
+#define TSB_F(I) _Pragma("unroll") for (int u = 0; u < U; ++u) _Pragma("unroll") for (int k = 0; k < VEC; ++k) R.r[I][u][k] = acc[u][k]
+  TSB_RVM_WITH_REG(dst, TSB_F)
+#undef TSB_F
+}
+
+// one lane-vector of an operand (three-operand ops keep their scratch to VEC words per operand)
+template <int VEC, int U, int NR>
+__device__ __forceinline__ void rvm_fetch_u(const tsb_op &op, int which, const RegFile<VEC, U, NR> &R,
+                                            const unsigned (&acc)[U][VEC], int u, unsigned (&v)[VEC]) {
+  if (which == TSB_REG_ACC) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v[k] = acc[u][k];
+  } else if (which == TSB_REG_IMM) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v[k] = op.imm2;
+  } else {
+#define TSB_F(I) _Pragma("unroll") for (int k = 0; k < VEC; ++k) v[k] = R.r[I][u][k]
+    TSB_RVM_WITH_REG(which, TSB_F)
+#undef TSB_F
+  }
+}
+
+template <int OPC, int VEC, int U, int NR>
+__device__ __forceinline__ void rvm_alu(const tsb_op &op, RegFile<VEC, U, NR> &R, unsigned (&acc)[U][VEC]) {
+  constexpr int AR = alu_arity<OPC>();
+  if constexpr (AR >= 3) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      unsigned a[VEC], b[VEC], c[VEC];
+      rvm_fetch_u<VEC, U, NR>(op, op.a, R, acc, u, a);
+      rvm_fetch_u<VEC, U, NR>(op, op.b, R, acc, u, b);
+      rvm_fetch_u<VEC, U, NR>(op, op.c, R, acc, u, c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[u][k] = alu_op<OPC, false>(op, a[k], b[k], c[k]);
+    }
+  } else {
+    unsigned b[U][VEC];
+    // b first: it may name the accumulator, which operand a is about to replace
+    if (AR >= 2) rvm_fetch<VEC, U, NR>(op, op.b, R, acc, b);
+    if (op.a != TSB_REG_ACC) rvm_fetch<VEC, U, NR>(op, op.a, R, acc, acc);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[u][k] = alu_op<OPC, false>(op, acc[u][k], AR >= 2 ? b[u][k] : 0u, 0u);
+  }
+  if (alu_rounds<OPC>() && op.type != TSB_F32) {
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[u][k] = __float_as_uint(round_to(__uint_as_float(acc[u][k]), op.type));
+  }
+  rvm_put<VEC, U, NR>(op.dst, R, acc);
+}
+
+template <int VEC, int U, int NR, typename LoadFn, typename StoreFn>
+__device__ __forceinline__ void rvm_exec(const tsb_op *ops, int n_ops, LoadFn ld, StoreFn st) {
+  RegFile<VEC, U, NR> R;
+  unsigned acc[U][VEC];
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      acc[u][k] = 0u;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) R.r[r][u][k] = 0u;
+    }
+  for (int i = 0; i < n_ops; ++i) {
+    const tsb_op &op = ops[i];
+    switch (op.opcode) {
+      case TSB_OP_LOAD:
+        ld(op.a, acc);
+        rvm_put<VEC, U, NR>(op.dst, R, acc);
+        break;
+      case TSB_OP_STORE:
+        if (op.b != TSB_REG_ACC) rvm_fetch<VEC, U, NR>(op, op.b, R, acc, acc);
+        st(op.a, acc);
+        break;
+      case TSB_OP_CONST:
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) acc[u][k] = op.imm;
+        rvm_put<VEC, U, NR>(op.dst, R, acc);
+        break;
+#define TSB_VM_CASE(O) \
+  case O: rvm_alu<O, VEC, U, NR>(op, R, acc); break;
+        TSB_ALU_OPCODES(TSB_VM_CASE)
+#undef TSB_VM_CASE
+      default: break;
+    }
+  }
+}
+
+// Decode the flat iteration number q of a perfect loop nest into per-level counters.
+__device__ __forceinline__ void loop_counters(const EwParams &P, long long q, int it[TSB_MAX_LOOPS]) {
+#pragma unroll
+  for (int l = TSB_MAX_LOOPS - 1; l >= 0; --l) {
+    if (l < P.n_loops) {
+      it[l] = (int)(q % P.trip[l]);
+      q /= P.trip[l];
+    } else {
+      it[l] = 0;
+    }
+  }
+}
+
 template <int VEC, int U>
 __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwParams P) {
   extern __shared__ __align__(16) unsigned vm_smem[];
@@ -162,35 +339,110 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
   const VmRegs<VEC, U> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
   const int items = P.lanes / VEC;
   const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
+  grid_dependency_wait();
+  grid_launch_dependents();
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
     long long px, py, pz;
     split_pid(P.grid, P.order, prog, px, py, pz);
-    __syncthreads();  // the previous program's state is no longer read
-    if (threadIdx.x < P.n_acc) program_state(P.acc[threadIdx.x], P.size, px, py, pz, st[threadIdx.x]);
-    __syncthreads();
-    for (int it0 = threadIdx.x; it0 < items; it0 += blockDim.x * U) {
-      auto coords = [&](int u, int &i0, int &i1, int &i2) {
-        const int it = it0 + u * (int)blockDim.x;
-        const int l = it * VEC;
-        i2 = l & (P.size[2] - 1);
-        i1 = (l >> sh1) & (P.size[1] - 1);
-        i0 = l >> sh0;
-        return it < items;
-      };
-      vm_exec<VEC, U>(
-          P.ops, P.n_ops, R,
-          [&](int a, int u, unsigned(&r)[VEC]) {
-            int i0, i1, i2;
-            if (coords(u, i0, i1, i2)) {
-              load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
-            } else {
+    // a loop nest around the body runs here, in order, one iteration after the other: a later
+    // iteration sees what an earlier one of the same program stored
+    for (long long q = 0; q < P.total_trips; ++q) {
+      int it[TSB_MAX_LOOPS];
+      loop_counters(P, q, it);
+      __threadfence_block();
+      __syncthreads();  // the previous program's (iteration's) state is no longer read
+      if (threadIdx.x < P.n_acc) program_state_loops(P.acc[threadIdx.x], P.size, px, py, pz, it, st[threadIdx.x]);
+      __syncthreads();
+      for (int it0 = threadIdx.x; it0 < items; it0 += blockDim.x * U) {
+        auto coords = [&](int u, int &i0, int &i1, int &i2) {
+          const int itm = it0 + u * (int)blockDim.x;
+          const int l = itm * VEC;
+          i2 = l & (P.size[2] - 1);
+          i1 = (l >> sh1) & (P.size[1] - 1);
+          i0 = l >> sh0;
+          return itm < items;
+        };
+        vm_exec<VEC, U>(
+            P.ops, P.n_ops, R,
+            [&](int a, int u, unsigned(&r)[VEC]) {
+              int i0, i1, i2;
+              if (coords(u, i0, i1, i2)) {
+                load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
+              } else {
 #pragma unroll
-              for (int v = 0; v < VEC; ++v) r[v] = 0u;
+                for (int v = 0; v < VEC; ++v) r[v] = 0u;
+              }
+            },
+            [&](int a, int u, const unsigned(&r)[VEC]) {
+              int i0, i1, i2;
+              if (coords(u, i0, i1, i2)) store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
+            },
+            [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC], unsigned(&r)[VEC]) {
+              int i0, i1, i2;
+              if (coords(u, i0, i1, i2)) {
+                load_vec_indirect<VEC>(P.acc[a], st[a], i0, i1, i2, flags & MEM_INDEX, flags & MEM_MASK, ix, mk, r);
+              } else {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) r[v] = 0u;
+              }
+            },
+            [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC],
+                const unsigned(&r)[VEC]) {
+              int i0, i1, i2;
+              if (coords(u, i0, i1, i2))
+                store_vec_indirect<VEC>(P.acc[a], st[a], i0, i1, i2, flags & MEM_INDEX, flags & MEM_MASK, ix, mk, r);
+            });
+      }
+    }
+  }
+}
+
+// Register-resident form of the blocked kernel.  A program of `items` lane-vectors is shared by
+// G = items / U consecutive threads, each carrying U vectors G apart (consecutive threads touch
+// consecutive vectors); programs are dealt to thread groups in the walk order of the launch, so
+// a CTA of 256 threads works on 256 / G programs at once and small blocks still fill it.  Each
+// thread derives the program's access state itself when the body reaches the load or store.
+template <int NR>
+__global__ void __launch_bounds__(256, 2) ew_rvm_kernel(const __grid_constant__ EwParams P, int lg_g) {
+  constexpr int VEC = 4, U = 4;
+  const int G = 1 << lg_g;
+  const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
+  const long long n_threads = (P.pid_hi - P.pid_lo) << lg_g;
+  grid_dependency_wait();
+  grid_launch_dependents();
+  for (long long base = (long long)blockIdx.x * blockDim.x; base < n_threads; base += (long long)gridDim.x * blockDim.x) {
+    const long long g = base + threadIdx.x;
+    const bool live = g < n_threads;
+    const int within = (int)(g & (G - 1));
+    long long px = 0, py = 0, pz = 0;
+    if (live) split_pid(P.grid, P.order, P.pid_lo + (g >> lg_g), px, py, pz);
+    for (long long q = 0; q < P.total_trips; ++q) {
+      int it[TSB_MAX_LOOPS];
+      loop_counters(P, q, it);
+      if (P.n_loops) {  // later iterations of a program see the stores of earlier ones (same CTA)
+        __threadfence_block();
+        __syncthreads();
+      }
+      if (!live) continue;
+      rvm_exec<VEC, U, NR>(
+          P.ops, P.n_ops,
+          [&](int a, unsigned(&r)[U][VEC]) {
+            ProgState ps;
+            program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int l = (within + u * G) * VEC;
+              load_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r[u]);
             }
           },
-          [&](int a, int u, const unsigned(&r)[VEC]) {
-            int i0, i1, i2;
-            if (coords(u, i0, i1, i2)) store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
+          [&](int a, const unsigned(&r)[U][VEC]) {
+            ProgState ps;
+            program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int l = (within + u * G) * VEC;
+              store_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r[u]);
+            }
           });
     }
   }
@@ -508,6 +760,39 @@ __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__
         [&](int a, int u, const unsigned(&r)[4]) {
           const long long v = v0 + (long long)u * blockDim.x;
           if (v < n_vec) flat_store(P.acc[a], P.g_lo + v * 4, r);
+        },
+        [&](int, int, unsigned, const unsigned(&)[4], const unsigned(&)[4], unsigned(&)[4]) {},
+        [&](int, int, unsigned, const unsigned(&)[4], const unsigned(&)[4], const unsigned(&)[4]) {});
+  }
+}
+
+template <int NR>
+__global__ void __launch_bounds__(256, 2) ew_flat_rvm_kernel(const __grid_constant__ FlatParams P) {
+  constexpr int U = FLAT_VM_U;
+  const long long n_vec = (P.g_hi - P.g_lo) >> 2;
+  const long long step = (long long)gridDim.x * blockDim.x * U;
+  grid_dependency_wait();
+  grid_launch_dependents();
+  for (long long v0 = (long long)blockIdx.x * blockDim.x * U + threadIdx.x; v0 < n_vec; v0 += step) {
+    rvm_exec<4, U, NR>(
+        P.ops, P.n_ops,
+        [&](int a, unsigned(&r)[U][4]) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < n_vec) {
+              flat_load(P.acc[a], P.g_lo + v * 4, r[u]);
+            } else {
+              r[u][0] = r[u][1] = r[u][2] = r[u][3] = 0u;
+            }
+          }
+        },
+        [&](int a, const unsigned(&r)[U][4]) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < n_vec) flat_store(P.acc[a], P.g_lo + v * 4, r[u]);
+          }
         });
   }
 }
@@ -515,7 +800,7 @@ __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__
 
 static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
                         const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, EwParams &P,
-                        int &vec) {
+                        int &vec) {  // on return P.ops / P.n_ops hold the body without its loop ops
   if (!acc || !ops || !grid) return fail(TSB_ERR_INVALID, "tsb_elementwise: null argument");
   if (n_acc < 1 || n_acc > TSB_MAX_ACCESSES)
     return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: %d accesses (max %d)", n_acc, TSB_MAX_ACCESSES);
@@ -546,10 +831,38 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
     int rc = convert_access(acc, a, rank, P.size, grid, vec, P.acc[a]);
     if (rc != TSB_OK) return rc;
   }
+  // a perfect loop nest around the whole body: leading LOOP_BEGINs (slot = nesting depth, imm =
+  // trip count) matched by trailing LOOP_ENDs
+  int n_loops = 0;
+  while (n_loops < n_ops && ops[n_loops].opcode == TSB_OP_LOOP_BEGIN) ++n_loops;
+  if (n_loops > TSB_MAX_LOOPS) return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: loops nested %d deep (max %d)", n_loops, TSB_MAX_LOOPS);
+  if (n_ops < 2 * n_loops + 1) return fail(TSB_ERR_INVALID, "tsb_elementwise: loop ops without a body");
+  P.total_trips = 1;
+  for (int l = 0; l < n_loops; ++l) {
+    const tsb_op &b = ops[l], &e = ops[n_ops - 1 - l];
+    if (b.a != l || e.opcode != TSB_OP_LOOP_END || e.a != l)
+      return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: loops must form one perfect nest around the whole body");
+    P.trip[l] = (int)b.imm;
+    if ((long long)b.imm > 0x7fffffffll) return fail(TSB_ERR_INVALID, "tsb_elementwise: trip count %u", b.imm);
+    P.total_trips *= (long long)b.imm;
+    if (P.total_trips > (1ll << 40)) return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: loop nest of more than 2^40 iterations");
+  }
+  P.n_loops = n_loops;
+  ops += n_loops;
+  n_ops -= 2 * n_loops;
+  for (int a = 0; a < n_acc; ++a)
+    for (int l = n_loops; l < TSB_MAX_LOOPS; ++l) {
+      P.acc[a].off_loop[l] = 0;
+      for (int d = 0; d < 3; ++d) P.acc[a].mstart_loop[d][l] = 0;
+    }
+  auto reg_ok = [](int r) { return r >= TSB_REG_IMM && r < TSB_NUM_REGS; };
   for (int k = 0; k < n_ops; ++k) {
     const tsb_op &o = ops[k];
     P.ops[k] = o;
     const bool is_mem = o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_STORE;
+    if (o.opcode == TSB_OP_LOOP_BEGIN || o.opcode == TSB_OP_LOOP_END || o.opcode == TSB_OP_REDUCE ||
+        o.opcode == TSB_OP_ARGREDUCE)
+      return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: op %d (opcode %d) is not an elementwise op", k, o.opcode);
     if (is_mem && (o.a < 0 || o.a >= n_acc))
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d names access %d of %d", k, o.a, n_acc);
     if (o.opcode == TSB_OP_LOAD && acc[o.a].is_store == 1)
@@ -558,11 +871,20 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d stores to a load access", k);
     if (o.opcode != TSB_OP_STORE && (o.dst < TSB_REG_ACC || o.dst >= TSB_NUM_REGS))
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, o.dst);
-    const int regs[3] = {is_mem || o.opcode == TSB_OP_CONST ? 0 : o.a,
-                         o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_CONST ? 0 : o.b,
+    if (is_mem) {
+      if (o.imm & ~(MEM_INDEX | MEM_MASK)) return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d has memory flags %u", k, o.imm);
+      if (o.imm) P.indirect = 1;
+      const int ix = o.opcode == TSB_OP_LOAD ? o.b : o.c, mk = o.opcode == TSB_OP_LOAD ? o.c : o.dst;
+      if (((o.imm & MEM_INDEX) && (!reg_ok(ix) || ix == TSB_REG_IMM)) || ((o.imm & MEM_MASK) && (!reg_ok(mk) || mk == TSB_REG_IMM)))
+        return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d index or mask operand out of range", k);
+      if (o.opcode == TSB_OP_STORE && !reg_ok(o.b))
+        return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, o.b);
+      continue;
+    }
+    const int regs[3] = {o.opcode == TSB_OP_CONST ? 0 : o.a, o.opcode == TSB_OP_CONST ? 0 : o.b,
                          (o.opcode == TSB_OP_SELECT || o.opcode == TSB_OP_FMA) ? o.c : 0};
     for (int r = 0; r < 3; ++r) {
-      if (regs[r] < TSB_REG_IMM || regs[r] >= TSB_NUM_REGS)
+      if (!reg_ok(regs[r]))
         return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, regs[r]);
       if (regs[r] == TSB_REG_IMM && o.opcode == TSB_OP_CAST)
         return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d: a cast cannot take an immediate operand", k);
@@ -677,46 +999,63 @@ static bool is_fast_binary(const tsb_access *acc, const tsb_op *ops, int n_ops, 
 
 using namespace tsb;
 
-extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
+constexpr int RVM_REGS = 3;  // registers of the hardware-register VM (besides the accumulator)
+
+// TSB_RVM=0 in the environment keeps every body on the shared-memory VM (for comparisons).
+static bool rvm_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("TSB_RVM");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *ops_in, int n_ops_in,
                                const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, void *stream) {
   static thread_local EwParams P;
   int vec = 1;
-  int rc = build_params(acc, n_acc, ops, n_ops, grid, pid_lo, pid_hi, P, vec);
+  int rc = build_params(acc, n_acc, ops_in, n_ops_in, grid, pid_lo, pid_hi, P, vec);
   if (rc != TSB_OK) return rc;
+  const tsb_op *ops = P.ops;  // the body without its loop ops
+  const int n_ops = P.n_ops;
   const long long n_prog = pid_hi - pid_lo;
-  if (n_prog == 0) return TSB_OK;
+  if (n_prog == 0 || P.total_trips == 0) return TSB_OK;
   const int items = P.lanes / vec;
   int threads = items >= 256 ? 256 : (items >= 128 ? 128 : (items >= 64 ? 64 : 32));
   const long long max_ctas = (long long)sm_count() * (2048 / threads) * 4;
   cudaStream_t s = (cudaStream_t)stream;
+  const bool plain = P.n_loops == 0 && !P.indirect;  // eligible for the flat and the dedicated kernels
   bool swapped = false;
-  const bool fast_binary = is_fast_binary(acc, ops, n_ops, swapped);
+  const bool fast_binary = plain && is_fast_binary(acc, ops, n_ops, swapped);
   if (fast_binary && swapped) {  // the fast kernels take ops[0] as the load of operand a
     const int t = P.ops[0].a;
     P.ops[0].a = P.ops[1].a;
     P.ops[1].a = t;
   }
+  const int regs_used = vm_regs_used(ops, n_ops);
+  const bool rvm = rvm_enabled() && !P.indirect && regs_used <= RVM_REGS && vec == 4;
   static thread_local FlatParams F;
-  if (build_flat(P, vec, F)) {
+  if (plain && build_flat(P, vec, F)) {
     const long long n_vec = (F.g_hi - F.g_lo) / 4;
     const bool fast = fast_binary;
     // the VM's register file lives in shared memory: fewer threads per CTA when the body uses many registers
     int flat_threads = 256;
-    const size_t regs_bytes = (size_t)vm_regs_used(ops, n_ops) * FLAT_VM_U * 4 * sizeof(unsigned);
-    while (!fast && regs_bytes * flat_threads > 96 * 1024 && flat_threads > 32) flat_threads /= 2;
+    const size_t regs_bytes = (size_t)regs_used * FLAT_VM_U * 4 * sizeof(unsigned);
+    while (!fast && !rvm && regs_bytes * flat_threads > 96 * 1024 && flat_threads > 32) flat_threads /= 2;
     const long long per_cta = fast ? 256ll * FLAT_UNROLL : (long long)flat_threads * FLAT_VM_U;
     long long ctas = (n_vec + per_cta - 1) / per_cta;
     const long long cap = (long long)sm_count() * 8 * 4;
     if (ctas > cap) ctas = cap;
     if (fast) {
       ew_flat_binary_f32_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
+    } else if (rvm) {
+      TSB_CUDA_OK(launch_pdl(ew_flat_rvm_kernel<RVM_REGS>, dim3((unsigned)ctas), dim3(256), 0, s, F));
+      return TSB_OK;
     } else {
       const size_t smem = regs_bytes * flat_threads;
-      static size_t set_flat = 0;
-      if (smem > 48 * 1024 && set_flat < smem) {
-        TSB_CUDA_OK(cudaFuncSetAttribute(ew_flat_vm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        set_flat = 200 * 1024;
-      }
+      static SmemLimit lim_flat;
+      if (smem > 48 * 1024) TSB_CUDA_OK(allow_dynamic_smem(ew_flat_vm_kernel, 200 * 1024, lim_flat));
       ew_flat_vm_kernel<<<(unsigned)ctas, flat_threads, smem, s>>>(F);
     }
     TSB_LAUNCH_OK("ew_flat_kernel");
@@ -730,7 +1069,7 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     TSB_LAUNCH_OK("ew_binary_f32_kernel");
     return TSB_OK;
   }
-  if (is_copy(acc, ops, n_ops)) {
+  if (plain && is_copy(acc, ops, n_ops)) {
     long long ctas = n_prog < max_ctas ? n_prog : max_ctas;
     if (copy2d_ok(P, grid)) {
       ew_copy2d_kernel<<<(unsigned)ctas, 256, 0, s>>>(P);
@@ -742,19 +1081,29 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     TSB_LAUNCH_OK("ew_copy_kernel");
     return TSB_OK;
   }
+  if (rvm && items >= 4) {
+    // items / 4 threads per program, 256 / that many programs per CTA pass
+    int lg_g = 0;
+    while ((4 << (lg_g + 1)) <= items && lg_g < 8) ++lg_g;  // G = items / 4, at most 256
+    const long long n_thr = n_prog << lg_g;
+    long long ctas = (n_thr + 255) / 256;
+    const long long cap = (long long)sm_count() * 2 * 8;
+    if (ctas > cap) ctas = cap;
+    TSB_CUDA_OK(launch_pdl(ew_rvm_kernel<RVM_REGS>, dim3((unsigned)ctas), dim3(256), 0, s, P, lg_g));
+    return TSB_OK;
+  }
   // four lane-vectors per thread when the block is large enough to keep at least a warp busy
   const int U = (vec == 4 && items >= 128) ? 4 : 1;
   if (U == 4) {
     threads = items / 4 >= 256 ? 256 : (items / 4 >= 128 ? 128 : (items / 4 >= 64 ? 64 : 32));
   }
-  while ((size_t)vm_regs_used(ops, n_ops) * U * vec * threads * sizeof(unsigned) > 96 * 1024 && threads > 32) threads /= 2;
+  while ((size_t)regs_used * U * vec * threads * sizeof(unsigned) > 96 * 1024 && threads > 32) threads /= 2;
   long long ctas = n_prog < max_ctas ? n_prog : max_ctas;
-  const size_t smem = (size_t)vm_regs_used(ops, n_ops) * U * vec * threads * sizeof(unsigned);
-  static size_t set_vm = 0;
-  if (smem > 48 * 1024 && set_vm < smem) {
-    TSB_CUDA_OK(cudaFuncSetAttribute(ew_vm_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    TSB_CUDA_OK(cudaFuncSetAttribute(ew_vm_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    set_vm = 200 * 1024;
+  const size_t smem = (size_t)regs_used * U * vec * threads * sizeof(unsigned);
+  static SmemLimit lim44, lim41;
+  if (smem > 48 * 1024) {
+    TSB_CUDA_OK(allow_dynamic_smem(ew_vm_kernel<4, 4>, 200 * 1024, lim44));
+    TSB_CUDA_OK(allow_dynamic_smem(ew_vm_kernel<4, 1>, 200 * 1024, lim41));
   }
   if (U == 4) ew_vm_kernel<4, 4><<<(unsigned)ctas, threads, smem, s>>>(P);
   else if (vec == 4) ew_vm_kernel<4, 1><<<(unsigned)ctas, threads, smem, s>>>(P);

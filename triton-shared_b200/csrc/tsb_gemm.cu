@@ -441,11 +441,8 @@ extern "C" int tsb_gemm(const void *a, const void *b, void *c, int32_t dtype, in
     if (stages < 2) return fail(TSB_ERR_UNSUPPORTED, "tsb_gemm: block does not fit two pipeline stages");
     P.stages = stages;
     const int smem = stages * stage_bytes + 1024;
-    static int smem_set = 0;
-    if (smem_set < smem) {
-      TSB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      smem_set = smem;
-    }
+    static SmemLimit smem_limit;
+    TSB_CUDA_OK(allow_dynamic_smem(gemm_tcgen05_kernel, smem, smem_limit));
     long long ctas = pid_hi - pid_lo;
     if (ctas > sm_count()) ctas = sm_count();
     gemm_tcgen05_kernel<<<(unsigned)ctas, GEMM_THREADS, smem, s>>>(map_a, map_b, P);

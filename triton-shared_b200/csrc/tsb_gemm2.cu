@@ -352,11 +352,8 @@ extern "C" int tsb_gemm_paired(const void *a, const void *b, void *c, int32_t dt
   if (stages < 2) return fail(TSB_ERR_UNSUPPORTED, "tsb_gemm_paired: block does not fit two pipeline stages");
   P.stages = stages;
   const int smem = stages * stage_bytes + 1024;
-  static int smem_set = 0;
-  if (smem_set < smem) {
-    TSB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    smem_set = smem;
-  }
+  static SmemLimit smem_limit;
+  TSB_CUDA_OK(allow_dynamic_smem(gemm_tcgen05_pair_kernel, smem, smem_limit));
   long long clusters = n_pairs;
   const long long max_clusters = sm_count() / 2;
   if (clusters > max_clusters) clusters = max_clusters;

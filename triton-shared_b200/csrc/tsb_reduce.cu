@@ -8,6 +8,7 @@
 // The CPU backend copies each ragged block element by element
 // (CRunnerUtils.cpp:58-113) and folds left to right on one thread.
 #include "tsb_common.cuh"
+#include <cooperative_groups.h>
 
 namespace tsb {
 
@@ -22,17 +23,23 @@ constexpr int RC_WARPS = 8;
 constexpr int RC_UNROLL = 8;
 constexpr int RC_TILE = 128;
 
-template <bool VEC4>
+// CLUSTER: the CTAs that share a row tile (blockIdx.y = split) form one thread-block cluster.
+// Each leaves its 128 partial sums in its own shared memory; after a cluster barrier the CTA of
+// rank 0 adds them in split order through distributed shared memory and writes the row sums, so
+// that the whole reduction is one launch with no global scratch and a fixed order of additions.
+template <bool VEC4, bool CLUSTER>
 __global__ void __launch_bounds__(RC_WARPS * 32)
 reduce_rows_contig_m_kernel(const float *__restrict__ x, float *__restrict__ dst,
                             long long dst_stride_i, long long dst_stride_split, long long stride_n,
                             long long n_valid, long long row_lo, long long row_hi, int j_per_split) {
   __shared__ float red[RC_WARPS][RC_TILE];
+  __shared__ float tile_sum[RC_TILE];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long tile0 = row_lo + (long long)blockIdx.x * RC_TILE;
   const long long j_lo = (long long)blockIdx.y * j_per_split;
   long long j_hi = j_lo + j_per_split;
   if (j_hi > n_valid) j_hi = n_valid;
+  grid_dependency_wait();
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   if (VEC4 && tile0 + RC_TILE <= row_hi) {
     const float *p = x + tile0 + lane * 4;
@@ -42,14 +49,14 @@ reduce_rows_contig_m_kernel(const float *__restrict__ x, float *__restrict__ dst
       float4 q[RC_UNROLL];
 #pragma unroll
       for (int u = 0; u < RC_UNROLL; ++u)
-        q[u] = __ldg(reinterpret_cast<const float4 *>(p + (j + u * RC_WARPS) * stride_n));
+        q[u] = __ldcs(reinterpret_cast<const float4 *>(p + (j + u * RC_WARPS) * stride_n));
 #pragma unroll
       for (int u = 0; u < RC_UNROLL; ++u) {
         acc[0] += q[u].x; acc[1] += q[u].y; acc[2] += q[u].z; acc[3] += q[u].w;
       }
     }
     for (; j < j_hi; j += RC_WARPS) {
-      float4 q = __ldg(reinterpret_cast<const float4 *>(p + j * stride_n));
+      float4 q = __ldcs(reinterpret_cast<const float4 *>(p + j * stride_n));
       acc[0] += q.x; acc[1] += q.y; acc[2] += q.z; acc[3] += q.w;
     }
 #pragma unroll
@@ -64,14 +71,31 @@ reduce_rows_contig_m_kernel(const float *__restrict__ x, float *__restrict__ dst
 #pragma unroll
     for (int k = 0; k < 4; ++k) red[warp][lane + 32 * k] = acc[k];
   }
+  grid_launch_dependents();
   __syncthreads();
   // 128 row sums per CTA, combined over the 8 warps in a fixed order
+  float s = 0.f;
   if (threadIdx.x < RC_TILE) {
     const int r = threadIdx.x;
-    float s = red[0][r];
+    s = red[0][r];
 #pragma unroll
     for (int w = 1; w < RC_WARPS; ++w) s += red[w][r];
-    const long long i = tile0 + r;
+  }
+  if (CLUSTER) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x < RC_TILE) tile_sum[threadIdx.x] = s;
+    cluster.sync();  // every split's partial sums are in place
+    if (cluster.block_rank() == 0 && threadIdx.x < RC_TILE) {
+      const unsigned n = cluster.num_blocks();
+      float t = tile_sum[threadIdx.x];
+      for (unsigned k = 1; k < n; ++k) t += cluster.map_shared_rank(tile_sum, k)[threadIdx.x];  // split order
+      const long long i = tile0 + threadIdx.x;
+      if (i < row_hi) dst[(i - row_lo) * dst_stride_i] = t;
+    }
+    cluster.sync();  // no CTA leaves while its shared memory may still be read
+  } else if (threadIdx.x < RC_TILE) {
+    const long long i = tile0 + threadIdx.x;
     if (i < row_hi) dst[(i - row_lo) * dst_stride_i + (long long)blockIdx.y * dst_stride_split] = s;
   }
 }
@@ -129,6 +153,8 @@ __global__ void reduce_rows_generic_kernel(const float *__restrict__ x, float *_
 __global__ void __launch_bounds__(1024)
 reduce_all_kernel(const float *__restrict__ x, float *__restrict__ out, long long n, long long stride) {
   __shared__ float red[32];
+  grid_dependency_wait();
+  grid_launch_dependents();
   float s = 0.f;
   for (long long i = threadIdx.x; i < n; i += 1024) s += __ldg(x + i * stride);
   s = warp_sum(s);
@@ -145,7 +171,39 @@ struct ContigMPlan {
   long long i_tiles;
   int splits;
   int j_per_split;
+  bool cluster;  // the splits of a row tile form one cluster (no scratch, one launch)
 };
+
+constexpr int RC_MAX_CLUSTER = 16;  // 8 is the portable limit; 16 is opted into per device
+
+// Largest cluster (splits per row tile) this device schedules for the kernel: 16 where the
+// non-portable size is available, else the portable 8.  Asked once per device.
+static int max_cluster_splits() {
+  static int cached[64];
+  const int dev = device_slot();
+  if (cached[dev]) return cached[dev];
+  int best = 8;
+  auto kern = reduce_rows_contig_m_kernel<true, true>;
+  auto kern2 = reduce_rows_contig_m_kernel<false, true>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+      cudaFuncSetAttribute(kern2, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, RC_MAX_CLUSTER, 1);
+    cfg.blockDim = dim3(RC_WARPS * 32, 1, 1);
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1;
+    at[0].val.clusterDim.y = RC_MAX_CLUSTER;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) best = RC_MAX_CLUSTER;
+  }
+  (void)cudaGetLastError();  // a refused query is an answer, not an error of the caller
+  cached[dev] = best;
+  return best;
+}
 
 // Depends on the problem shape only, so that the scratch size a caller asked
 // for earlier always matches the launch.
@@ -158,11 +216,44 @@ static ContigMPlan plan_contig_m(long long n_rows, long long n_valid) {
   if (want > max_splits) want = max_splits;
   if (want > 1024) want = 1024;
   if (want < 1) want = 1;
+  // With enough row tiles, 16 splits per tile already put four or more CTAs on every SM: then
+  // the splits are combined inside a cluster.  Fewer tiles need more splits than a cluster holds
+  // and go through partial sums in scratch memory.
+  p.cluster = want > 1 && want <= 4 * RC_MAX_CLUSTER;
+  if (p.cluster) {
+    int c = 1;
+    const int cmax = max_cluster_splits();
+    while (c < want && c < cmax) c *= 2;
+    want = c;
+  }
   p.j_per_split = (int)((n_valid + want - 1) / want);
   if (p.j_per_split < 1) p.j_per_split = 1;
-  p.splits = (int)((n_valid + p.j_per_split - 1) / p.j_per_split);
+  p.splits = p.cluster ? (int)want : (int)((n_valid + p.j_per_split - 1) / p.j_per_split);
   if (p.splits < 1) p.splits = 1;
   return p;
+}
+
+template <bool VEC4>
+static int launch_contig_m_cluster(const ContigMPlan &p, const float *x, float *out, long long out_stride,
+                                   long long stride_n, long long n_valid, long long row_lo, long long row_hi,
+                                   cudaStream_t s) {
+  auto kern = reduce_rows_contig_m_kernel<VEC4, true>;  // cluster sizes above 8: see max_cluster_splits()
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)p.i_tiles, (unsigned)p.splits, 1);
+  cfg.blockDim = dim3(RC_WARPS * 32, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 1;
+  at[0].val.clusterDim.y = (unsigned)p.splits;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, x, out + row_lo * out_stride, out_stride, 0ll, stride_n, n_valid, row_lo,
+                                 row_hi, p.j_per_split));
+  return TSB_OK;
 }
 
 }  // namespace tsb
@@ -174,7 +265,7 @@ extern "C" int64_t tsb_reduce_rows_scratch_bytes(int64_t n_rows, int64_t n_valid
   (void)stride_n;
   if (n_rows <= 0 || n_valid <= 0 || stride_m != 1) return 0;
   ContigMPlan p = plan_contig_m(n_rows, n_valid);
-  return p.splits > 1 ? (int64_t)p.splits * n_rows * (int64_t)sizeof(float) : 0;
+  return (p.splits > 1 && !p.cluster) ? (int64_t)p.splits * n_rows * (int64_t)sizeof(float) : 0;
 }
 
 extern "C" int tsb_reduce_rows(const float *x, float *out, int64_t stride_m, int64_t stride_n,
@@ -187,18 +278,21 @@ extern "C" int tsb_reduce_rows(const float *x, float *out, int64_t stride_m, int
   cudaStream_t s = (cudaStream_t)stream;
   if (stride_m == 1 && n_valid > 0) {
     const ContigMPlan p = plan_contig_m(n_rows, n_valid);
+    const bool vec4 = ((uintptr_t)(x + row_lo) % 16) == 0 && stride_n % 4 == 0;
+    if (p.cluster)
+      return vec4 ? launch_contig_m_cluster<true>(p, x, out, out_stride, stride_n, n_valid, row_lo, row_hi, s)
+                  : launch_contig_m_cluster<false>(p, x, out, out_stride, stride_n, n_valid, row_lo, row_hi, s);
     if (p.splits > 1 && !scratch)
       return fail(TSB_ERR_INVALID, "tsb_reduce_rows: %lld bytes of scratch required, got NULL",
                   (long long)p.splits * n_rows * (long long)sizeof(float));
-    const bool vec4 = ((uintptr_t)(x + row_lo) % 16) == 0 && stride_n % 4 == 0;
     dim3 grid((unsigned)p.i_tiles, (unsigned)p.splits);
     float *dst = p.splits > 1 ? (float *)scratch : out + row_lo * out_stride;
     const long long dsi = p.splits > 1 ? 1 : out_stride;
     const long long dss = p.splits > 1 ? n_rows : 0;
     if (vec4)
-      reduce_rows_contig_m_kernel<true><<<grid, RC_WARPS * 32, 0, s>>>(x, dst, dsi, dss, stride_n, n_valid, row_lo, row_hi, p.j_per_split);
+      reduce_rows_contig_m_kernel<true, false><<<grid, RC_WARPS * 32, 0, s>>>(x, dst, dsi, dss, stride_n, n_valid, row_lo, row_hi, p.j_per_split);
     else
-      reduce_rows_contig_m_kernel<false><<<grid, RC_WARPS * 32, 0, s>>>(x, dst, dsi, dss, stride_n, n_valid, row_lo, row_hi, p.j_per_split);
+      reduce_rows_contig_m_kernel<false, false><<<grid, RC_WARPS * 32, 0, s>>>(x, dst, dsi, dss, stride_n, n_valid, row_lo, row_hi, p.j_per_split);
     TSB_LAUNCH_OK("reduce_rows_contig_m_kernel");
     if (p.splits > 1) {
       reduce_rows_finalize_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, s>>>(
@@ -221,8 +315,8 @@ extern "C" int tsb_reduce_rows(const float *x, float *out, int64_t stride_m, int
 extern "C" int tsb_reduce_all(const float *x, float *out, int64_t n, int64_t stride, void *stream) {
   if (!x || !out) return fail(TSB_ERR_INVALID, "tsb_reduce_all: null pointer");
   if (n < 0) return fail(TSB_ERR_INVALID, "tsb_reduce_all: negative length");
-  reduce_all_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(x, out, n, stride);
-  TSB_LAUNCH_OK("reduce_all_kernel");
+  TSB_CUDA_OK(launch_pdl(reduce_all_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, x, out, (long long)n,
+                         (long long)stride));
   return TSB_OK;
 }
 
@@ -238,7 +332,7 @@ extern "C" int tsb_reduce_all(const float *x, float *out, int64_t n, int64_t str
 // in a fixed array inside this library's device image.
 //
 // Facts a user must know:
-//  * The array is TSB_REDUCE_STATIC_SCRATCH_BYTES (2 MiB) of device memory per GPU
+//  * The array is TSB_REDUCE_STATIC_SCRATCH_BYTES (1 MiB) of device memory per GPU
 //    that loads the library, held until the process exits.
 //  * Calls whose partials do not fit are refused with TSB_ERR_UNSUPPORTED; nothing
 //    is allocated behind the caller's back (no cudaMalloc, cudaFree, or any

@@ -11,6 +11,7 @@
 // shuffles plus a shared-memory step across warps, and written once.
 #include "tsb_common.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 namespace tsb {
 
@@ -217,55 +218,56 @@ struct RowTile {
   }
 };
 
-// Weight and bias are staged once per CTA in shared memory as fp32 (no per-row
-// conversion), the row is expanded to fp32 registers once, and the next row's 16-byte
-// loads are issued before the current row is reduced, so that a CTA always has a full
-// row in flight.  The kernel is close to issue-bound, so every per-element instruction
-// counts: masks are evaluated per 16-byte vector, not per element.
-template <typename T, int THREADS, int VPT, bool ALIGNED>
-__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 768 / THREADS : (THREADS == 512 ? 2 : 1)))
+// Weight and bias are read once per CTA.  WB_REGS: they stay in registers in their memory
+// type (one 16-byte vector per row vector, converted on use), so the kernel needs no shared
+// memory beyond the reduction exchange and its occupancy is set by registers alone.  Otherwise
+// (rows too wide for that) they are staged in shared memory, again in their memory type.
+// The row is expanded to fp32 registers once, and the next row's 16-byte loads are issued
+// before the current row is reduced, so that a CTA always has a full row in flight.  The kernel
+// is close to issue-bound, so every per-element instruction counts: masks are evaluated per
+// 16-byte vector, not per element.  Products and sums are rounded separately (no contraction),
+// as in the reference's lowering.
+// resident CTAs per SM the kernel is compiled for (bounds the registers per thread)
+constexpr int ln_min_ctas(int threads, int vpt, bool wb_regs) {
+  return threads <= 128 ? 1024 / threads
+                        : (threads == 256 ? (wb_regs && vpt >= 4 ? 2 : 3) : (threads == 512 ? 2 : 1));
+}
+
+template <typename T, int THREADS, int VPT, bool ALIGNED, bool WB_REGS>
+__global__ void __launch_bounds__(THREADS, ln_min_ctas(THREADS, VPT, WB_REGS))
 layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__restrict__ W,
                      const T *__restrict__ B, float *__restrict__ Mean, float *__restrict__ Rstd,
                      long long xs, long long ys, int n_cols, float eps, long long row_lo,
                      long long row_hi) {
   using Tile = RowTile<T, THREADS, VPT, ALIGNED>;
   constexpr int EPV = Io<T>::EPV;
-  constexpr int SLOTS = THREADS * VPT;  // 16-byte vectors per row
   extern __shared__ __align__(16) unsigned char ln_smem[];
-  // slot (v, t) holds EPV floats as EPV/4 float4; element group j of the slot sits at
-  // [(j * SLOTS + v * THREADS + t)] so that a warp reads consecutive float4 (no bank conflicts)
-  float4 *sw = reinterpret_cast<float4 *>(ln_smem);
-  float4 *sb = sw + SLOTS * (EPV / 4);
+  T *sw = reinterpret_cast<T *>(ln_smem);
+  T *sb = sw + THREADS * VPT * EPV;
   // two exchange buffers, used alternately, so that one barrier per reduction suffices:
   // buffer 0 is next written a full reduction (and its barrier) after its last read
   __shared__ float red[2][THREADS / 32];
   const int t = threadIdx.x;
-  // the first row's loads go out before weight and bias are staged, so the two latencies overlap
+  grid_dependency_wait();
+  grid_launch_dependents();  // all CTAs of this launch are resident: successors only take freed slots
+  // the first row's loads go out before weight and bias, so the latencies overlap
   long long row = row_lo + blockIdx.x;
   uint4 xq[VPT];
   if (row < row_hi) Tile::load(X + row * xs, n_cols, t, xq);
-  {
+  uint4 wq[WB_REGS ? VPT : 1], bq[WB_REGS ? VPT : 1];
+  if (WB_REGS) {
+    Tile::load(W, n_cols, t, wq);
+    Tile::load(B, n_cols, t, bq);
+  } else {
     uint4 q[VPT];
     Tile::load(W, n_cols, t, q);
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      float f[EPV];
-      Io<T>::unpack(q[v], f);
-#pragma unroll
-      for (int j = 0; j < EPV / 4; ++j)
-        sw[j * SLOTS + v * THREADS + t] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
-    }
+    for (int v = 0; v < VPT; ++v) Tile::put(sw, v, t, q[v]);
     Tile::load(B, n_cols, t, q);
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      float f[EPV];
-      Io<T>::unpack(q[v], f);
-#pragma unroll
-      for (int j = 0; j < EPV / 4; ++j)
-        sb[j * SLOTS + v * THREADS + t] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
-    }
+    for (int v = 0; v < VPT; ++v) Tile::put(sb, v, t, q[v]);
+    // each thread reads back only the slots it wrote: no barrier needed
   }
-  // each thread reads back only the slots it wrote: no barrier needed
   const float fn = (float)n_cols;
   for (; row < row_hi; row += gridDim.x) {
     float x[VPT][EPV];
@@ -273,7 +275,7 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
     for (int v = 0; v < VPT; ++v) Io<T>::unpack(xq[v], x[v]);
     const long long next = row + gridDim.x;
     if (next < row_hi) Tile::load(X + next * xs, n_cols, t, xq);  // in flight during the reductions
-    // four independent accumulators per thread keep the add/fma chains short
+    // four independent accumulators per thread keep the add chains short
     float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int v = 0; v < VPT; ++v)
@@ -288,13 +290,13 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
 #pragma unroll
         for (int k = 0; k < EPV; ++k) {
           x[v][k] = x[v][k] - mean;  // kept: the output pass starts from the centred value
-          q4[k & 3] = fmaf(x[v][k], x[v][k], q4[k & 3]);
+          q4[k & 3] += x[v][k] * x[v][k];
         }
       } else {
 #pragma unroll
         for (int k = 0; k < EPV; ++k) {
           x[v][k] = (Tile::col(v, k, t) < n_cols) ? x[v][k] - mean : 0.f;
-          q4[k & 3] = fmaf(x[v][k], x[v][k], q4[k & 3]);
+          q4[k & 3] += x[v][k] * x[v][k];
         }
       }
     }
@@ -308,17 +310,12 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
     T *dst = Y + row * ys;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      float y[EPV];
+      float w[EPV], b[EPV], y[EPV];
+      Io<T>::unpack(WB_REGS ? wq[v] : Tile::get(sw, v, t), w);
+      Io<T>::unpack(WB_REGS ? bq[v] : Tile::get(sb, v, t), b);
+      // x already holds x - mean: ((x - mean) * rstd) * w + b, one rounding per op
 #pragma unroll
-      for (int j = 0; j < EPV / 4; ++j) {
-        const float4 w = sw[j * SLOTS + v * THREADS + t];
-        const float4 b = sb[j * SLOTS + v * THREADS + t];
-        // x already holds x - mean: ((x - mean) * rstd) * w + b, one rounding per op
-        y[4 * j + 0] = (x[v][4 * j + 0] * rstd) * w.x + b.x;
-        y[4 * j + 1] = (x[v][4 * j + 1] * rstd) * w.y + b.y;
-        y[4 * j + 2] = (x[v][4 * j + 2] * rstd) * w.z + b.z;
-        y[4 * j + 3] = (x[v][4 * j + 3] * rstd) * w.w + b.w;
-      }
+      for (int k = 0; k < EPV; ++k) y[k] = (x[v][k] * rstd) * w[k] + b[k];
       if (ALIGNED && Tile::col(v, EPV - 1, t) < n_cols) {
         __stcs(reinterpret_cast<uint4 *>(dst + Tile::col(v, 0, t)), Io<T>::pack(y));
       } else {
@@ -330,35 +327,34 @@ layernorm_fwd_kernel(const T *__restrict__ X, T *__restrict__ Y, const T *__rest
   }
 }
 
-template <typename T, int THREADS, int VPT>
+template <typename T, int THREADS, int VPT, bool WB_REGS>
 static int launch_ln(const void *x, void *y, const void *w, const void *b, float *mean, float *rstd,
                      long long xs, long long ys, int n_cols, float eps, long long row_lo,
                      long long row_hi, bool aligned, cudaStream_t s) {
   const long long rows = row_hi - row_lo;
-  constexpr int SMEM = 2 * THREADS * VPT * Io<T>::EPV * 4;  // weight + bias as fp32
-  auto kt = layernorm_fwd_kernel<T, THREADS, VPT, true>;
-  auto kf = layernorm_fwd_kernel<T, THREADS, VPT, false>;
-  if (SMEM > 48 * 1024) {
-    TSB_CUDA_OK(cudaFuncSetAttribute(kt, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    TSB_CUDA_OK(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  constexpr int SMEM = WB_REGS ? 0 : 2 * THREADS * VPT * 16;  // weight + bias in their memory type
+  auto kt = layernorm_fwd_kernel<T, THREADS, VPT, true, WB_REGS>;
+  auto kf = layernorm_fwd_kernel<T, THREADS, VPT, false, WB_REGS>;
+  static SmemLimit lim_t, lim_f;
+  static int per_sm_cache[64][2];
+  TSB_CUDA_OK(allow_dynamic_smem(kt, SMEM, lim_t));
+  TSB_CUDA_OK(allow_dynamic_smem(kf, SMEM, lim_f));
+  const int dev = device_slot();
+  int per_sm = per_sm_cache[dev][aligned ? 1 : 0];
+  if (per_sm == 0) {
+    if (aligned) {
+      TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kt, THREADS, SMEM));
+    } else {
+      TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kf, THREADS, SMEM));
+    }
+    if (per_sm < 1) per_sm = 1;
+    per_sm_cache[dev][aligned ? 1 : 0] = per_sm;
   }
-  int per_sm = 0;
-  if (aligned) {
-    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kt, THREADS, SMEM));
-  } else {
-    TSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kf, THREADS, SMEM));
-  }
-  if (per_sm < 1) per_sm = 1;
   // all resident CTAs, so that every SM carries the same number of them
   long long ctas = (long long)sm_count() * per_sm;
   if (ctas > rows) ctas = rows;
-  if (aligned)
-    kt<<<(unsigned)ctas, THREADS, SMEM, s>>>((const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys,
-                                            n_cols, eps, row_lo, row_hi);
-  else
-    kf<<<(unsigned)ctas, THREADS, SMEM, s>>>((const T *)x, (T *)y, (const T *)w, (const T *)b, mean, rstd, xs, ys,
-                                            n_cols, eps, row_lo, row_hi);
-  TSB_LAUNCH_OK("layernorm_fwd_kernel");
+  TSB_CUDA_OK(launch_pdl(aligned ? kt : kf, dim3((unsigned)ctas), dim3(THREADS), (size_t)SMEM, s, (const T *)x, (T *)y,
+                         (const T *)w, (const T *)b, mean, rstd, xs, ys, n_cols, eps, row_lo, row_hi));
   return TSB_OK;
 }
 
@@ -372,20 +368,28 @@ static int dispatch_ln(const void *x, void *y, const void *w, const void *b, flo
                        ((uintptr_t)b % vb) == 0 && xs % EPV == 0 && ys % EPV == 0;
   const long long vecs = (n_cols + EPV - 1) / EPV;  // 16-byte vectors per row
   const int n = (int)n_cols;
-#define TSB_LN(THREADS, VPT) \
-  return launch_ln<T, THREADS, VPT>(x, y, w, b, mean, rstd, xs, ys, n, eps, row_lo, row_hi, aligned, s)
-  if (vecs <= 32) TSB_LN(32, 1);
-  if (vecs <= 64) TSB_LN(64, 1);
-  if (vecs <= 128) TSB_LN(128, 1);
-  if (vecs <= 256) TSB_LN(256, 1);
-  if (vecs <= 512) TSB_LN(256, 2);
-  if (vecs <= 1024) TSB_LN(256, 4);
-  if (vecs <= 2048) TSB_LN(512, 4);
-  // weight and bias are held as fp32 in shared memory: 2 * 4 bytes per column, at most 227 KB
-  if (vecs <= 4096 && 2ll * 4096 * EPV * 4 <= 227 * 1024) TSB_LN(1024, 4);
+#define TSB_LN(THREADS, VPT, WB_REGS) \
+  return launch_ln<T, THREADS, VPT, WB_REGS>(x, y, w, b, mean, rstd, xs, ys, n, eps, row_lo, row_hi, aligned, s)
+  if (vecs <= 32) TSB_LN(32, 1, true);
+  if (vecs <= 64) TSB_LN(64, 1, true);
+  if (vecs <= 128) TSB_LN(128, 1, true);
+  if (vecs <= 256) TSB_LN(256, 1, true);
+  if (vecs <= 512) TSB_LN(256, 2, true);
+  if (vecs <= 1024) {
+    static int variant = -1;  // TEMPORARY tuning knob
+    if (variant < 0) { const char *e = getenv("TSB_LN_VARIANT"); variant = e ? atoi(e) : 0; }
+    if (variant == 1) TSB_LN(256, 4, true);
+    if (variant == 2) TSB_LN(1024, 1, true);
+    if (variant == 3) TSB_LN(256, 4, false);
+    if (variant == 4) TSB_LN(512, 2, false);
+    TSB_LN(512, 2, true);
+  }
+  if (vecs <= 2048) TSB_LN(1024, 2, true);
+  // wider rows: weight and bias in shared memory in their memory type, 2 * 16 bytes per vector
+  if (vecs <= 4096) TSB_LN(1024, 4, false);
 #undef TSB_LN
   return fail(TSB_ERR_UNSUPPORTED, "tsb_layernorm_fwd: rows of %lld elements exceed the on-chip limit (%d)",
-              n_cols, (2ll * 4096 * EPV * 4 <= 227 * 1024 ? 4096 : 2048) * EPV);
+              n_cols, 4096 * EPV);
 }
 
 }  // namespace tsb

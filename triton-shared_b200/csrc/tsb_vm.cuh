@@ -426,6 +426,46 @@ __device__ __forceinline__ void store_vec(const DAcc &A, const ProgState &s, int
 }
 
 
+// Data-dependent accesses (gather / scatter): lane k of the vector reads or writes element
+//   structured address + (int)index[k]        (when has_index)
+// and takes part only if the structured mask admits it and mask[k] & 1 (when has_mask).
+// One scalar access per lane; lanes of a warp that address neighbouring elements still coalesce.
+template <int VEC>
+__device__ __forceinline__ void load_vec_indirect(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
+                                                  bool has_index, bool has_mask, const unsigned (&index)[VEC],
+                                                  const unsigned (&mask)[VEC], unsigned (&out)[VEC]) {
+  const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
+  const long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
+  const unsigned fill = A.has_other ? A.other : 0u;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    bool ok = outer && (i2 + k) < s.dim[2];
+    if (has_mask) ok = ok && (mask[k] & 1u);
+    long long ek = e + k * A.stride[2];
+    if (A.n_wrap) ek += wrap_addend(A, s, i0, i1, i2 + k);
+    if (has_index) ek += (long long)(int)index[k];
+    out[k] = A.kind == 2 ? (ok ? 1u : 0u) : (A.kind == 3 ? (unsigned)ek : (ok ? ld_elem(A.base + ek * A.esize, A.dtype) : fill));
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_vec_indirect(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
+                                                   bool has_index, bool has_mask, const unsigned (&index)[VEC],
+                                                   const unsigned (&mask)[VEC], const unsigned (&in)[VEC]) {
+  if (!(i0 < s.dim[0] && i1 < s.dim[1])) return;
+  const long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    bool ok = (i2 + k) < s.dim[2];
+    if (has_mask) ok = ok && (mask[k] & 1u);
+    if (!ok) continue;
+    long long ek = e + k * A.stride[2];
+    if (A.n_wrap) ek += wrap_addend(A, s, i0, i1, i2 + k);
+    if (has_index) ek += (long long)(int)index[k];
+    st_elem(A.base + ek * A.esize, A.dtype, in[k]);
+  }
+}
+
 // One ALU op on one lane with the opcode known at compile time: the per-op switch is taken
 // once per thread (see TSB_ALU_OPCODES), not once per lane.  ROUND = false leaves a float result
 // unrounded (the caller rounds all lanes of the op at once when the op's type is 16-bit).
