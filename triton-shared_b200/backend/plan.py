@@ -460,17 +460,7 @@ class _EwLowering:
     def allocate(self):
         """Hoist loads; turn constants into immediate operands; keep a value that only the next op
         reads in the accumulator; map what remains onto TSB_NUM_REGS shared-memory registers."""
-        hoisted = self._allocate(True)
-        if _regs_used(hoisted) > rt.RVM_REGS:
-            # loads at their point of use keep fewer values alive: take that order when it lets the
-            # body run on the hardware-register VM (rt.RVM_REGS registers besides the accumulator)
-            try:
-                inplace = self._allocate(False)
-            except UnsupportedTTIR:
-                return hoisted
-            if _regs_used(inplace) <= rt.RVM_REGS:
-                return inplace
-        return hoisted
+        return self._allocate(True)
 
     def _allocate(self, hoist_loads: bool):
         ACC, IMM = rt.REG_ACC, rt.REG_IMM

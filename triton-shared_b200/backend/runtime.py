@@ -16,7 +16,6 @@ TSB_MAX_OPS = 96
 TSB_NUM_REGS = 16
 TSB_MAX_LOOPS = 4
 REG_ACC, REG_IMM = -1, -2  # operand forms of tsb_elementwise (TSB_REG_ACC, TSB_REG_IMM)
-RVM_REGS = 3  # bodies naming at most this many registers run with the register file in hardware registers
 MEM_INDEX, MEM_MASK = 1, 2  # flags in the imm field of load / store ops: per-lane index / mask operand
 
 DTYPES = {"f32": 0, "f16": 1, "bf16": 2, "i32": 3, "i16": 4, "i8": 5, "i1": 6, "i64": 7, "f64": 8,

@@ -10,29 +10,10 @@
 //   elementwise op  lib/Conversion/TritonArithToLinalg/TritonArithToLinalg.cpp:104
 // The CPU backend materialises every block in a malloc'ed buffer and runs one
 // scalar loop per op; here a lane's values stay in registers from load to store.
-#include "tsb_vm.cuh"
+#include "tsb_ew.cuh"
 #include <stdlib.h>
 
 namespace tsb {
-
-struct EwParams {
-  DAcc acc[TSB_MAX_ACCESSES];
-  tsb_op ops[TSB_MAX_OPS];
-  int n_acc, n_ops;
-  int size[3];
-  int lg[3];      // log2 of sizes (Triton block shapes are powers of two)
-  int lanes;      // size[0]*size[1]*size[2]
-  int grid[3];
-  int order[3];   // grid axes from fastest to slowest in the order programs are walked
-  long long pid_lo, pid_hi;
-  int n_loops;               // perfect loop nest around the whole body (outermost first)
-  int trip[TSB_MAX_LOOPS];
-  long long total_trips;     // product of the trip counts
-  int indirect;              // some load/store takes a per-lane index or mask operand
-};
-
-// flags in the imm field of TSB_OP_LOAD / TSB_OP_STORE
-constexpr unsigned MEM_INDEX = 1u, MEM_MASK = 2u;
 
 // ---- general body: a small register VM ----------------------------------------
 // One pass over the op list for VEC lanes; `ld(access, regs)` and `st(access, regs)`
@@ -182,156 +163,6 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRe
   }
 }
 
-// ---- register-resident VM ------------------------------------------------------------------
-// Bodies that need at most NR registers besides the accumulator run with the whole register file
-// in hardware registers: register r of a thread is U lane-vectors of VEC words held in an array
-// that is only ever indexed by compile-time constants (a run-time register number selects a
-// `case` of a switch, never an array slot), so nothing touches shared or local memory.  Operand
-// a of an op is brought into the accumulator (no work when it already is the accumulator, the
-// usual case), operand b into a scratch vector, and the result replaces the accumulator: about
-// two instructions per lane and op plus the decode shared by U*VEC lanes.
-template <int VEC, int U, int NR>
-struct RegFile {
-  unsigned r[NR][U][VEC];
-};
-
-#define TSB_RVM_WITH_REG(idx, F)                  \
-  switch (idx) {                                  \
-    case 0: F(0); break;                          \
-    case 1: if (NR > 1) { F(1 % NR); } break;     \
-    default: if (NR > 2) { F(2 % NR); } break;    \
-  }
-
-// v <- operand `which`: a register, the accumulator or the op's immediate
-template <int VEC, int U, int NR>
-__device__ __forceinline__ void rvm_fetch(const tsb_op &op, int which, const RegFile<VEC, U, NR> &R,
-                                          const unsigned (&acc)[U][VEC], unsigned (&v)[U][VEC]) {
-  if (which == TSB_REG_ACC) {
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) v[u][k] = acc[u][k];
-  } else if (which == TSB_REG_IMM) {
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) v[u][k] = op.imm2;
-  } else {
-#define TSB_F(I) _Pragma("unroll") for (int u = 0; u < U; ++u) _Pragma("unroll") for (int k = 0; k < VEC; ++k) v[u][k] = R.r[I][u][k]
-    TSB_RVM_WITH_REG(which, TSB_F)
-#undef TSB_F
-  }
-}
-
-template <int VEC, int U, int NR>
-__device__ __forceinline__ void rvm_put(int dst, RegFile<VEC, U, NR> &R, const unsigned (&acc)[U][VEC]) {
-  if (dst < 0) return;
-#define TSB_F(I) _Pragma("unroll") for (int u = 0; u < U; ++u) _Pragma("unroll") for (int k = 0; k < VEC; ++k) R.r[I][u][k] = acc[u][k]
-  TSB_RVM_WITH_REG(dst, TSB_F)
-#undef TSB_F
-}
-
-// one lane-vector of an operand (three-operand ops keep their scratch to VEC words per operand)
-template <int VEC, int U, int NR>
-__device__ __forceinline__ void rvm_fetch_u(const tsb_op &op, int which, const RegFile<VEC, U, NR> &R,
-                                            const unsigned (&acc)[U][VEC], int u, unsigned (&v)[VEC]) {
-  if (which == TSB_REG_ACC) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) v[k] = acc[u][k];
-  } else if (which == TSB_REG_IMM) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) v[k] = op.imm2;
-  } else {
-#define TSB_F(I) _Pragma("unroll") for (int k = 0; k < VEC; ++k) v[k] = R.r[I][u][k]
-    TSB_RVM_WITH_REG(which, TSB_F)
-#undef TSB_F
-  }
-}
-
-template <int OPC, int VEC, int U, int NR>
-__device__ __forceinline__ void rvm_alu(const tsb_op &op, RegFile<VEC, U, NR> &R, unsigned (&acc)[U][VEC]) {
-  constexpr int AR = alu_arity<OPC>();
-  if constexpr (AR >= 3) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      unsigned a[VEC], b[VEC], c[VEC];
-      rvm_fetch_u<VEC, U, NR>(op, op.a, R, acc, u, a);
-      rvm_fetch_u<VEC, U, NR>(op, op.b, R, acc, u, b);
-      rvm_fetch_u<VEC, U, NR>(op, op.c, R, acc, u, c);
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) acc[u][k] = alu_op<OPC, false>(op, a[k], b[k], c[k]);
-    }
-  } else {
-    unsigned b[U][VEC];
-    // b first: it may name the accumulator, which operand a is about to replace
-    if (AR >= 2) rvm_fetch<VEC, U, NR>(op, op.b, R, acc, b);
-    if (op.a != TSB_REG_ACC) rvm_fetch<VEC, U, NR>(op, op.a, R, acc, acc);
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) acc[u][k] = alu_op<OPC, false>(op, acc[u][k], AR >= 2 ? b[u][k] : 0u, 0u);
-  }
-  if (alu_rounds<OPC>() && op.type != TSB_F32) {
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) acc[u][k] = __float_as_uint(round_to(__uint_as_float(acc[u][k]), op.type));
-  }
-  rvm_put<VEC, U, NR>(op.dst, R, acc);
-}
-
-template <int VEC, int U, int NR, typename LoadFn, typename StoreFn>
-__device__ __forceinline__ void rvm_exec(const tsb_op *ops, int n_ops, LoadFn ld, StoreFn st) {
-  RegFile<VEC, U, NR> R;
-  unsigned acc[U][VEC];
-#pragma unroll
-  for (int u = 0; u < U; ++u)
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      acc[u][k] = 0u;
-#pragma unroll
-      for (int r = 0; r < NR; ++r) R.r[r][u][k] = 0u;
-    }
-  for (int i = 0; i < n_ops; ++i) {
-    const tsb_op &op = ops[i];
-    switch (op.opcode) {
-      case TSB_OP_LOAD:
-        ld(op.a, acc);
-        rvm_put<VEC, U, NR>(op.dst, R, acc);
-        break;
-      case TSB_OP_STORE:
-        if (op.b != TSB_REG_ACC) rvm_fetch<VEC, U, NR>(op, op.b, R, acc, acc);
-        st(op.a, acc);
-        break;
-      case TSB_OP_CONST:
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-          for (int k = 0; k < VEC; ++k) acc[u][k] = op.imm;
-        rvm_put<VEC, U, NR>(op.dst, R, acc);
-        break;
-#define TSB_VM_CASE(O) \
-  case O: rvm_alu<O, VEC, U, NR>(op, R, acc); break;
-        TSB_ALU_OPCODES(TSB_VM_CASE)
-#undef TSB_VM_CASE
-      default: break;
-    }
-  }
-}
-
-// Decode the flat iteration number q of a perfect loop nest into per-level counters.
-__device__ __forceinline__ void loop_counters(const EwParams &P, long long q, int it[TSB_MAX_LOOPS]) {
-#pragma unroll
-  for (int l = TSB_MAX_LOOPS - 1; l >= 0; --l) {
-    if (l < P.n_loops) {
-      it[l] = (int)(q % P.trip[l]);
-      q /= P.trip[l];
-    } else {
-      it[l] = 0;
-    }
-  }
-}
-
 template <int VEC, int U>
 __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwParams P) {
   extern __shared__ __align__(16) unsigned vm_smem[];
@@ -397,14 +228,17 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
   }
 }
 
-// Register-resident form of the blocked kernel.  A program of `items` lane-vectors is shared by
-// G = items / U consecutive threads, each carrying U vectors G apart (consecutive threads touch
-// consecutive vectors); programs are dealt to thread groups in the walk order of the launch, so
-// a CTA of 256 threads works on 256 / G programs at once and small blocks still fill it.  Each
-// thread derives the program's access state itself when the body reaches the load or store.
-template <int NR>
-__global__ void __launch_bounds__(256, 2) ew_rvm_kernel(const __grid_constant__ EwParams P, int lg_g) {
+// Packed form of the blocked VM kernel for programs of at most 1024 lane-vectors.  A program of
+// `items` lane-vectors is shared by G = items / U consecutive threads, each carrying U vectors G
+// apart (consecutive threads touch consecutive vectors); programs are dealt to thread groups in
+// the walk order of the launch, so a CTA of 256 threads works on 256 / G programs at once and
+// small blocks still fill it.  Each thread derives the program's access state itself when the
+// body reaches the load or store: no shared state, no barrier per program.
+template <bool LOOPS>
+__global__ void __launch_bounds__(256, 4) ew_vm_packed_kernel(const __grid_constant__ EwParams P, int lg_g) {
   constexpr int VEC = 4, U = 4;
+  extern __shared__ __align__(16) unsigned vm_smem[];
+  const VmRegs<VEC, U> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
   const int G = 1 << lg_g;
   const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
   const long long n_threads = (P.pid_hi - P.pid_lo) << lg_g;
@@ -416,33 +250,45 @@ __global__ void __launch_bounds__(256, 2) ew_rvm_kernel(const __grid_constant__ 
     const int within = (int)(g & (G - 1));
     long long px = 0, py = 0, pz = 0;
     if (live) split_pid(P.grid, P.order, P.pid_lo + (g >> lg_g), px, py, pz);
-    for (long long q = 0; q < P.total_trips; ++q) {
-      int it[TSB_MAX_LOOPS];
-      loop_counters(P, q, it);
-      if (P.n_loops) {  // later iterations of a program see the stores of earlier ones (same CTA)
+    for (long long q = 0; q < (LOOPS ? P.total_trips : 1); ++q) {
+      int it[TSB_MAX_LOOPS] = {0, 0, 0, 0};
+      if (LOOPS) {  // later iterations of a program see the stores of earlier ones (same CTA)
+        loop_counters(P, q, it);
         __threadfence_block();
         __syncthreads();
       }
       if (!live) continue;
-      rvm_exec<VEC, U, NR>(
-          P.ops, P.n_ops,
-          [&](int a, unsigned(&r)[U][VEC]) {
-            ProgState ps;
-            program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const int l = (within + u * G) * VEC;
-              load_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r[u]);
-            }
+      auto state = [&](int a, ProgState &ps) {
+        if (LOOPS) program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
+        else program_state(P.acc[a], P.size, px, py, pz, ps);
+      };
+      auto lane0 = [&](int u) { return (within + u * G) * VEC; };
+      // the access state is derived once per op (for sub-item 0) and kept for the other sub-items
+      ProgState ps;
+      vm_exec<VEC, U>(
+          P.ops, P.n_ops, R,
+          [&](int a, int u, unsigned(&r)[VEC]) {
+            if (u == 0) state(a, ps);
+            const int l = lane0(u);
+            load_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r);
           },
-          [&](int a, const unsigned(&r)[U][VEC]) {
-            ProgState ps;
-            program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const int l = (within + u * G) * VEC;
-              store_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r[u]);
-            }
+          [&](int a, int u, const unsigned(&r)[VEC]) {
+            if (u == 0) state(a, ps);
+            const int l = lane0(u);
+            store_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r);
+          },
+          [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC], unsigned(&r)[VEC]) {
+            if (u == 0) state(a, ps);
+            const int l = lane0(u);
+            load_vec_indirect<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1),
+                                   flags & MEM_INDEX, flags & MEM_MASK, ix, mk, r);
+          },
+          [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC],
+              const unsigned(&r)[VEC]) {
+            if (u == 0) state(a, ps);
+            const int l = lane0(u);
+            store_vec_indirect<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1),
+                                    flags & MEM_INDEX, flags & MEM_MASK, ix, mk, r);
           });
     }
   }
@@ -586,77 +432,6 @@ __global__ void __launch_bounds__(256) ew_copy2d_kernel(const __grid_constant__ 
   }
 }
 
-// ---- flat addressing ------------------------------------------------------------
-// When every access is a unit-stride 1-D block whose offset and mask start advance
-// by exactly the block size per program (the "pid * BLOCK + arange(BLOCK)" idiom on a
-// 1-D grid), lane l of program p is element g = p*BLOCK + l of one flat range: it
-// lives at base + shift + g and is accessible iff g < limit.  The kernels below walk
-// that range with no per-program bookkeeping; results are identical to the blocked
-// kernels.
-struct FlatAcc {
-  char *base;
-  long long shift;
-  long long limit;
-  int dtype, esize, vec_ok, has_other, kind;
-  unsigned other;
-};
-struct FlatParams {
-  FlatAcc acc[TSB_MAX_ACCESSES];
-  tsb_op ops[TSB_MAX_OPS];
-  int n_acc, n_ops;
-  long long g_lo, g_hi;
-};
-
-__device__ __forceinline__ void flat_load(const FlatAcc &A, long long g, unsigned (&out)[4]) {
-  const long long e = A.shift + g;
-  if (A.kind >= 2) {
-#pragma unroll
-    for (int k = 0; k < 4; ++k) out[k] = A.kind == 2 ? ((g + k) < A.limit ? 1u : 0u) : (unsigned)(e + k);
-    return;
-  }
-  const char *p = A.base + e * A.esize;
-  if (A.vec_ok && g + 4 <= A.limit) {
-    if (A.esize == 4) {
-      const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(p));
-      out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
-    } else if (A.esize == 2) {
-      const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(p));
-      out[0] = v.x & 0xffffu; out[1] = v.x >> 16; out[2] = v.y & 0xffffu; out[3] = v.y >> 16;
-      raw_to_reg<4>(A.dtype, out);
-    } else {
-      const unsigned v = __ldcs(reinterpret_cast<const unsigned *>(p));
-#pragma unroll
-      for (int k = 0; k < 4; ++k) out[k] = (v >> (8 * k)) & 0xffu;
-      raw_to_reg<4>(A.dtype, out);
-    }
-    return;
-  }
-  const unsigned fill = A.has_other ? A.other : 0u;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) out[k] = (g + k) < A.limit ? ld_elem(p + k * A.esize, A.dtype) : fill;
-}
-
-__device__ __forceinline__ void flat_store(const FlatAcc &A, long long g, const unsigned (&in)[4]) {
-  char *p = A.base + (A.shift + g) * A.esize;
-  if (A.vec_ok && g + 4 <= A.limit) {
-    if (A.esize == 4) {
-      __stcs(reinterpret_cast<uint4 *>(p), make_uint4(in[0], in[1], in[2], in[3]));
-    } else if (A.esize == 2) {
-      unsigned h[4] = {in[0], in[1], in[2], in[3]};
-      reg_to_raw<4>(A.dtype, h);
-      __stcs(reinterpret_cast<uint2 *>(p), make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16)));
-    } else {
-      unsigned h[4] = {in[0], in[1], in[2], in[3]};
-      reg_to_raw<4>(A.dtype, h);
-      __stcs(reinterpret_cast<unsigned *>(p), h[0] | (h[1] << 8) | (h[2] << 16) | (h[3] << 24));
-    }
-    return;
-  }
-#pragma unroll
-  for (int k = 0; k < 4; ++k)
-    if (g + k < A.limit) st_elem(p + k * A.esize, A.dtype, in[k]);
-}
-
 constexpr int FLAT_UNROLL = 4;
 
 // out = OPC(in0, in1) over the flat range.  The leading `interior` vectors lie below
@@ -739,7 +514,6 @@ __global__ void __launch_bounds__(256) ew_flat_binary_f32_kernel(const __grid_co
   }
 }
 
-constexpr int FLAT_VM_U = 4;
 
 __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__ FlatParams P) {
   extern __shared__ __align__(16) unsigned vm_smem[];
@@ -765,38 +539,6 @@ __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__
         [&](int, int, unsigned, const unsigned(&)[4], const unsigned(&)[4], const unsigned(&)[4]) {});
   }
 }
-
-template <int NR>
-__global__ void __launch_bounds__(256, 2) ew_flat_rvm_kernel(const __grid_constant__ FlatParams P) {
-  constexpr int U = FLAT_VM_U;
-  const long long n_vec = (P.g_hi - P.g_lo) >> 2;
-  const long long step = (long long)gridDim.x * blockDim.x * U;
-  grid_dependency_wait();
-  grid_launch_dependents();
-  for (long long v0 = (long long)blockIdx.x * blockDim.x * U + threadIdx.x; v0 < n_vec; v0 += step) {
-    rvm_exec<4, U, NR>(
-        P.ops, P.n_ops,
-        [&](int a, unsigned(&r)[U][4]) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const long long v = v0 + (long long)u * blockDim.x;
-            if (v < n_vec) {
-              flat_load(P.acc[a], P.g_lo + v * 4, r[u]);
-            } else {
-              r[u][0] = r[u][1] = r[u][2] = r[u][3] = 0u;
-            }
-          }
-        },
-        [&](int a, const unsigned(&r)[U][4]) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const long long v = v0 + (long long)u * blockDim.x;
-            if (v < n_vec) flat_store(P.acc[a], P.g_lo + v * 4, r[u]);
-          }
-        });
-  }
-}
-
 
 static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
                         const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, EwParams &P,
@@ -999,18 +741,6 @@ static bool is_fast_binary(const tsb_access *acc, const tsb_op *ops, int n_ops, 
 
 using namespace tsb;
 
-constexpr int RVM_REGS = 3;  // registers of the hardware-register VM (besides the accumulator)
-
-// TSB_RVM=0 in the environment keeps every body on the shared-memory VM (for comparisons).
-static bool rvm_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char *e = getenv("TSB_RVM");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1;
-}
-
 extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *ops_in, int n_ops_in,
                                const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, void *stream) {
   static thread_local EwParams P;
@@ -1034,7 +764,6 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     P.ops[1].a = t;
   }
   const int regs_used = vm_regs_used(ops, n_ops);
-  const bool rvm = rvm_enabled() && !P.indirect && regs_used <= RVM_REGS && vec == 4;
   static thread_local FlatParams F;
   if (plain && build_flat(P, vec, F)) {
     const long long n_vec = (F.g_hi - F.g_lo) / 4;
@@ -1042,16 +771,13 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     // the VM's register file lives in shared memory: fewer threads per CTA when the body uses many registers
     int flat_threads = 256;
     const size_t regs_bytes = (size_t)regs_used * FLAT_VM_U * 4 * sizeof(unsigned);
-    while (!fast && !rvm && regs_bytes * flat_threads > 96 * 1024 && flat_threads > 32) flat_threads /= 2;
+    while (!fast && regs_bytes * flat_threads > 96 * 1024 && flat_threads > 32) flat_threads /= 2;
     const long long per_cta = fast ? 256ll * FLAT_UNROLL : (long long)flat_threads * FLAT_VM_U;
     long long ctas = (n_vec + per_cta - 1) / per_cta;
     const long long cap = (long long)sm_count() * 8 * 4;
     if (ctas > cap) ctas = cap;
     if (fast) {
       ew_flat_binary_f32_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
-    } else if (rvm) {
-      TSB_CUDA_OK(launch_pdl(ew_flat_rvm_kernel<RVM_REGS>, dim3((unsigned)ctas), dim3(256), 0, s, F));
-      return TSB_OK;
     } else {
       const size_t smem = regs_bytes * flat_threads;
       static SmemLimit lim_flat;
@@ -1081,16 +807,23 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     TSB_LAUNCH_OK("ew_copy_kernel");
     return TSB_OK;
   }
-  if (rvm && items >= 4) {
-    // items / 4 threads per program, 256 / that many programs per CTA pass
+  if (vec == 4 && items >= 4 && items <= 1024) {
+    // packed form: items / 4 threads per program, 256 / that many programs per CTA pass
     int lg_g = 0;
-    while ((4 << (lg_g + 1)) <= items && lg_g < 8) ++lg_g;  // G = items / 4, at most 256
-    const long long n_thr = n_prog << lg_g;
-    long long ctas = (n_thr + 255) / 256;
-    const long long cap = (long long)sm_count() * 2 * 8;
-    if (ctas > cap) ctas = cap;
-    TSB_CUDA_OK(launch_pdl(ew_rvm_kernel<RVM_REGS>, dim3((unsigned)ctas), dim3(256), 0, s, P, lg_g));
-    return TSB_OK;
+    while ((4 << (lg_g + 1)) <= items) ++lg_g;  // G = items / 4, at most 256
+    const size_t smem = (size_t)regs_used * 4 * 4 * 256 * sizeof(unsigned);
+    if (smem <= 200 * 1024) {
+      static SmemLimit lim_p0, lim_p1;
+      TSB_CUDA_OK(allow_dynamic_smem(ew_vm_packed_kernel<false>, 200 * 1024, lim_p0));
+      TSB_CUDA_OK(allow_dynamic_smem(ew_vm_packed_kernel<true>, 200 * 1024, lim_p1));
+      const long long n_thr = n_prog << lg_g;
+      long long ctas = (n_thr + 255) / 256;
+      const long long cap = (long long)sm_count() * 4 * 8;
+      if (ctas > cap) ctas = cap;
+      if (P.n_loops) TSB_CUDA_OK(launch_pdl(ew_vm_packed_kernel<true>, dim3((unsigned)ctas), dim3(256), smem, s, P, lg_g));
+      else TSB_CUDA_OK(launch_pdl(ew_vm_packed_kernel<false>, dim3((unsigned)ctas), dim3(256), smem, s, P, lg_g));
+      return TSB_OK;
+    }
   }
   // four lane-vectors per thread when the block is large enough to keep at least a warp busy
   const int U = (vec == 4 && items >= 128) ? 4 : 1;

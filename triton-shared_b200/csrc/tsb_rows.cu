@@ -11,7 +11,6 @@
 // shuffles plus a shared-memory step across warps, and written once.
 #include "tsb_common.cuh"
 #include <math.h>
-#include <stdlib.h>
 
 namespace tsb {
 
@@ -230,7 +229,7 @@ struct RowTile {
 // resident CTAs per SM the kernel is compiled for (bounds the registers per thread)
 constexpr int ln_min_ctas(int threads, int vpt, bool wb_regs) {
   return threads <= 128 ? 1024 / threads
-                        : (threads == 256 ? (wb_regs && vpt >= 4 ? 2 : 3) : (threads == 512 ? 2 : 1));
+                        : (threads == 256 ? (wb_regs && vpt >= 4 ? 2 : 3) : (threads == 512 ? (vpt >= 4 ? 1 : 2) : 1));
 }
 
 template <typename T, int THREADS, int VPT, bool ALIGNED, bool WB_REGS>
@@ -375,17 +374,10 @@ static int dispatch_ln(const void *x, void *y, const void *w, const void *b, flo
   if (vecs <= 128) TSB_LN(128, 1, true);
   if (vecs <= 256) TSB_LN(256, 1, true);
   if (vecs <= 512) TSB_LN(256, 2, true);
-  if (vecs <= 1024) {
-    static int variant = -1;  // TEMPORARY tuning knob
-    if (variant < 0) { const char *e = getenv("TSB_LN_VARIANT"); variant = e ? atoi(e) : 0; }
-    if (variant == 1) TSB_LN(256, 4, true);
-    if (variant == 2) TSB_LN(1024, 1, true);
-    if (variant == 3) TSB_LN(256, 4, false);
-    if (variant == 4) TSB_LN(512, 2, false);
-    TSB_LN(512, 2, true);
-  }
-  if (vecs <= 2048) TSB_LN(1024, 2, true);
-  // wider rows: weight and bias in shared memory in their memory type, 2 * 16 bytes per vector
+  // four vectors per thread: weight and bias in shared memory in their memory type (2 * 16 bytes per
+  // vector); measured faster than twice the threads with two vectors each and the weights in registers
+  if (vecs <= 1024) TSB_LN(256, 4, false);
+  if (vecs <= 2048) TSB_LN(512, 4, false);
   if (vecs <= 4096) TSB_LN(1024, 4, false);
 #undef TSB_LN
   return fail(TSB_ERR_UNSUPPORTED, "tsb_layernorm_fwd: rows of %lld elements exceed the on-chip limit (%d)",
