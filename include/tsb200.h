@@ -40,7 +40,7 @@ extern "C" {
 #endif
 
 #define TSB_MAX_RANK 3
-#define TSB_MAX_ACCESSES 16
+#define TSB_MAX_ACCESSES 24
 #define TSB_MAX_OPS 96
 #define TSB_NUM_REGS 16
 #define TSB_MAX_LOOPS 4
@@ -54,7 +54,7 @@ enum tsb_dtype {
   TSB_I16 = 4,
   TSB_I8 = 5,
   TSB_I1 = 6,  /* stored as one byte, like memref<..xi1> */
-  TSB_I64 = 7,
+  TSB_I64 = 7, /* memory type only: a value is its low 32 bits, sign-extended when stored (index tensors) */
   TSB_F64 = 8,
   TSB_U32 = 9,
   TSB_U16 = 10,
@@ -122,10 +122,10 @@ typedef struct tsb_access {
   int32_t n_wrap;      /* 0..2 wrap-around terms added to the address */
   int32_t pad2_;
   tsb_wrap wrap[2];
-  /* tsb_block_program only: per iteration of enclosing loop l (TSB_OP_LOOP_BEGIN slot l) the
+  /* per iteration of enclosing loop l (TSB_OP_LOOP_BEGIN slot l) the
    * element offset advances by offset_loop[l] and the mask start of dim d by
    * mask_start_loop[d][l] (loop-carried pointers and `for off in range(0, N, BLOCK)` offsets,
-   * PtrAnalysis.cpp:1536-1602).  Ignored by the other entry points. */
+   * PtrAnalysis.cpp:1536-1602).  tsb_elementwise reads them for a loop nest around its body; the other entry points ignore them. */
   int64_t offset_loop[TSB_MAX_LOOPS];
   int64_t mask_start_loop[TSB_MAX_RANK][TSB_MAX_LOOPS];
 } tsb_access;
@@ -157,8 +157,8 @@ enum tsb_opcode {
   TSB_OP_BITCAST = 91,
   TSB_OP_FMA = 92, /* math.fma: single rounding */
   TSB_OP_REDUCE = 100, /* tsb_block_program only: dst <- fold of reg a along dim imm2 with combiner opcode imm */
-  TSB_OP_LOOP_BEGIN = 101, /* tsb_block_program only: loop slot a runs imm iterations; b = index of the op after its LOOP_END */
-  TSB_OP_LOOP_END = 102,   /* tsb_block_program only: closes loop slot a */
+  TSB_OP_LOOP_BEGIN = 101, /* loop slot a runs imm iterations; tsb_block_program: b = index of the op after its LOOP_END */
+  TSB_OP_LOOP_END = 102,   /* closes loop slot a */
   TSB_OP_ARGREDUCE = 103   /* tsb_block_program only: (dst, c) <- (value, index) of the largest (imm = 1) or smallest
                               (imm = 0) element of reg a along dim imm2, indices from reg b, ties to the smaller index */
 };
@@ -181,6 +181,18 @@ enum tsb_cmp {
  */
 #define TSB_REG_ACC (-1)
 #define TSB_REG_IMM (-2)
+
+/*
+ * Data-dependent accesses (gather / scatter, the reference's tts.make_gather_scatter_tptr and
+ * unstructured loads/stores, TritonStructuredDialect.td:125-230): a load or store may take a per-lane
+ * element index that is added to the access's structured address, and / or a per-lane mask bit that
+ * is and-ed with the structured mask.  Flags TSB_MEM_INDEX / TSB_MEM_MASK sit in `imm` for
+ * tsb_elementwise bodies and in `imm2` for tsb_block_program bodies (where a store's imm names the
+ * dims it walks).  Operands: load  dst <- access[a] (index: b, mask: c);
+ *                            store access[a] <- b   (index: c, mask: dst).
+ */
+#define TSB_MEM_INDEX 1u
+#define TSB_MEM_MASK 2u
 
 typedef struct tsb_op {
   int32_t opcode; /* enum tsb_opcode */
@@ -209,7 +221,10 @@ int tsb_sm_count(void);
  * body is {memrefCopy loads, linalg.generic ops, memrefCopy stores}
  * (driver.py:116-133; CRunnerUtils.cpp:58-113; TritonArithToLinalg.cpp:104).
  * All accesses share one iteration space (sizes[] equal); loads of smaller
- * blocks are expressed with stride 0 along broadcast dims.
+ * blocks are expressed with stride 0 along broadcast dims.  The body may be wrapped in a perfect
+ * loop nest: leading TSB_OP_LOOP_BEGIN ops (a = nesting depth, imm = trip count) matched by
+ * trailing TSB_OP_LOOP_END ops; iteration it of depth l shifts every access by offset_loop[l] * it
+ * and its mask starts by mask_start_loop[d][l] * it, and the iterations of one program run in order.
  */
 int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
                     const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, void *stream);

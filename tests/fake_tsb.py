@@ -16,7 +16,7 @@ import numpy as np
 import oracle
 from triton_shared_b200.backend import runtime as rt
 
-_SIZE = {0: 4, 1: 2, 2: 2, 3: 4, 4: 2, 5: 1, 6: 1, 9: 4, 10: 2, 11: 1}
+_SIZE = {0: 4, 1: 2, 2: 2, 3: 4, 4: 2, 5: 1, 6: 1, 7: 8, 9: 4, 10: 2, 11: 1}
 _OPNAME = {v: k for k, v in rt.OPCODES.items()}
 _CMPF = {v: k for k, v in rt.CMPF.items()}
 _CMPI = {v: k for k, v in rt.CMPI.items()}
@@ -218,6 +218,11 @@ class FakeLib:
                 if name == "load":
                     A = accs[o.a]
                     elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes, it)
+                    bcast = lambda r: np.ascontiguousarray(np.broadcast_to(R[r], sizes)).reshape(-1)
+                    if o.imm2 & rt.MEM_INDEX:
+                        elem = elem + bcast(o.b).view(np.int32).astype(np.int64)
+                    if o.imm2 & rt.MEM_MASK:
+                        valid = valid & ((bcast(o.c) & 1) != 0)
                     if A.is_store == 2:
                         full = valid.astype(np.uint32)
                     elif A.is_store == 3:
@@ -228,6 +233,11 @@ class FakeLib:
                 elif name == "store":
                     A = accs[o.a]
                     elem, valid = self._acc_state(A, p, rank, sizes, idx, lanes, it)
+                    bcast = lambda r: np.ascontiguousarray(np.broadcast_to(R[r], sizes)).reshape(-1)
+                    if o.imm2 & rt.MEM_INDEX:
+                        elem = elem + bcast(o.c).view(np.int32).astype(np.int64)
+                    if o.imm2 & rt.MEM_MASK:
+                        valid = valid & ((bcast(o.dst) & 1) != 0)
                     m = int(o.imm)
                     val = np.broadcast_to(R[o.b], shape_of(m))
                     sel = take(np.arange(lanes), m).reshape(-1)  # one lane per walked element
@@ -303,6 +313,8 @@ class FakeLib:
             bits = _f32_to_bf16(reg.view(np.float32))
         elif dt == 6:
             bits = (reg & 1).astype(np.uint8)
+        elif dt == 7:  # 64-bit integers are held as their low 32 bits and stored sign-extended
+            bits = reg.view(np.int32).astype(np.int64).view(np.uint64)
         else:
             bits = reg.astype(np.uint32)
         for i in np.nonzero(valid)[0]:
@@ -444,6 +456,22 @@ class FakeLib:
     def tsb_gemm(self, a, b, c, dt, M, N, K, sam, sak, sbk, sbn, scm, scn, bm, bn, bk, tiles, n_prog, lo, hi,
                  status, stream):
         self.calls.append(("tsb_gemm", lo, hi))
+        if dt == 0:  # fp32 operands: the oracle's matmul is 16-bit only; numpy per tile
+            t = np.ctypeslib.as_array((ctypes.c_int32 * (2 * n_prog)).from_address(tiles)).reshape(-1, 2)
+            elem = lambda base, n: np.ctypeslib.as_array((ctypes.c_float * n).from_address(int(base)))
+            for pid in range(lo, hi):
+                r0, c0 = int(t[pid][0]) * bm, int(t[pid][1]) * bn
+                r1, c1 = min(r0 + bm, M), min(c0 + bn, N)
+                if r1 <= r0 or c1 <= c0:
+                    continue
+                ri, ci, ki = np.arange(r0, r1), np.arange(c0, c1), np.arange(K)
+                Af = np.array([[elem(a + 4 * (r * sam + k * sak), 1)[0] for k in ki] for r in ri], dtype=np.float32)
+                Bf = np.array([[elem(b + 4 * (k * sbk + cc * sbn), 1)[0] for cc in ci] for k in ki], dtype=np.float32)
+                Cf = Af @ Bf
+                for i, r in enumerate(ri):
+                    for j, cc in enumerate(ci):
+                        elem(c + 4 * (r * scm + cc * scn), 1)[0] = Cf[i, j]
+            return 0
         oracle.lib().orc_matmul(a, b, c, {1: 1, 2: 2}[dt], M, N, K, sam, sak, sbk, sbn, scm, scn, bm, bn, bk,
                                 tiles, lo, hi, 1)
         return 0

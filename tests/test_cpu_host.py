@@ -83,9 +83,10 @@ def test_vec_add_descriptor_matches_reference_lowering():
 def test_unsupported_kernel_is_rejected_at_compile_time():
     @triton.jit
     def gather_kernel(x_ptr, idx_ptr, out_ptr, BLOCK: tl_constexpr):
+        # atomics have no counterpart in the reference's lowering either
         offs = tl.arange(0, BLOCK)
         idx = tl.load(idx_ptr + offs)
-        tl.store(out_ptr + offs, tl.load(x_ptr + idx))
+        tl.atomic_add(out_ptr + idx, tl.load(x_ptr + offs))
 
     with pytest.raises(Exception) as e:
         triton.compile(ASTSource(gather_kernel, {"x_ptr": "*fp32", "idx_ptr": "*i32", "out_ptr": "*fp32", "BLOCK": "constexpr"},
@@ -456,3 +457,27 @@ def test_launch_hooks_are_called():
         knobs.runtime.launch_enter_hook, knobs.runtime.launch_exit_hook = old_enter, old_exit
     assert [s[0] for s in seen] == ["enter", "exit"] and seen[0][1] == "add_kernel"
     assert torch.equal(out, x + 1)
+
+
+# ------------------------------------------------------------------ the reference's own example tests
+def _reference_cases():
+    import reference_examples as R
+    # the host stand-in executes lanes in numpy: keep to the cases it finishes in seconds
+    return [c for c in R.cases() if "b=2048" not in c[0] and "b=4096" not in c[0] and "h=5120" not in c[0]
+            and "h=7680" not in c[0] and "h=8192" not in c[0] and "(128, 2, 4)" not in c[0] and "(64, 2, 4)" not in c[0]]
+
+
+_REF = _reference_cases()
+
+
+@pytest.mark.skipif(not _REF, reason="TSB_REFERENCE_EXAMPLES does not name a directory of reference examples")
+@pytest.mark.parametrize("case", _REF or [None], ids=[c[0] for c in _REF] or ["none"])
+def test_reference_example_on_host_stand_in(case):
+    """python/examples of the reference, unmodified, with B200Driver for CPUDriver and the C library
+    replaced by its host stand-in (plan compilation and descriptor evaluation are the real ones)."""
+    import reference_examples as R
+    import triton_shared_b200
+    triton_shared_b200.activate()
+    _, path, name, kw = case
+    with fake_device():
+        R.run_case(path, name, kw, "cpu")

@@ -275,6 +275,7 @@ def _mask_json(mask: Optional[TMask], shape):
 
 class _EwLowering:
     """Linearises the value graphs of all stores into VM ops over one iteration space."""
+    FLAG_FIELD = "imm"  # where a load / store carries its MEM_INDEX / MEM_MASK flags
 
     def __init__(self, kernel: Kernel, an: Analyzer, space: Tuple[int, ...]):
         self.k, self.an, self.space = kernel, an, space
@@ -383,7 +384,8 @@ class _EwLowering:
             ob = other_bits(acc.other, acc.elem)
             ai = self.acc_for("load", acc.elem, acc.shape, dimmap, acc.offset, acc.strides,
                               _mask_json(acc.mask, acc.shape), ob, acc.arg, acc.wrapped)
-            return self.emit("load", acc.elem, a=ai)
+            idx, msk, flags = self.lane_operands(acc, dimmap)
+            return self.emit("load", acc.elem, a=ai, b=idx, c=msk, **{self.FLAG_FIELD: flags})
         if op in ("splat",):
             return self.value(n.args[0], ())
         if op == "broadcast":
@@ -447,6 +449,15 @@ class _EwLowering:
             return self.emit("cast", n.dtype, a=a, imm=rt.DTYPES[src.dtype], imm2=mode)
         raise UnsupportedTTIR(f"operation {op} has no elementwise lowering")
 
+    def lane_operands(self, acc: Access, dimmap):
+        """(index register, mask register, flags) of an access with data-dependent offsets / mask."""
+        idx = msk = flags = 0
+        if acc.indirect is not None:
+            idx, flags = self.value(acc.indirect, dimmap), flags | rt.MEM_INDEX
+        if acc.mask_data is not None:
+            msk, flags = self.value(acc.mask_data, dimmap), flags | rt.MEM_MASK
+        return idx, msk, flags
+
     def lower(self, stores: List[Access]):
         for acc in stores:
             shape = acc.shape
@@ -454,7 +465,8 @@ class _EwLowering:
             v = self.value(acc.value, dimmap)
             ai = self.acc_for("store", acc.elem, shape, dimmap, acc.offset, acc.strides,
                               _mask_json(acc.mask, shape), None, acc.arg, acc.wrapped)
-            self.ops.append(["store", acc.elem, -1, ai, v, 0, 0, 0])
+            idx, msk, flags = self.lane_operands(acc, dimmap)
+            self.ops.append(["store", acc.elem, msk if flags & rt.MEM_MASK else -1, ai, v, idx, flags, 0])
         return self.allocate()
 
     def allocate(self):
@@ -464,14 +476,21 @@ class _EwLowering:
 
     def _allocate(self, hoist_loads: bool):
         ACC, IMM = rt.REG_ACC, rt.REG_IMM
-        loads = [o for o in self.ops if o[0] == "load"]
-        rest = [o for o in self.ops if o[0] != "load"]
+        # plain loads go first (all of them in flight before the first use); a load that takes an index
+        # or mask operand stays where its operands are computed
+        plain = lambda o: o[0] == "load" and o[6] == 0
+        loads = [o for o in self.ops if plain(o)]
+        rest = [o for o in self.ops if not plain(o)]
         ops = [list(o) for o in (loads + rest if hoist_loads else self.ops)]
-        slots = {"store": (4,), "select": (3, 4, 5), "fma": (3, 4, 5)}
+        slots = {"select": (3, 4, 5), "fma": (3, 4, 5)}
 
         def read_slots(o):
-            if o[0] in ("load", "const"):
+            if o[0] == "const":
                 return ()
+            if o[0] == "load":   # [load, type, dst, access, index, mask, flags, -]
+                return ((4,) if o[6] & rt.MEM_INDEX else ()) + ((5,) if o[6] & rt.MEM_MASK else ())
+            if o[0] == "store":  # [store, type, mask, access, value, index, flags, -]
+                return (4,) + ((5,) if o[6] & rt.MEM_INDEX else ()) + ((2,) if o[6] & rt.MEM_MASK else ())
             if o[0] in slots:
                 return slots[o[0]]
             return (3,) if len(_reads(o)) == 1 else (3, 4)
@@ -532,27 +551,16 @@ class _EwLowering:
         return out
 
 
-def _regs_used(ops) -> int:
-    """Highest register number an allocated body names, plus one (accumulator and immediate forms are negative)."""
-    hi = -1
-    for o in ops:
-        named = [] if o[0] == "store" else [o[2]]
-        if o[0] == "store":
-            named.append(o[4])
-        elif o[0] in ("select", "fma"):
-            named += [o[3], o[4], o[5]]
-        elif o[0] not in ("load", "const"):
-            named += [o[3]] if len(_reads(o)) == 1 else [o[3], o[4]]
-        hi = max([hi] + [r for r in named if isinstance(r, int)])
-    return hi + 1
-
-
 def _reads(o):
     opc = o[0]
-    if opc in ("load", "const", "iota", "loop_begin", "loop_end"):
+    if opc == "load":   # block programs: flags in imm2, index in b, mask in c
+        f = o[7] if isinstance(o[7], int) else 0
+        return ([o[4]] if f & rt.MEM_INDEX else []) + ([o[5]] if f & rt.MEM_MASK else [])
+    if opc in ("const", "iota", "loop_begin", "loop_end"):
         return []
-    if opc == "store":
-        return [o[4]]
+    if opc == "store":  # value in b; block programs: index in c, mask in dst
+        f = o[7] if isinstance(o[7], int) else 0
+        return [o[4]] + ([o[5]] if f & rt.MEM_INDEX else []) + ([o[2]] if f & rt.MEM_MASK else [])
     if opc in ("select", "fma"):
         return [o[3], o[4], o[5]]
     if opc in ("exp", "exp2", "log", "log2", "sqrt", "rsqrt", "sin", "cos", "tanh", "erf", "absf", "negf",
@@ -563,8 +571,19 @@ def _reads(o):
 
 def _remap(o, mapped):
     opc = o[0]
-    if opc == "store":
-        o[4] = mapped[o[4]]
+    if opc in ("store", "load"):
+        f = o[7] if isinstance(o[7], int) else 0
+        if opc == "store":
+            o[4] = mapped[o[4]]
+            if f & rt.MEM_INDEX:
+                o[5] = mapped[o[5]]
+            if f & rt.MEM_MASK:
+                o[2] = mapped[o[2]]
+        else:
+            if f & rt.MEM_INDEX:
+                o[4] = mapped[o[4]]
+            if f & rt.MEM_MASK:
+                o[5] = mapped[o[5]]
         return
     rs = _reads(o)
     if len(rs) >= 1:
@@ -604,6 +623,17 @@ class ElementwisePlan(Plan):
             stored_args.update(s.arg for s in stores)
             return len(segments) - 1
 
+        def lower_run(stores: List[Access]):
+            """A run of consecutive stores as one segment, or as several (launched in order) when
+            together they exceed the engine's limits on accesses, ops or live values."""
+            try:
+                return [lower_segment(stores)]
+            except UnsupportedTTIR:
+                if len(stores) == 1:
+                    raise
+                half = len(stores) // 2
+                return lower_run(stores[:half]) + lower_run(stores[half:])
+
         def walk(effects):
             tree, run = [], []
             for kind, e in effects:
@@ -611,7 +641,7 @@ class ElementwisePlan(Plan):
                     run.append(e)
                     continue
                 if run:
-                    tree.append(["seg", lower_segment(run)])
+                    tree.extend(["seg", i] for i in lower_run(run))
                     run = []
                 loop: Loop = e
                 for init in loop.inits:
@@ -622,7 +652,7 @@ class ElementwisePlan(Plan):
                         raise UnsupportedTTIR("elementwise family: loop bounds depend on program_id")
                 tree.append(["loop", loop.id, loop.lb, loop.ub, loop.step, walk(loop.effects)])
             if run:
-                tree.append(["seg", lower_segment(run)])
+                tree.extend(["seg", i] for i in lower_run(run))
             return tree
 
         tree = walk(kernel.effects)
@@ -786,7 +816,10 @@ class ElementwisePlan(Plan):
             x = ops[k]
             x.opcode = rt.OPCODES[opc]
             x.type = rt.DTYPES[dt]
-            x.dst, x.a, x.b, x.c = (dst if opc != "store" else 0), ra, rb, rc
+            # a store names no result; in tsb_elementwise bodies its dst field carries the mask operand
+            flags = imm2 if "loops" in seg else imm  # block programs keep the memory flags in imm2
+            store_mask = opc == "store" and isinstance(flags, int) and flags & rt.MEM_MASK
+            x.dst, x.a, x.b, x.c = (dst if (opc != "store" or store_mask) else 0), ra, rb, rc
             if isinstance(imm, (list, tuple)) and imm[0] == "trip":
                 q = trips[str(imm[1])]
                 x.imm = max(0, int(q.evaluate(e0)))
@@ -937,6 +970,8 @@ class _BpLowering(_EwLowering):
         self.red_pos = red_pos
         self.arg_pairs: Dict[tuple, tuple] = {}
 
+    FLAG_FIELD = "imm2"  # a block-program store's imm names the dims it walks
+
     def acc_for(self, kind, elem, shape, dimmap, offset, strides, mask, other, arg=None, wrapped=()):
         # a mask bound that moves with a loop counter (`k < K - it*BLOCK`) is the same mask with the
         # counter moved into the start (`it*BLOCK + k < K`): dims = max(min(s+size,b),s)-s is shift-invariant
@@ -1026,7 +1061,8 @@ class _BpLowering(_EwLowering):
                 v = self.value(e.value, dimmap)
                 ai = self.acc_for("store", e.elem, e.shape, dimmap, e.offset, e.strides,
                                   _mask_json(e.mask, e.shape), None, e.arg, e.wrapped)
-                self.ops.append(["store", e.elem, -1, ai, v, 0, self.acc_mask[ai], 0])
+                idx, msk, flags = self.lane_operands(e, dimmap)
+                self.ops.append(["store", e.elem, msk if flags & rt.MEM_MASK else -1, ai, v, idx, self.acc_mask[ai], flags])
                 continue
             loop: Loop = e
             if depth >= 4:
@@ -1145,7 +1181,7 @@ class _BpLowering(_EwLowering):
         if len(masks) > 24:
             raise UnsupportedTTIR("block program: more than 24 block values alive")
         if len(out) > rt.TSB_MAX_OPS or len(self.accs) > rt.TSB_MAX_ACCESSES:
-            raise UnsupportedTTIR("block program: too many ops or accesses")
+            raise UnsupportedTTIR(f"block program: {len(out)} ops or {len(self.accs)} accesses exceed {rt.TSB_MAX_OPS} / {rt.TSB_MAX_ACCESSES}")
         words = sum(int(np.prod([self.space[d] for d in range(len(self.space)) if m & (1 << d)])) for m in masks)
         if words * 4 > 200 * 1024:
             raise UnsupportedTTIR(f"block program: {words * 4} bytes of block values exceed the 200 KB on-chip budget")
@@ -1564,11 +1600,18 @@ class GemmPlan(Plan):
         if const_value(loop.inits[acc_k].node) != 0.0:
             raise UnsupportedTTIR("gemm family: accumulator does not start at zero")
         rb: Dict[str, Node] = {}
-        if not match(st.value, ("trunc", ("attrs", ("$", "r"), {"loop": loop.id, "k": acc_k})), rb) or rb["r"].op != "loop_result":
-            raise UnsupportedTTIR("gemm family: store does not write the (truncated) accumulator")
+        res = ("attrs", ("$", "r"), {"loop": loop.id, "k": acc_k})
+        tail = None
+        if not match(st.value, ("trunc", res), rb) or rb["r"].op != "loop_result":
+            # a peeled last K step after the loop: acc = dot(load, load, loop result), masked along K
+            rb = {}
+            if not match(st.value, ("trunc", ("op", "dot", ("$", "a2"), ("$", "b2"), res)), rb) or rb["r"].op != "loop_result" \
+                    or rb["a2"].op != "load" or rb["b2"].op != "load":
+                raise UnsupportedTTIR("gemm family: store does not write the (truncated) accumulator")
+            tail = (an.access_of(rb["a2"]), an.access_of(rb["b2"]))
         A, B = an.access_of(b["a"]), an.access_of(b["b"])
-        if A.elem not in ("f16", "bf16") or B.elem != A.elem or st.elem != A.elem:
-            raise UnsupportedTTIR("gemm family: operands and result must all be f16 or all bf16")
+        if A.elem not in ("f16", "bf16", "f32") or B.elem != A.elem or st.elem != A.elem:
+            raise UnsupportedTTIR("gemm family: operands and result must all be f16, all bf16 or all f32")
         if len(A.shape) != 2 or len(B.shape) != 2 or len(st.shape) != 2 or A.shape[1] != B.shape[0] \
                 or st.shape != (A.shape[0], B.shape[1]):
             raise UnsupportedTTIR("gemm family: block shapes do not form a matmul")
@@ -1614,6 +1657,17 @@ class GemmPlan(Plan):
         }
         if st.wrapped:
             raise UnsupportedTTIR("gemm family: wrap-around store")
+        if tail is not None:
+            A2, B2 = tail
+            if A2.arg != A.arg or B2.arg != B.arg or A2.shape != A.shape or B2.shape != B.shape or \
+                    A2.strides != A.strides or B2.strides != B.strides or A2.wrapped != A.wrapped or B2.wrapped != B.wrapped:
+                raise UnsupportedTTIR("gemm family: the peeled K step addresses other blocks than the loop")
+            ka2, kb2 = _single_bound(A2.mask, 1), _single_bound(B2.mask, 0)
+            if ka2 is None or kb2 is None or other_bits(A2.other, A.elem) != 0 or other_bits(B2.other, A.elem) != 0:
+                raise UnsupportedTTIR("gemm family: the peeled K step needs K masks with other=0")
+            if mka is not None or mkb is not None:
+                raise UnsupportedTTIR("gemm family: K masks both in the loop and in a peeled step")
+            params["tail"] = {"a_off": A2.offset, "b_off": B2.offset, "ka": list(ka2), "kb": list(kb2)}
         return GemmPlan(kernel.name, params)
 
     def __init__(self, name, params):
@@ -1638,6 +1692,16 @@ class GemmPlan(Plan):
                 if K is not None and K != k_here:
                     raise UnsupportedTTIR("gemm family: A and B K-masks disagree")
                 K = k_here
+        tail = p.get("tail")
+        if tail is not None:
+            # loop of `trip` full steps plus one masked step: the same product with K taken from the tail mask
+            ks = ev(tail["ka"][0])
+            if ks != trip * BK or ev(tail["kb"][0]) != ks or ev(tail["kb"][1]) != ev(tail["ka"][1]):
+                raise UnsupportedTTIR("gemm family: the peeled K step does not continue where the loop ends")
+            K = ev(tail["ka"][1])
+            if not (ks < K <= ks + BK):
+                raise UnsupportedTTIR(f"gemm family: peeled K step covers [{ks}, {K}) which is not one block")
+            trip += 1
         if K is None:
             K = trip * BK
         if trip != -(-K // BK) and not (K <= 0 and trip == 0):
@@ -1696,6 +1760,11 @@ class GemmPlan(Plan):
         for key, lim, what in (("am", M, "A rows"), ("bn", N, "B columns")):
             if p[key] is not None and ev(p[key][1]) != lim:
                 raise UnsupportedTTIR(f"gemm family: mask bound of {what} differs from the store bound")
+        if tail is not None:
+            steps = ev(p["trip"])
+            if np.any(full(tail["a_off"]) != full(p["a_base"]) + steps * ev(p["a_adv"])) or \
+                    np.any(full(tail["b_off"]) != full(p["b_base"]) + steps * ev(p["b_adv"])):
+                raise UnsupportedTTIR("gemm family: the peeled K step does not address the next K block")
         unmasked_rows = p["am"] is None and p["a_wrap"] is None and p["cm"] is None
         tiles = np.stack([row0 // BM, col0 // BN], axis=1).astype(np.int32)
         return dict(M=M, N=N, K=K, sam=sam, sak=sak, sbk=sbk, sbn=sbn, scm=scm, scn=scn, tiles=tiles,

@@ -11,7 +11,7 @@ _PKG = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_PKG, "libtsb200.so")
 
 TSB_MAX_RANK = 3
-TSB_MAX_ACCESSES = 16
+TSB_MAX_ACCESSES = 24
 TSB_MAX_OPS = 96
 TSB_NUM_REGS = 16
 TSB_MAX_LOOPS = 4

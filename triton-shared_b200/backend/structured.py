@@ -260,6 +260,7 @@ class SPtr:
     arg: int
     elem: str
     offset: Poly
+    indirect: Optional["Node"] = None  # data-dependent element offset (a scalar integer value)
 
 
 @dataclass(frozen=True)
@@ -270,6 +271,9 @@ class TPtr:
     offset: Poly
     strides: Tuple[Poly, ...]
     wrapped: Tuple[Wrapped, ...] = ()
+    # data-dependent element offsets (an integer block value of this shape) added to the structured
+    # address: what the reference turns into tts.make_gather_scatter_tptr / unstructured accesses
+    indirect: Optional["Node"] = None
 
 
 @dataclass(frozen=True)
@@ -316,6 +320,8 @@ class Access:
     value: Optional[Node] = None  # stored value
     loops: Tuple[int, ...] = ()
     index: int = -1
+    indirect: Optional[Node] = None   # per-lane element offsets computed as data (gather / scatter)
+    mask_data: Optional[Node] = None  # per-lane i1 mask computed as data (conjoined with `mask`)
 
 
 @dataclass
@@ -406,8 +412,56 @@ class Analyzer:
             else:
                 raise UnsupportedTTIR(f"kernel argument of type {ty.elem}")
         effects: List[object] = []
-        self.walk(self.fn.body, env, effects, (), True)
+        self.guards: List[object] = []  # conditions under which the rest of the kernel runs (early returns)
+        self._walk_cfg(self.fn.body, env, effects, 0)
         return Kernel(self.fn.name, self.fn.args, self.accesses, effects, self.loops)
+
+    def _walk_cfg(self, block: Block, env, effects, depth: int):
+        """Walk a function body whose only control flow between blocks is the early return
+        (`if cond: return`): a conditional branch one of whose targets returns at once.  The
+        condition becomes a guard and-ed into the mask of every later access."""
+        if depth > 16:
+            raise UnsupportedTTIR("control flow between blocks nests too deeply")
+        for op in block.ops:
+            if op.name == "cf.br":
+                return self._walk_cfg(self._target(op.attrs["dests"][0]), env, effects, depth + 1)
+            if op.name == "cf.cond_br":
+                cond = env[op.operands[0]]
+                yes, no = (self._target(d) for d in op.attrs["dests"])
+                returns = lambda b: len(b.ops) == 1 and b.ops[0].name == "tt.return"
+                if returns(yes):
+                    self.guards.append((cond, False))
+                    return self._walk_cfg(no, env, effects, depth + 1)
+                if returns(no):
+                    self.guards.append((cond, True))
+                    return self._walk_cfg(yes, env, effects, depth + 1)
+                raise UnsupportedTTIR("conditional branch other than an early return")
+            self.visit(op, env, effects, (), True)
+
+    def _target(self, label: str) -> Block:
+        b = self.fn.blocks.get(label)
+        if b is None or b.args:
+            raise UnsupportedTTIR(f"branch to {label}: unknown block or block with arguments")
+        return b
+
+    def _guarded(self, shape, mask, mask_data):
+        """(mask, mask_data) with the early-return guards added."""
+        for cond, want in self.guards:
+            if isinstance(cond, SInt):
+                p = cond.poly if want else Poly.fn("cmp_eq", cond.poly, Poly.const(0))
+                base = mask if mask is not None else TMask(tuple(shape), tuple(() for _ in shape))
+                mask = TMask(base.shape, base.dims, base.scalar_conds + (p,))
+            else:
+                n = self.as_data(cond)
+                if n.shape != ():
+                    raise UnsupportedTTIR("branch on a block value")
+                if not want:
+                    one = self.node("sint", (), {"poly": Poly.const(1)}, (), "i1")
+                    n = self.node("xori", (n, one), (), (), "i1")
+                if shape:
+                    n = self.node("splat", (n,), (), tuple(shape), "i1")
+                mask_data = n if mask_data is None else self.node("andi", (mask_data, n), (), tuple(shape), "i1")
+        return mask, mask_data
 
     # ---- helpers
     def as_data(self, v, ty_shape=None) -> Node:
@@ -417,12 +471,24 @@ class Analyzer:
         if isinstance(v, SInt):
             return self.node("sint", (), {"poly": v.poly}, (), v.elem)
         if isinstance(v, TIdx):
-            if v.wrapped:
-                raise UnsupportedTTIR("wrapped (modulo) index tensor used as data")
-            return self.node("index", (), {"offset": v.offset, "strides": v.strides}, v.shape, v.elem)
+            n = self.node("index", (), {"offset": v.offset, "strides": v.strides}, v.shape, v.elem)
+            zero = Poly.const(0)
+            for w in v.wrapped:
+                # scale * ((inner_offset + inner_stride * i_dim) mod modulus) as lane arithmetic
+                st = tuple(w.inner_stride if d == w.dim else zero for d in range(len(v.shape)))
+                inner = self.node("index", (), {"offset": w.inner_offset, "strides": st}, v.shape, v.elem)
+                r = self.node("remsi", (inner, self._splat_int(w.modulus, v.shape, v.elem)), (), v.shape, v.elem)
+                if w.scale != Poly.const(1):
+                    r = self.node("muli", (r, self._splat_int(w.scale, v.shape, v.elem)), (), v.shape, v.elem)
+                n = self.node("addi", (n, r), (), v.shape, v.elem)
+            return n
         if isinstance(v, TMask):
             return self.node("maskval", (), {"dims": v.dims, "conds": v.scalar_conds}, v.shape, "i1")
         raise UnsupportedTTIR(f"value of kind {type(v).__name__} used as data")
+
+    def _splat_int(self, p: Poly, shape, elem) -> Node:
+        n = self.node("sint", (), {"poly": p}, (), elem)
+        return self.node("splat", (n,), (), tuple(shape), elem) if shape else n
 
     @staticmethod
     def _shape_of(v):
@@ -458,6 +524,8 @@ class Analyzer:
             env[res] = self._expand_dims(get(0), op.attrs["axis"], rty)
         elif n == "tt.broadcast":
             env[res] = self._broadcast(get(0), rty)
+        elif n == "tt.reshape":
+            env[res] = self._reshape(get(0), rty.shape)
         elif n == "tt.addptr":
             env[res] = self._addptr(get(0), get(1))
         elif n in _BIN_INT:
@@ -525,7 +593,8 @@ class Analyzer:
         if isinstance(v, SInt):
             return TIdx(ty.shape, v.poly, zeros, v.elem)
         if isinstance(v, SPtr):
-            return TPtr(v.arg, v.elem, ty.shape, v.offset, zeros)
+            ind = None if v.indirect is None else self.node("splat", (v.indirect,), (), ty.shape, v.indirect.dtype)
+            return TPtr(v.arg, v.elem, ty.shape, v.offset, zeros, (), ind)
         if isinstance(v, TData):
             return TData(self.node("splat", (v.node,), (), ty.shape, v.node.dtype))
         raise UnsupportedTTIR("tt.splat of an unsupported value")
@@ -542,7 +611,9 @@ class Analyzer:
         if isinstance(v, TIdx):
             return TIdx(ins(v.shape, 1), v.offset, ins(v.strides, Poly.const(0)), v.elem, shift(v.wrapped))
         if isinstance(v, TPtr):
-            return TPtr(v.arg, v.elem, ins(v.shape, 1), v.offset, ins(v.strides, Poly.const(0)), shift(v.wrapped))
+            ind = None if v.indirect is None else self.node("expand_dims", (v.indirect,), {"axis": axis}, ins(v.shape, 1),
+                                                            v.indirect.dtype)
+            return TPtr(v.arg, v.elem, ins(v.shape, 1), v.offset, ins(v.strides, Poly.const(0)), shift(v.wrapped), ind)
         if isinstance(v, TMask):
             return TMask(ins(v.shape, 1), ins(v.dims, ()), v.scalar_conds)
         if isinstance(v, TData):
@@ -558,22 +629,36 @@ class Analyzer:
                     raise UnsupportedTTIR("broadcast along a wrapped dimension")
             if isinstance(v, TIdx):
                 return TIdx(ty.shape, v.offset, strides, v.elem, v.wrapped)
-            return TPtr(v.arg, v.elem, ty.shape, v.offset, strides, v.wrapped)
+            ind = None if v.indirect is None else self.node("broadcast", (v.indirect,), (), ty.shape, v.indirect.dtype)
+            return TPtr(v.arg, v.elem, ty.shape, v.offset, strides, v.wrapped, ind)
         if isinstance(v, TMask):
             return TMask(ty.shape, v.dims, v.scalar_conds)
         if isinstance(v, TData):
             return TData(self.node("broadcast", (v.node,), (), ty.shape, v.node.dtype))
         raise UnsupportedTTIR("tt.broadcast of an unsupported value")
 
+    def _add_indirect(self, ind: Optional[Node], n: Node, shape) -> Node:
+        return n if ind is None else self.node("addi", (ind, n), (), tuple(shape), n.dtype)
+
     def _addptr(self, p, o):
         if isinstance(p, SPtr) and isinstance(o, SInt):
-            return SPtr(p.arg, p.elem, p.offset + o.poly)
+            return SPtr(p.arg, p.elem, p.offset + o.poly, p.indirect)
+        if isinstance(p, SPtr) and isinstance(o, TData) and o.node.shape == ():
+            # a scalar offset that was loaded from memory: a data-dependent base
+            return SPtr(p.arg, p.elem, p.offset, self._add_indirect(p.indirect, o.node, ()))
         if isinstance(p, TPtr) and isinstance(o, TIdx):
             if p.shape != o.shape:
                 raise UnsupportedTTIR("tt.addptr shape mismatch")
             return TPtr(p.arg, p.elem, p.shape, p.offset + o.offset,
-                        tuple(a + b for a, b in zip(p.strides, o.strides)), p.wrapped + o.wrapped)
-        raise UnsupportedTTIR("tt.addptr with a data-dependent offset (gather/scatter) is outside the structured subset")
+                        tuple(a + b for a, b in zip(p.strides, o.strides)), p.wrapped + o.wrapped, p.indirect)
+        if isinstance(p, TPtr) and isinstance(o, TData):
+            # offsets that are block data (loaded indices, divisions of lane numbers, ...): kept as a
+            # per-lane index added to the structured part of the address (gather / scatter)
+            if o.node.shape != p.shape:
+                raise UnsupportedTTIR("tt.addptr shape mismatch")
+            return TPtr(p.arg, p.elem, p.shape, p.offset, p.strides, p.wrapped,
+                        self._add_indirect(p.indirect, o.node, p.shape))
+        raise UnsupportedTTIR("tt.addptr of these operand kinds is outside the supported subset")
 
     def _bin_int(self, name, a, b, ty: Type):
         if isinstance(a, SInt) and isinstance(b, SInt):
@@ -658,25 +743,36 @@ class Analyzer:
         na, nb = self.as_data(a), self.as_data(b)
         return TData(self.node("cmpi", (na, nb), {"pred": pred}, ty.shape, "i1"))
 
+    def _split_mask(self, mask, p):
+        """A tt.load / tt.store mask operand as (structured TMask or None, data mask node or None)."""
+        if mask is None or isinstance(mask, TMask):
+            return mask, None
+        if isinstance(mask, SInt) and isinstance(p, SPtr):
+            return TMask((), (), (mask.poly,)), None
+        if isinstance(mask, TData) and mask.node.dtype == "i1":
+            return None, mask.node
+        if isinstance(mask, TIdx) and mask.elem == "i1" and mask.uniform:
+            return TMask(mask.shape, tuple(() for _ in mask.shape), (mask.offset,)), None
+        raise UnsupportedTTIR("mask operand of an unsupported kind")
+
     def _load(self, op: Op, env, loop_stack, record, ty: Type):
         p = env[op.operands[0]]
         mask = env[op.operands[1]] if len(op.operands) > 1 else None
         other = env[op.operands[2]] if len(op.operands) > 2 else None
-        if mask is not None and not isinstance(mask, TMask):
-            if isinstance(mask, SInt) and isinstance(p, SPtr):
-                mask = TMask((), (), (mask.poly,))
-            else:
-                raise UnsupportedTTIR("load mask is not a structured range comparison")
+        if not isinstance(p, (SPtr, TPtr)):
+            raise UnsupportedTTIR("load from a non-structured pointer")
+        mask, mask_data = self._split_mask(mask, p)
         other_node = None
         if other is not None:
             other_node = self.as_data(other)
+        shape = p.shape if isinstance(p, TPtr) else ()
+        mask, mask_data = self._guarded(shape, mask, mask_data)
         if isinstance(p, SPtr):
             acc = Access("load", p.arg, p.elem, (), p.offset, (), mask, other_node, (), None, loop_stack)
-        elif isinstance(p, TPtr):
+        else:
             acc = Access("load", p.arg, p.elem, p.shape, p.offset, p.strides, mask, other_node, p.wrapped,
                          None, loop_stack)
-        else:
-            raise UnsupportedTTIR("load from a non-structured pointer")
+        acc.indirect, acc.mask_data = p.indirect, mask_data
         if record:
             acc.index = len(self.accesses)
             self.accesses.append(acc)
@@ -694,22 +790,91 @@ class Analyzer:
         p = env[op.operands[0]]
         val = self.as_data(env[op.operands[1]])
         mask = env[op.operands[2]] if len(op.operands) > 2 else None
-        if mask is not None and not isinstance(mask, TMask):
-            if isinstance(mask, SInt) and isinstance(p, SPtr):
-                mask = TMask((), (), (mask.poly,))
-            else:
-                raise UnsupportedTTIR("store mask is not a structured range comparison")
+        if not isinstance(p, (SPtr, TPtr)):
+            raise UnsupportedTTIR("store to a non-structured pointer")
+        if val.op == "reshape" and isinstance(p, TPtr):
+            # store(ptr, reshape(v)) == store(reshape(ptr), v): the reshape moves to the address side
+            src = val.args[0]
+            p = self._reshape(p, src.shape)
+            if mask is not None:
+                mask = self._reshape(mask, src.shape)
+            val = src
+        mask, mask_data = self._split_mask(mask, p)
+        shape = p.shape if isinstance(p, TPtr) else ()
+        mask, mask_data = self._guarded(shape, mask, mask_data)
         if isinstance(p, SPtr):
             acc = Access("store", p.arg, p.elem, (), p.offset, (), mask, None, (), val, loop_stack)
-        elif isinstance(p, TPtr):
+        else:
             acc = Access("store", p.arg, p.elem, p.shape, p.offset, p.strides, mask, None, p.wrapped, val,
                          loop_stack)
-        else:
-            raise UnsupportedTTIR("store to a non-structured pointer")
+        acc.indirect, acc.mask_data = p.indirect, mask_data
         if record:
             acc.index = len(self.accesses)
             self.accesses.append(acc)
             effects.append(("store", acc))
+
+    # ---- tt.reshape: row-major re-indexing of the same elements
+    @staticmethod
+    def _row_major_strides(shape, unit: Poly):
+        st, acc = [], unit
+        for n in reversed(shape):
+            st.append(acc)
+            acc = acc * n
+        return tuple(reversed(st))
+
+    def _reshape(self, v, shape):
+        shape = tuple(shape)
+        if isinstance(v, (TIdx, TPtr)):
+            if v.wrapped or (isinstance(v, TPtr) and v.indirect is not None):
+                raise UnsupportedTTIR("tt.reshape of a wrapped or data-dependent pointer")
+            # the source must enumerate its elements as base + unit * (row-major lane number)
+            live = [d for d in range(len(v.shape)) if v.shape[d] > 1]
+            unit = v.strides[live[-1]] if live else Poly.const(0)
+            if tuple(v.strides[d] for d in live) != tuple(self._row_major_strides([v.shape[d] for d in live], unit)):
+                raise UnsupportedTTIR("tt.reshape of a block whose lanes are not evenly spaced in row-major order")
+            st = tuple(s if n > 1 else Poly.const(0) for s, n in zip(self._row_major_strides(shape, unit), shape))
+            if isinstance(v, TIdx):
+                return TIdx(shape, v.offset, st, v.elem)
+            return TPtr(v.arg, v.elem, shape, v.offset, st)
+        if isinstance(v, TMask):
+            dims = []
+            for d, cons in enumerate(v.dims):
+                for start, bound in cons:
+                    # only a constraint that is known to admit the whole dim can be dropped
+                    if not (start.is_const and bound.is_const and start.as_const + v.shape[d] <= bound.as_const):
+                        raise UnsupportedTTIR("tt.reshape of a mask that may cut the block")
+            return TMask(shape, tuple(() for _ in shape), v.scalar_conds)
+        if isinstance(v, TData):
+            n = v.node
+            if n.op == "load" and n.id in getattr(self, "_load_nodes", {}):
+                # reshape(load(ptr)) == load(reshape(ptr)): re-issue the load with the reshaped address
+                acc = self._load_nodes[n.id]
+                if acc.indirect is None and acc.mask_data is None and not acc.wrapped:
+                    src = TPtr(acc.arg, acc.elem, acc.shape, acc.offset, acc.strides)
+                    q = self._reshape(src, shape)
+                    mask = self._reshape(acc.mask, shape) if acc.mask is not None else None
+                    other = acc.other
+                    if other is not None and other.shape not in ((), shape):
+                        base = other
+                        while base.op in ("splat", "broadcast", "expand_dims"):
+                            base = base.args[0]
+                        if base.op == "const":
+                            other = self.node("const", (), dict(base.attrs), shape, base.dtype)
+                        elif base.op == "index" and all(st.is_zero for st in base.attr("strides")):
+                            other = self.node("index", (), {"offset": base.attr("offset"),
+                                                            "strides": tuple(Poly.const(0) for _ in shape)}, shape, base.dtype)
+                        else:
+                            other = self.node("splat", (base,), (), shape, base.dtype) if base.shape == () else None
+                        if other is None:
+                            raise UnsupportedTTIR("tt.reshape of a load whose `other` is not a splat")
+                    new = Access("load", q.arg, q.elem, shape, q.offset, q.strides, mask, other, (), None, acc.loops)
+                    new.index = len(self.accesses)
+                    self.accesses.append(new)
+                    node = self.node("load", (), {"access": new.index, "rec": True}, shape, n.dtype)
+                    self._load_nodes[node.id] = new
+                    return TData(node)
+            return TData(self.node("reshape", (n,), (), shape, n.dtype))
+        raise UnsupportedTTIR("tt.reshape of an unsupported value")
 
     def _reduce(self, op: Op, env):
         blk = op.regions[0]
@@ -749,7 +914,62 @@ class Analyzer:
                                                     {"axis": op.attrs["axis"], "comb": kind, "out": k},
                                                     rty.shape, rty.elem))
 
+    MAX_UNROLL = 64
+
     def _for(self, op: Op, env, effects, loop_stack, record):
+        """A loop is first analysed symbolically (carried pointers and integers advance by a
+        loop-invariant amount, carried block data become iter_arg nodes).  Where that fails (a
+        carried index tensor that is recomputed non-linearly, a carried value that changes kind, ...)
+        and the trip count is a small constant, the loop is unrolled instead: its body is walked
+        once per iteration with the induction variable a constant."""
+        snap = (len(self.accesses), len(effects), set(self.loops), self._next_loop, dict(getattr(self, "_load_nodes", {})),
+                dict(env))
+        lb, ub, step = (env.get(o) for o in op.operands[:3])
+        const = all(isinstance(x, SInt) and x.poly.is_const for x in (lb, ub, step))
+        trip = -(-(ub.poly.as_const - lb.poly.as_const) // step.poly.as_const) if const and step.poly.as_const > 0 else None
+        can_unroll = trip is not None and trip <= self.MAX_UNROLL
+        # a carried integer block value is an index tensor that the body recomputes: as a loop-carried
+        # datum it could only run as a block program, which has no data-dependent addressing
+        carried_index = any(isinstance(env.get(o), TData) and env[o].node.dtype.startswith("i") and env[o].node.shape
+                            for o in op.operands[3:])
+        try:
+            if can_unroll and carried_index:
+                raise UnsupportedTTIR("loop carries an index tensor as data")
+            return self._for_structured(op, env, effects, loop_stack, record)
+        except UnsupportedTTIR:
+            if not can_unroll:
+                raise
+            del self.accesses[snap[0]:]
+            del effects[snap[1]:]
+            for k in set(self.loops) - snap[2]:
+                del self.loops[k]
+            self._next_loop = snap[3]
+            self._load_nodes = snap[4]
+            env.clear()
+            env.update(snap[5])
+            self._for_unrolled(op, env, effects, loop_stack, record, lb.poly.as_const, step.poly.as_const, max(trip, 0))
+
+    def _for_unrolled(self, op: Op, env, effects, loop_stack, record, lb: int, step: int, trip: int):
+        blk = op.regions[0]
+        iv_name, iv_ty = blk.args[0]
+        iter_args = blk.args[1:]
+        if blk.ops and blk.ops[-1].name == "scf.yield":
+            yield_op, body_ops = blk.ops[-1], blk.ops[:-1]
+        else:
+            yield_op, body_ops = None, blk.ops
+        cur = [env[o] for o in op.operands[3:]]
+        for t in range(trip):
+            e = dict(env)
+            e[iv_name] = SInt(Poly.const(lb + t * step), iv_ty.elem)
+            for (name, _), v in zip(iter_args, cur):
+                e[name] = v
+            self.walk(Block(blk.args, body_ops), e, effects, loop_stack, record)
+            if yield_op is not None:
+                cur = [e[y] for y in yield_op.operands]
+        for (rname, _), v in zip(op.results, cur):
+            env[rname] = v
+
+    def _for_structured(self, op: Op, env, effects, loop_stack, record):
         lb, ub, step = (env[o] for o in op.operands[:3])
         if not all(isinstance(x, SInt) for x in (lb, ub, step)):
             raise UnsupportedTTIR("scf.for bounds are not scalar integers")
@@ -772,6 +992,8 @@ class Analyzer:
             e = dict(env)
             e[iv_name] = iv
             for k, ((name, ty), init) in enumerate(zip(iter_args, inits)):
+                if isinstance(init, (TPtr, SPtr)) and init.indirect is not None:
+                    raise UnsupportedTTIR("loop-carried pointer with data-dependent offsets")
                 if isinstance(init, (TPtr, SPtr, SInt, TIdx)):
                     adv = Poly.atom(("carry", lid, k)) if deltas is None else it * deltas[k]
                     if isinstance(init, TPtr):
@@ -804,8 +1026,8 @@ class Analyzer:
                 raise UnsupportedTTIR("loop-carried value changes kind")
             if isinstance(y, (TPtr, TIdx)) and (y.strides != cur.strides or y.wrapped != cur.wrapped):
                 raise UnsupportedTTIR("loop-carried pointer changes strides")
-            if isinstance(y, (TPtr, SPtr)) and y.arg != cur.arg:
-                raise UnsupportedTTIR("loop-carried pointer changes base")
+            if isinstance(y, (TPtr, SPtr)) and (y.arg != cur.arg or y.indirect is not None):
+                raise UnsupportedTTIR("loop-carried pointer changes base or gains data-dependent offsets")
             d = off(y) - off(cur)
             if any(a[0] == "carry" and a[1] == lid for a in d.atoms()) or any(a == ("it", lid) for a in d.atoms()):
                 raise UnsupportedTTIR("loop-carried pointer advance is not loop-invariant")

@@ -88,6 +88,7 @@ class Function:
     name: str
     args: List[Tuple[str, Type]]
     body: Block
+    blocks: Dict[str, Block] = field(default_factory=dict)  # labelled successor blocks (^bb1, ...) of the body
 
 
 _SSA = r"%[A-Za-z0-9_.$#-]+"
@@ -158,7 +159,8 @@ def _find_trailing_type(s: str) -> Tuple[str, str]:
 
 class _Lines:
     def __init__(self, text: str):
-        self.lines = [l.rstrip() for l in text.splitlines()]
+        # a trailing `// pred: ^bb0` comment follows block labels
+        self.lines = [re.sub(r"\s+//.*$", "", l.rstrip()) for l in text.splitlines()]
         self.i = 0
 
     def peek(self) -> Optional[str]:
@@ -202,25 +204,36 @@ def _parse_func(line: str, L: _Lines) -> Function:
         # strip an argument attribute dict such as {tt.divisibility = 16 : i32}
         ty = re.sub(r"\s*\{[^}]*\}\s*$", "", ty)
         args.append((am.group(1), parse_type(ty)))
-    body = _parse_block_body(L)
-    return Function(m.group(1), args, body)
+    labels: Dict[str, Block] = {}
+    body = _parse_block_body(L, labels=labels)
+    return Function(m.group(1), args, body, labels)
 
 
-def _parse_block_body(L: _Lines, block: Optional[Block] = None) -> Block:
-    """Parse ops until the closing '}' (consumed). Returns the block."""
-    blk = block or Block()
+def _parse_block_body(L: _Lines, block: Optional[Block] = None, labels: Optional[Dict[str, Block]] = None) -> Block:
+    """Parse ops until the closing '}' (left for the caller). Returns the (entry) block.  A label
+    before the first op names the block's own arguments (region bodies); later labels start the
+    successor blocks of a function body, collected into `labels`."""
+    entry = blk = block or Block()
     while True:
         line = L.peek()
         if line is None:
             raise UnsupportedTTIR("unexpected end of module")
         if line.startswith("}"):
-            return blk  # caller inspects/consumes the closing line
+            return entry  # caller inspects/consumes the closing line
         L.next()
         if line.startswith("^bb"):
-            m = re.match(r"\^bb\d+\((.*)\):$", line)
-            for a in _split_top(m.group(1)):
+            m = re.match(r"(\^bb\d+)(?:\((.*)\))?:$", line)
+            if not m:
+                raise UnsupportedTTIR(f"cannot parse block label: {line}")
+            if blk is entry and not blk.ops and not blk.args and labels is None:
+                target = blk
+            else:
+                if labels is None:
+                    raise UnsupportedTTIR("control flow between blocks inside a region")
+                target = blk = labels.setdefault(m.group(1), Block())
+            for a in _split_top(m.group(2) or ""):
                 am = re.match(rf"({_SSA})\s*:\s*(.*)$", a)
-                blk.args.append((am.group(1), parse_type(am.group(2))))
+                target.args.append((am.group(1), parse_type(am.group(2))))
             continue
         blk.ops.append(_parse_op(line, L))
 
@@ -327,6 +340,13 @@ _CMP_OPS = {"arith.cmpi", "arith.cmpf"}
 
 def _parse_simple(lhs, name, body, line) -> Op:
     attrs: Dict[str, object] = {}
+    if name in ("cf.cond_br", "cf.br"):
+        parts = _split_top(body)
+        operands = [x for x in parts if re.match(rf"^{_SSA}$", x)]
+        dests = [x for x in parts if x.startswith("^")]
+        if any("(" in d for d in dests) or len(dests) != (2 if name == "cf.cond_br" else 1):
+            raise UnsupportedTTIR(f"branch with block arguments: {line}")
+        return Op(name, [], operands, {"dests": dests}, [], line)
     if name in ("tt.return", "scf.yield", "tt.reduce.return", "tt.scan.return"):
         head, tys = _find_trailing_type(body)
         operands = [x.strip() for x in _split_top(head)] if head.strip() else []

@@ -145,7 +145,22 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         program_state_loops(A, P.size, px, py, pz, it, st);
         const int m = P.reg_mask[op.dst];
         unsigned *dst = bp_smem + P.reg_off[op.dst];
-        if ((m & 4) && (P.size[2] & 3) == 0) {
+        if (op.imm2 & 3u) {
+          // data-dependent access (flags in imm2: 1 = per-lane index in register b, 2 = per-lane mask
+          // in register c): one element per thread and step
+          const bool hi = op.imm2 & 1u, hm = op.imm2 & 2u;
+          const unsigned *ri = bp_smem + P.reg_off[hi ? op.b : 0], *rm = bp_smem + P.reg_off[hm ? op.c : 0];
+          const int mi = P.reg_mask[hi ? op.b : 0], mm = P.reg_mask[hm ? op.c : 0];
+          for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
+            int i0, i1, i2;
+            reg_coords(P.lg, m, e, i0, i1, i2);
+            const unsigned ix[1] = {hi ? ri[reg_index(P.lg, mi, i0, i1, i2)] : 0u};
+            const unsigned mk[1] = {hm ? rm[reg_index(P.lg, mm, i0, i1, i2)] : 1u};
+            unsigned v[1];
+            load_vec_indirect<1>(A, st, i0, i1, i2, hi, hm, ix, mk, v);
+            dst[e] = v[0];
+          }
+        } else if ((m & 4) && (P.size[2] & 3) == 0) {
           // 4-lane vectors along the innermost dim, four independent loads in flight per thread
           const int n4 = P.reg_n[op.dst] >> 2;
           for (int e0 = tid; e0 < n4; e0 += BP_THREADS * 4) {
@@ -182,7 +197,20 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         const int ms = P.reg_mask[op.b];
         const unsigned *src = bp_smem + P.reg_off[op.b];
         const int n = ((m & 1) ? P.size[0] : 1) * ((m & 2) ? P.size[1] : 1) * ((m & 4) ? P.size[2] : 1);
-        if ((m & 4) && ms == m && (P.size[2] & 3) == 0) {
+        if (op.imm2 & 3u) {
+          // data-dependent store: per-lane index in register c, per-lane mask in register dst
+          const bool hi = op.imm2 & 1u, hm = op.imm2 & 2u;
+          const unsigned *ri = bp_smem + P.reg_off[hi ? op.c : 0], *rm = bp_smem + P.reg_off[hm ? op.dst : 0];
+          const int mi = P.reg_mask[hi ? op.c : 0], mm = P.reg_mask[hm ? op.dst : 0];
+          for (int e = tid; e < n; e += BP_THREADS) {
+            int i0, i1, i2;
+            reg_coords(P.lg, m, e, i0, i1, i2);
+            const unsigned ix[1] = {hi ? ri[reg_index(P.lg, mi, i0, i1, i2)] : 0u};
+            const unsigned mk[1] = {hm ? rm[reg_index(P.lg, mm, i0, i1, i2)] : 1u};
+            const unsigned v[1] = {src[reg_index(P.lg, ms, i0, i1, i2)]};
+            store_vec_indirect<1>(A, st, i0, i1, i2, hi, hm, ix, mk, v);
+          }
+        } else if ((m & 4) && ms == m && (P.size[2] & 3) == 0) {
           for (int e4 = tid; e4 < (n >> 2); e4 += BP_THREADS) {
             int i0, i1, i2;
             reg_coords(P.lg, m, e4 * 4, i0, i1, i2);
@@ -368,8 +396,12 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
       P.ops[k] = o;
       continue;
     }
-    const int regs[4] = {o.opcode == TSB_OP_STORE ? 0 : o.dst, mem || o.opcode == TSB_OP_CONST ? 0 : o.a,
-                         o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_CONST ? 0 : o.b, o.c};
+    if (mem && (o.imm2 & ~3u)) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d has memory flags %u", k, o.imm2);
+    // operands of a load: index in b, mask in c; of a store: value in b, index in c, mask in dst (each only when flagged)
+    const bool ld = o.opcode == TSB_OP_LOAD, stn = o.opcode == TSB_OP_STORE;
+    const int regs[4] = {stn ? ((o.imm2 & 2u) ? o.dst : 0) : o.dst, mem || o.opcode == TSB_OP_CONST ? 0 : o.a,
+                         (ld ? ((o.imm2 & 1u) ? o.b : 0) : (o.opcode == TSB_OP_CONST ? 0 : o.b)),
+                         mem ? (((ld ? o.imm2 & 2u : o.imm2 & 1u)) ? o.c : 0) : o.c};
     for (int r = 0; r < 4; ++r)
       if (regs[r] < 0 || regs[r] >= n_regs) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d register %d out of range", k, regs[r]);
     P.ops[k] = o;

@@ -658,7 +658,7 @@ static bool build_flat(const EwParams &P, int vec, FlatParams &F) {
     f.shift = d.off0;
     f.limit = (d.masked & 4) ? d.bound[2] - d.mstart0[2] : 0x7fffffffffffffffll;
     f.dtype = d.dtype; f.esize = d.esize; f.has_other = d.has_other; f.kind = d.kind; f.other = d.other;
-    f.vec_ok = d.kind < 2 && ((uintptr_t)d.base % (4ull * d.esize)) == 0 && d.off0 % 4 == 0;
+    f.vec_ok = d.kind < 2 && d.esize <= 4 && ((uintptr_t)d.base % (4ull * d.esize)) == 0 && d.off0 % 4 == 0;
   }
   memcpy(F.ops, P.ops, sizeof(tsb_op) * P.n_ops);
   F.n_acc = P.n_acc;
@@ -687,7 +687,7 @@ static int vm_regs_used(const tsb_op *ops, int n_ops) {
 static bool is_copy(const tsb_access *acc, const tsb_op *ops, int n_ops) {
   return n_ops == 2 && ops[0].opcode == TSB_OP_LOAD && ops[1].opcode == TSB_OP_STORE &&
          (ops[1].b == TSB_REG_ACC || ops[1].b == ops[0].dst) && acc[ops[0].a].is_store == 0 &&
-         acc[ops[0].a].dtype == acc[ops[1].a].dtype;
+         acc[ops[0].a].dtype == acc[ops[1].a].dtype && acc[ops[0].a].dtype != TSB_I64;
 }
 
 // ew_copy2d_kernel applies when both sides are plain memory accesses of rank <= 2 with unit inner

@@ -88,13 +88,16 @@ __device__ __forceinline__ void reg_to_raw(int dt, unsigned (&x)[VEC]) {
     default: break;
   }
 }
+// 64-bit integers (index tensors) are held as their low 32 bits and stored sign-extended
 __device__ __forceinline__ unsigned ld_raw(const char *p, int esize) {
+  if (esize == 8) return (unsigned)*reinterpret_cast<const unsigned long long *>(p);
   if (esize == 4) return *reinterpret_cast<const unsigned *>(p);
   if (esize == 2) return *reinterpret_cast<const unsigned short *>(p);
   return *reinterpret_cast<const unsigned char *>(p);
 }
 __device__ __forceinline__ void st_raw(char *p, int esize, unsigned v) {
-  if (esize == 4) *reinterpret_cast<unsigned *>(p) = v;
+  if (esize == 8) *reinterpret_cast<long long *>(p) = (long long)(int)v;
+  else if (esize == 4) *reinterpret_cast<unsigned *>(p) = v;
   else if (esize == 2) *reinterpret_cast<unsigned short *>(p) = (unsigned short)v;
   else *reinterpret_cast<unsigned char *>(p) = (unsigned char)v;
 }
@@ -589,7 +592,7 @@ inline int convert_access(const tsb_access *acc, int a, int rank, const int size
   const tsb_access &s = acc[a];
   if (s.rank != rank) return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has rank %d, expected %d", a, s.rank, rank);
   const int es = dtype_size(s.dtype);
-  if (es == 0 || es == 8)
+  if (es == 0 || s.dtype == TSB_F64)
     return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: access %d has unsupported dtype %d", a, s.dtype);
   if (s.is_store < 0 || s.is_store > 3)
     return fail(TSB_ERR_INVALID, "tsb_elementwise: access %d has kind %d", a, s.is_store);
@@ -637,7 +640,7 @@ inline int convert_access(const tsb_access *acc, int a, int rank, const int size
   }
   // 4-lane vectors need: unit inner stride, vector-aligned base and offsets
   const long long vb = 4ll * es;
-  bool ok = vec == 4 && d.stride[2] == 1 && ((uintptr_t)d.base % vb) == 0 && d.off0 % 4 == 0;
+  bool ok = vec == 4 && es <= 4 && d.stride[2] == 1 && ((uintptr_t)d.base % vb) == 0 && d.off0 % 4 == 0;
   for (int k = 0; k < 3; ++k) ok = ok && (grid[k] <= 1 || d.off_pid[k] % 4 == 0);
   ok = ok && (size[1] <= 1 || d.stride[1] % 4 == 0) && (size[0] <= 1 || d.stride[0] % 4 == 0);
   ok = ok && !d.wrap_inner && !wrap_unaligned;
