@@ -50,6 +50,7 @@ def _is_float(dt):
 
 class HostMemory:
     """Replacement for the driver's device-memory provider: plain host arrays."""
+    host_pointers = True  # the stand-in executes on host memory: host tensors are what it wants
 
     def __init__(self):
         self._scratch = None

@@ -152,6 +152,10 @@ class LaunchArgs:
         dp = getattr(v, "data_ptr", None)
         if dp is None:
             raise TypeError("Pointer argument must be either uint64 or have data_ptr method")
+        # a host tensor handed to a GPU launch would fault the device: the launcher stages such
+        # tensors through device memory (HostStaging); one that reaches this point unstaged is refused
+        if getattr(v, "is_cuda", True) is False and not getattr(self._mem, "host_pointers", False):
+            raise ValueError("Pointer argument (at %d) cannot be accessed from the GPU: it is a host tensor" % k)
         p = dp()
         if not isinstance(p, int):
             raise TypeError("data_ptr method of Pointer object must return 64-bit int")
@@ -165,6 +169,45 @@ class LaunchArgs:
 
     def status_word(self, stream) -> int:
         return self._mem.status()
+
+
+class HostStaging:
+    """Host (CPU) torch tensors among a launch's pointer arguments, staged through device memory.
+
+    Programs written for the reference keep their tensors on the CPU.  For each such argument the
+    whole underlying storage is copied to a device buffer before the launch (so every offset and
+    stride the kernel was given stays valid), the kernel gets the device address of the tensor's
+    first element, and after the launch the storage is copied back.  The launch is synchronous for
+    these calls.  Tensors that share a storage share one device copy."""
+
+    def __init__(self):
+        self.copies = {}  # storage address -> (host bytes view, device bytes tensor)
+
+    def device_address(self, t):
+        import torch
+        st = t.untyped_storage()
+        key = st.data_ptr()
+        if key not in self.copies:
+            host = torch.empty(0, dtype=torch.uint8).set_(st)
+            self.copies[key] = (host, host.to("cuda"))
+        return self.copies[key][1].data_ptr() + (t.data_ptr() - key)
+
+    def finish(self):
+        import torch
+        if self.copies:
+            torch.cuda.synchronize()
+            for host, dev in self.copies.values():
+                host.copy_(dev)
+
+
+class _Staged:
+    """A pointer argument replaced by its staged device address."""
+
+    def __init__(self, address):
+        self._a = address
+
+    def data_ptr(self):
+        return self._a
 
 
 class B200Launcher(object):
@@ -186,11 +229,17 @@ class B200Launcher(object):
         if launch_enter_hook is not None:
             launch_enter_hook(launch_metadata)
         values = []
+        staging = None
+        host_ok = getattr(B200Launcher.memory, "host_pointers", False)
         for idx in self.order:
             ty = self.signature[idx]
             if ty == "constexpr":
                 continue
-            values.append((ty, args[idx]))
+            v = args[idx]
+            if ty[0] == '*' and not host_ok and getattr(v, "is_cuda", True) is False and hasattr(v, "untyped_storage"):
+                staging = staging or HostStaging()
+                v = _Staged(staging.device_address(v))
+            values.append((ty, v))
         grid = (int(gridX), int(gridY), int(gridZ))
         total = grid[0] * grid[1] * grid[2]
         if total > 0:
@@ -198,6 +247,8 @@ class B200Launcher(object):
             lo, hi = (0, total) if drv is None else drv.range_for(total)
             if hi > lo:
                 plan.launch(LaunchArgs(B200Launcher.memory, values), grid, lo, hi, stream or 0)
+        if staging is not None:
+            staging.finish()
         if launch_exit_hook is not None:
             launch_exit_hook(launch_metadata)
 
