@@ -116,6 +116,33 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def bind_to_gpu_numa_node(gpu_index: int):
+    """Restrict this process to the CPUs of the NUMA node the GPU hangs off, so that pinned host
+    buffers allocated afterwards are local to it.  Best effort: returns what was done."""
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(gpu_index).pci_bus_id
+        dom = getattr(torch.cuda.get_device_properties(gpu_index), "pci_domain_id", 0)
+        dev = torch.cuda.get_device_properties(gpu_index).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        with open(path) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"node": None, "note": "the platform reports no NUMA node for the GPU"}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return {"node": node, "note": "none of the node's CPUs is available to this process"}
+        os.sched_setaffinity(0, allowed)
+        return {"node": node, "cpus": len(allowed)}
+    except Exception as e:  # noqa: BLE001 - placement is an optimisation, never a failure
+        return {"node": None, "note": f"{type(e).__name__}: {e}"[:120]}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -158,6 +185,56 @@ def cpu_softmax_rate(seconds_target=10.0, threads=None):
             break
     gbs = rows * SOFTMAX_COLS * 8 * passes / dt / 1e9
     return gbs, threads, (rows, passes), dt
+
+
+def cpu_baselines(seconds_each=1.5):
+    """The oracle (CPU restatement of the reference's lowered loops) on bounded samples of the other
+    workloads, at one thread (the reference launcher runs the grid serially on one thread,
+    backend/driver.py:116-133) and at all host threads.  Rates are in the workload's own unit."""
+    import numpy as np
+    import oracle
+    oracle.build()
+    nthr = oracle.max_threads()
+    rng = np.random.default_rng(7)
+    out = {}
+
+    def rate(fn, work, unit):
+        res = {}
+        for label, t in (("one_thread", 1), ("all_threads", nthr)):
+            fn(t)  # warm-up
+            n, t0 = 0, time.perf_counter()
+            while True:
+                fn(t)
+                n += 1
+                dt = time.perf_counter() - t0
+                if dt >= seconds_each or n >= 50:
+                    break
+            res[label] = {"value": work * n / dt / unit[1], "cores": t, "passes": n, "seconds": round(dt, 2)}
+        res["unit"], res["kind"] = unit[0], "port"
+        return res
+
+    n = 1 << 22
+    x, y = rng.random(n, dtype=np.float32), rng.random(n, dtype=np.float32)
+    o = np.empty(n, dtype=np.float32)
+    out["vec_add"] = rate(lambda t: oracle.vec_add(x, y, n, 1024, threads=t, out=o), 12 * n, ("GB/s", 1e9))
+    out["vec_add"]["sample"] = f"{n} of {ADD_N} elements per pass"
+    rows = 64
+    xh = rng.standard_normal((rows, LN_N), dtype=np.float32).astype(np.float16)
+    w = (rng.random(LN_N, dtype=np.float32) + 0.5).astype(np.float16)
+    b = (0.1 * rng.standard_normal(LN_N, dtype=np.float32)).astype(np.float16)
+    out["layernorm"] = rate(lambda t: oracle.layernorm_fwd(xh, w, b, 1e-5, 1024, threads=t), 4 * rows * LN_N, ("GB/s", 1e9))
+    out["layernorm"]["sample"] = f"{rows} of {LN_M} rows x {LN_N} columns per pass"
+    M, NT, NV = 1024, 1536, 1500
+    flat = rng.standard_normal(M * NT, dtype=np.float32)
+    out["strided_reduce"] = rate(lambda t: oracle.reduce_rows(flat, M, NV, 1, M, 64, 64, threads=t), 4 * M * NV, ("GB/s", 1e9))
+    out["strided_reduce"]["sample"] = f"{M} x {NV} of {RED_M} x {RED_NV} (strides [1, {M}]) per pass"
+    mm, mk = 1024, 128
+    bits = lambda a: (a.view(np.uint32) >> 16).astype(np.uint16)  # bf16 by truncation: timing only
+    A = bits(rng.random((mm, mk), dtype=np.float32) * 2 - 1)
+    B = bits(rng.random((mk, mm), dtype=np.float32) * 2 - 1)
+    out["matmul"] = rate(lambda t: oracle.matmul(A, B, oracle.BF16, 128, 256, 64, 8, threads=t), 2.0 * mm * mm * mk, ("TFLOP/s", 1e12))
+    out["matmul"]["sample"] = f"{mm} x {mm} x {mk} of {MM}^3 per pass ({(mm // 128) * (mm // 256)} programs)"
+    return out
 
 
 def run_reference(args):
@@ -294,7 +371,9 @@ def main():
     achieved = alg_bytes / (per_launch_ms * 1e-3) / 1e9
     ok = torch.allclose(y.sum(dim=1), torch.ones(rows, device="cuda"), rtol=1e-4)
 
-    # end to end: pinned host buffers, H2D + launch + D2H inside the timed region
+    # end to end: pinned host buffers, H2D + launch + D2H inside the timed region.  The rank's host
+    # threads (and so the pages it pins) are first bound to the CPUs of the GPU's own NUMA node.
+    numa = bind_to_gpu_numa_node(local_rank)
     hx = torch.randn(rows, cols).pin_memory()
     hy = torch.empty(rows, cols).pin_memory()
 
@@ -302,7 +381,7 @@ def main():
     # chunks of rows; chunk c is launched as the program range of its rows as soon as its
     # host->device copy has landed, and is copied back while later chunks are still in flight,
     # so the two copy directions and the kernel overlap (three streams, events between them).
-    n_chunks = 8 if rows % 8 == 0 and rows >= 64 else 1
+    n_chunks = 32 if rows % 32 == 0 and rows >= 1024 else (8 if rows % 8 == 0 and rows >= 64 else 1)
     crow = rows // n_chunks
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(n_chunks)]
@@ -352,6 +431,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": rows * cols * 4 * world,
                 "d2h_bytes_per_step": rows * cols * 4 * world, "steps": e2e_steps,
                 "pipeline": f"{n_chunks} row chunks per step: H2D, kernel and D2H on three streams",
+                "host_numa": numa,
                 "result_check": e2e_ok},
         "gpu_launches": args.steps,
         "clocks": clocks,
@@ -360,21 +440,26 @@ def main():
     torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ secondary workloads
-    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy"}
-    # kernels of the widened rows (general engines rather than dedicated kernels); not part of "all"
-    extra = {"gelu_bias", "rmsnorm", "wrap_rows"}
-    chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names | extra}
+    # the five configured workloads, the block copy, and three kernels that run on the general engines
+    # (elementwise VM, block programs, device-side loops) rather than on dedicated kernels
+    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy", "gelu_bias", "rmsnorm", "wrap_rows"}
+    chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names}
     if chosen:
         wl = {}
         steps2, warm2 = (3, 3) if args.small else (10, 3)
 
         def record(name, fn, alg, unit_scale, bound, unit, nbuf=1, launches=1, graph=True):
             """fn runs the workload once per rotating buffer set (nbuf passes of `alg` work)."""
+            smp = ClockSampler(local_rank)
+            smp.start()
+            time.sleep(0.25)
             try:
                 tot, per = timed(fn, steps2, warm2, launches_per_call=nbuf, graph=graph and not args.eager)
             except Exception as e:  # an unsupported family is reported, never hidden
+                smp.stop()
                 wl[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
                 return
+            clk = smp.stop()
             rate = alg / (per * 1e-3) / unit_scale
             peak = peaks["hbm"] if bound == "hbm" else peaks["tensor"]
             wl[name] = {"value": alg * world * steps2 * nbuf / (tot * 1e-3) / unit_scale, "unit": unit,
@@ -382,7 +467,19 @@ def main():
                                                          "frac": rate / peak, "unit": unit,
                                                          "traffic": NCU_TRAFFIC_BYTES.get(name),
                                                          "peak_source": f"of {peaks['src']}"},
-                        "gpu_launches": steps2 * launches * nbuf, "rotating_buffers": nbuf}
+                        "gpu_launches": steps2 * launches * nbuf, "rotating_buffers": nbuf, "clocks": clk}
+
+        def host_us_per_launch(fn, n=200):
+            """Host time to enqueue one launch through the plugin (plan evaluation, ctypes call, kernel
+            launch): wall time of a burst of eager launches that is not synchronised until its end."""
+            fn()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(n):
+                fn()
+            dt = time.perf_counter() - t0
+            torch.cuda.synchronize()
+            return dt / n * 1e6
 
         def wl_vec_add():
             # masked vector add, 2^30 fp32 per GPU
@@ -401,6 +498,7 @@ def main():
             if "value" in wl["vec_add"]:
                 wl["vec_add"]["n"] = n
                 wl["vec_add"]["result_check"] = bool(torch.equal(c[:1 << 20], a[:1 << 20] + b[:1 << 20]))
+                wl["vec_add"]["host_us_per_launch"] = host_us_per_launch(add_step, 20)
 
         def wl_layernorm():
             # LayerNorm forward 4096 x 8192 fp16 per GPU; rotating buffer sets (134 MB each is about the L2 size)
@@ -423,27 +521,59 @@ def main():
             record("layernorm", ln_step, 4 * m * LN_N + 4 * LN_N + 8 * m, 1e9, "hbm", "GB/s", nbuf=nb)
             if "value" in wl["layernorm"]:
                 wl["layernorm"]["rows"] = m
+                ref = torch.nn.functional.layer_norm(xs[0][:256].float(), (LN_N,), w.float(), bb.float(), 1e-5)
+                err = (ys[0][:256].float() - ref).abs().max().item()
+                mu = xs[nb - 1].float().mean(dim=1)  # mean / rstd hold the last buffer set's rows
+                merr = (mean[lo_ln:lo_ln + m] - mu).abs().max().item()
+                wl["layernorm"]["result_check"] = {"max_abs_err_y": err, "max_abs_err_mean": merr,
+                                                   "ok": bool(err <= 2e-2 and merr <= 1e-5)}
+
+                def one_launch():
+                    with drv.partition(rank, world):
+                        K.layernorm_fwd_kernel[(m * world,)](DP(xs[0].data_ptr() - lo_ln * LN_N * 2, torch.float16),
+                                                            DP(ys[0].data_ptr() - lo_ln * LN_N * 2, torch.float16),
+                                                            w, bb, mean, rstd, LN_N, LN_N, 1e-5, BLOCK_SIZE=1024)
+                wl["layernorm"]["host_us_per_launch"] = host_us_per_launch(one_launch)
 
         def wl_strided_reduce():
             # strided masked reduction 8192 x 12288 (strides [1, 8192]) masked to 12000 columns + scalar total
             nb = 2 if args.small else 4
             fl = [torch.randn(RED_M * RED_N, device="cuda") for _ in range(nb)]
-            rs = torch.empty(RED_M, device="cuda")
-            tot = torch.zeros(1, device="cuda")
+            rs = [torch.empty(RED_M, device="cuda") for _ in range(nb)]
+            tots = torch.zeros(nb, device="cuda")  # one scalar total per pass
 
             def red_step():
-                # every GPU reduces its own 8192-row matrix (weak scaling); the scalar is combined across GPUs
+                # every GPU reduces its own 8192-row matrix (weak scaling); the per-pass scalars are combined
+                # across GPUs with ONE all-reduce per step, after the last pass, so no pass waits on NCCL
                 for i in range(nb):
-                    K.row_sum_kernel[(RED_M // 64,)](fl[i], rs, RED_M, RED_NV, 1, RED_M, BLOCK_M=64, BLOCK_N=64)
-                    K.total_kernel[(1,)](rs, tot, RED_M, BLOCK=1024)
-                    if world > 1:
-                        dist.all_reduce(tot)
+                    K.row_sum_kernel[(RED_M // 64,)](fl[i], rs[i], RED_M, RED_NV, 1, RED_M, BLOCK_M=64, BLOCK_N=64)
+                    K.total_kernel[(1,)](rs[i], tots[i:i + 1], RED_M, BLOCK=1024)
+                if world > 1:
+                    dist.all_reduce(tots)
             record("strided_reduce", red_step, 4 * RED_M * RED_NV + 4 * RED_M + 4, 1e9, "hbm", "GB/s", nbuf=nb,
-                   launches=3)
+                   launches=2)
             if "unavailable" in wl["strided_reduce"] and world > 1:
                 # the all-reduce could not be captured into a graph here: time eager launches instead
                 record("strided_reduce", red_step, 4 * RED_M * RED_NV + 4 * RED_M + 4, 1e9, "hbm", "GB/s", nbuf=nb,
-                       launches=3, graph=False)
+                       launches=2, graph=False)
+            if "value" in wl["strided_reduce"]:
+                # row sums against an fp64 sum, to 1e-5 of sum|x| (sums of N(0,1) data cancel); the scalar total
+                # against the same sums combined over all GPUs
+                v = fl[0].view(RED_N, RED_M)[:RED_NV]
+                exact, scale = v.double().sum(dim=0), v.abs().double().sum(dim=0)
+                rows_ok = bool(torch.all((rs[0].double() - exact).abs() <= 1e-5 * scale))
+                red_step()
+                torch.cuda.synchronize()
+                want = torch.stack([fl[i].view(RED_N, RED_M)[:RED_NV].double().sum() for i in range(nb)])
+                mag = torch.stack([fl[i].view(RED_N, RED_M)[:RED_NV].abs().double().sum() for i in range(nb)])
+                if world > 1:
+                    dist.all_reduce(want)
+                    dist.all_reduce(mag)
+                tot_ok = bool(torch.all((tots.double() - want).abs() <= 1e-5 * mag))
+                wl["strided_reduce"]["result_check"] = {"row_sums": rows_ok, "scalar_total_all_gpus": tot_ok,
+                                                        "ok": rows_ok and tot_ok}
+                wl["strided_reduce"]["launches_per_pass"] = "2: the row-sum kernel and the single-program total kernel " \
+                                                            "(two Triton kernels; the reference has no atomics)"
 
         def wl_matmul():
             # bf16 matmul 8192^3, blocks 128/256/64, fp32 accumulation
@@ -472,10 +602,32 @@ def main():
                 burst = 2.0 * MM * MM * MM / (best * 1e-3) / 1e12
                 wl["matmul"]["burst"] = {"best_ms": best, "value": burst, "unit": "TFLOP/s",
                                          "frac_of_burst_peak": burst / peaks["tensor"]}
+                # seconds of back-to-back launches, the way the sustained peak itself was measured
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for _ in range(20):
+                        mm_step()
+                g.replay()
+                torch.cuda.synchronize()
+                smp = ClockSampler(local_rank)
+                smp.start()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps, t0 = 0, time.perf_counter()
+                e0.record()
+                while time.perf_counter() - t0 < 2.5:
+                    for _ in range(8):
+                        g.replay()
+                    reps += 8
+                    torch.cuda.synchronize()
+                e1.record()
+                torch.cuda.synchronize()
+                sus = 2.0 * MM * MM * MM * 20 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+                wl["matmul"]["sustained"] = {"seconds": e0.elapsed_time(e1) * 1e-3, "launches": 20 * reps, "value": sus,
+                                             "unit": "TFLOP/s", "frac_of_sustained_peak": sus / peaks["tensor_sustained"],
+                                             "clocks": smp.stop()}
                 ref = (A[:256].float() @ B.float())
                 err = (C[:256].float() - ref).abs().max().item() / ref.abs().max().item()
                 wl["matmul"]["result_check_rel_err"] = err
-                wl["matmul"]["roofline"]["frac_of_sustained"] = wl["matmul"]["roofline"]["achieved"] / peaks["tensor_sustained"]
 
         def wl_gelu_bias():
             # register-VM elementwise body (25 ops, fp16 I/O, broadcast bias), 16,384 x 8,192
@@ -507,7 +659,10 @@ def main():
 
             def step():
                 K.wrap_rows_kernel[(1,)](A, Cc, M, N, 1, N, 1, START=4090, BM=64, BN=64, STEPS=N // 64)
-            record("wrap_rows", step, 8 * 64 * N, 1e9, "hbm", "GB/s", launches=N // 64)
+            record("wrap_rows", step, 8 * 64 * N, 1e9, "hbm", "GB/s")  # one launch: the column loop runs on the device
+            if "value" in wl["wrap_rows"]:
+                wl["wrap_rows"]["result_check"] = bool(torch.equal(Cc, torch.cat([A[4090:], A[:58]])))
+                wl["wrap_rows"]["note"] = "a single program (one CTA) walks 256 column steps: bound by one SM, not by HBM"
 
         def wl_block_copy():
             # masked strided 2-D block copy, fp32 16,000 x 16,000 (ragged against 64 x 128 tiles), row-major to row-major
@@ -531,11 +686,153 @@ def main():
                 torch.cuda.empty_cache()
         line["workloads"] = wl
 
+    # ------------------------------------------------------------------ strong scaling: shards of ONE grid
+    if world > 1 and chosen:
+        from triton_shared_b200 import partition_range
+        strong = {}
+        steps3, warm3 = 10, 3
+
+        def nbuf_for(shard_bytes):
+            # enough rotating buffer sets that consecutive passes cannot be served from the 126 MB L2
+            return int(max(2, min(32, -(-400_000_000 // max(shard_bytes, 1)))))
+
+        def srecord(name, fn, alg_total, unit_scale, bound, unit, nbuf, check=None):
+            try:
+                tot, per = timed(fn, steps3, warm3, launches_per_call=nbuf)
+            except Exception as e:
+                strong[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+                return
+            peak = peaks["hbm"] if bound == "hbm" else peaks["tensor"]
+            per_gpu = alg_total / world / (per * 1e-3) / unit_scale
+            strong[name] = {"value": alg_total * steps3 * nbuf / (tot * 1e-3) / unit_scale, "unit": unit,
+                            "ms_per_pass": per, "per_gpu_frac_of_peak": per_gpu / peak, "rotating_buffers": nbuf,
+                            "problem": "fixed total size, contiguous program ranges per GPU, num_programs = full grid"}
+            if check is not None:
+                strong[name]["result_check"] = check()
+
+        def s_vec_add():
+            n = ADD_N
+            progs = n // 1024
+            lo_p, hi_p = partition_range(progs, rank, world)
+            ne = (hi_p - lo_p) * 1024
+            nb = nbuf_for(ne * 12)
+            bufs = [(torch.rand(ne, device="cuda"), torch.rand(ne, device="cuda"), torch.empty(ne, device="cuda")) for _ in range(nb)]
+            off = lo_p * 1024 * 4
+
+            def step():
+                for a, b, c in bufs:
+                    with drv.partition(rank, world):
+                        K.add_kernel[(progs,)](DP(a.data_ptr() - off, torch.float32), DP(b.data_ptr() - off, torch.float32),
+                                               DP(c.data_ptr() - off, torch.float32), n, BLOCK_SIZE=1024)
+            srecord("vec_add", step, n * 12, 1e9, "hbm", "GB/s", nb,
+                    lambda: bool(torch.equal(bufs[0][2], bufs[0][0] + bufs[0][1])))
+
+        def s_softmax():
+            R, C = SOFTMAX_ROWS, SOFTMAX_COLS
+            lo_r, hi_r = partition_range(R, rank, world)
+            nr = hi_r - lo_r
+            nb = nbuf_for(nr * C * 8)
+            bufs = [(torch.randn(nr, C, device="cuda"), torch.empty(nr, C, device="cuda")) for _ in range(nb)]
+            off = lo_r * C * 4
+
+            def step():
+                for xi, yi in bufs:
+                    with drv.partition(rank, world):
+                        K.softmax_kernel[(R,)](DP(yi.data_ptr() - off, torch.float32), DP(xi.data_ptr() - off, torch.float32),
+                                               C, C, C, BLOCK_SIZE=4096)
+            srecord("softmax", step, R * C * 8, 1e9, "hbm", "GB/s", nb,
+                    lambda: bool(torch.allclose(bufs[0][1].sum(dim=1), torch.ones(nr, device="cuda"), rtol=1e-4)))
+
+        def s_layernorm():
+            lo_r, hi_r = partition_range(LN_M, rank, world)
+            nr = hi_r - lo_r
+            nb = nbuf_for(nr * LN_N * 4)
+            bufs = [(torch.randn(nr, LN_N, device="cuda").half(), torch.empty(nr, LN_N, device="cuda", dtype=torch.float16))
+                    for _ in range(nb)]
+            w = (torch.rand(LN_N, device="cuda") + 0.5).half()
+            bb = (0.1 * torch.randn(LN_N, device="cuda")).half()
+            mean, rstd = torch.empty(LN_M, device="cuda"), torch.empty(LN_M, device="cuda")
+            off = lo_r * LN_N * 2
+
+            def step():
+                for xi, yi in bufs:
+                    with drv.partition(rank, world):
+                        K.layernorm_fwd_kernel[(LN_M,)](DP(xi.data_ptr() - off, torch.float16), DP(yi.data_ptr() - off, torch.float16),
+                                                        w, bb, mean, rstd, LN_N, LN_N, 1e-5, BLOCK_SIZE=1024)
+
+            def check():
+                ref = torch.nn.functional.layer_norm(bufs[0][0].float(), (LN_N,), w.float(), bb.float(), 1e-5)
+                return bool((bufs[0][1].float() - ref).abs().max().item() <= 2e-2)
+            srecord("layernorm", step, 4 * LN_M * LN_N + 4 * LN_N + 8 * LN_M, 1e9, "hbm", "GB/s", nb, check)
+
+        def s_reduce():
+            progs = RED_M // 64
+            lo_p, hi_p = partition_range(progs, rank, world)
+            lo_r, nr = lo_p * 64, (hi_p - lo_p) * 64
+            nb = nbuf_for(nr * RED_N * 4)
+            # this rank's rows of the [1, M]-strided matrix, stored compactly: element (i, j) at (i - lo_r) + j * nr
+            fl = [torch.randn(RED_N * nr, device="cuda") for _ in range(nb)]
+            rs = torch.empty(nr, device="cuda")
+            tots = torch.zeros(nb, device="cuda")
+
+            def step():
+                for i in range(nb):
+                    with drv.partition(rank, world):
+                        K.row_sum_kernel[(progs,)](DP(fl[i].data_ptr() - lo_r * 4, torch.float32), DP(rs.data_ptr() - lo_r * 4, torch.float32),
+                                                   RED_M, RED_NV, 1, nr, BLOCK_M=64, BLOCK_N=64)
+                    K.total_kernel[(1,)](rs, tots[i:i + 1], nr, BLOCK=1024)
+                dist.all_reduce(tots)  # the global scalar of every pass, one NCCL all-reduce per step
+
+            def check():
+                step()
+                torch.cuda.synchronize()
+                want = torch.stack([f.view(RED_N, nr)[:RED_NV].double().sum() for f in fl])
+                mag = torch.stack([f.view(RED_N, nr)[:RED_NV].abs().double().sum() for f in fl])
+                dist.all_reduce(want)
+                dist.all_reduce(mag)
+                return bool(torch.all((tots.double() - want).abs() <= 1e-5 * mag))
+            srecord("strided_reduce", step, 4 * RED_M * RED_NV + 4 * RED_M + 4, 1e9, "hbm", "GB/s", nb, check)
+
+        def s_matmul():
+            progs = (MM // 128) * (MM // 256)
+            lo_p, hi_p = partition_range(progs, rank, world)
+            per_group = 8 * (MM // 256)  # programs of one group of GROUP_M = 8 tile rows
+            if lo_p % per_group or hi_p % per_group:
+                strong["matmul"] = {"unavailable": "program ranges do not fall on tile-row groups at this GPU count"}
+                return
+            r0, r1 = lo_p // per_group * 8 * 128, hi_p // per_group * 8 * 128  # this rank's band of A / C rows
+            A = (2 * torch.rand(r1 - r0, MM, device="cuda") - 1).bfloat16()
+            B = (2 * torch.rand(MM, MM, device="cuda") - 1).bfloat16()  # replicated
+            C = torch.empty(r1 - r0, MM, device="cuda", dtype=torch.bfloat16)
+
+            def step():
+                with drv.partition(rank, world):
+                    K.matmul_kernel[(progs,)](DP(A.data_ptr() - r0 * MM * 2, torch.bfloat16), B, DP(C.data_ptr() - r0 * MM * 2, torch.bfloat16),
+                                              MM, MM, MM, MM, 1, MM, 1, MM, 1, BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
+
+            def check():
+                ref = A[:256].float() @ B.float()
+                return bool(((C[:256].float() - ref).abs().max() / ref.abs().max()).item() <= 1e-2)
+            srecord("matmul", step, 2.0 * MM ** 3, 1e12, "tensor", "TFLOP/s", 1, check)
+
+        for nm, fn in (("vec_add", s_vec_add), ("softmax", s_softmax), ("layernorm", s_layernorm),
+                       ("strided_reduce", s_reduce), ("matmul", s_matmul)):
+            if nm == "softmax" or nm in chosen:
+                fn()
+                torch.cuda.empty_cache()
+        line["strong_scaling"] = strong
+
     # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1)
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
         gbs, threads, (srows, passes), dt = cpu_softmax_rate()
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                                 "sample": f"{srows} of {SOFTMAX_ROWS} rows x {SOFTMAX_COLS} cols, {passes} passes, {dt:.1f} s"}
+        g1, _, (r1_, p1_), d1_ = cpu_softmax_rate(seconds_target=3.0, threads=1)
+        line["cpu_baseline"]["one_thread"] = {"value": g1, "cores": 1, "sample": f"{r1_} rows, {p1_} passes, {d1_:.1f} s",
+                                              "note": "the reference launcher runs the grid serially on one thread"}
+        for name, cb in cpu_baselines().items():
+            if name in line.get("workloads", {}):
+                line["workloads"][name]["cpu_baseline"] = cb
     if world > 1:
         dist.destroy_process_group()
     sys.stdout.flush()
