@@ -375,6 +375,46 @@ int tsb_gemm_paired(const void *a, const void *b, void *c, int32_t dtype, int64_
                     int32_t block_k, const int32_t *pairs, int64_t n_pairs, int32_t *status,
                     void *stream);
 
+/* ------------------------------------------------------------------------- */
+/* launch plans                                                              */
+
+/*
+ * A launch plan is the JSON text that this package's Triton backend emits as a kernel's "binary"
+ * (stage `plan`; it is also what TRITON_SHARED_DUMP_PATH/plan.json holds): a kernel family and its
+ * parameters as polynomials over the kernel's integer arguments, program ids and grid sizes.
+ * tsb_plan_create parses it once; tsb_launch evaluates it for one call and launches programs
+ * [pid_lo, pid_hi) of grid[3] on `stream`.  Replaces what the reference's generated launcher does
+ * after unmarshalling its arguments (backend/driver.py:102-246): the serial loop over the compiled
+ * kernel.  Arguments are indexed by position in the kernel's signature without its constexpr
+ * parameters: ptr_args[i] is the device address of pointer argument i (ignored elsewhere),
+ * scalar_args[i] the value of scalar argument i (kind TSB_SCALAR_NONE for pointers).
+ *
+ * The library allocates no device memory: a launch that needs device scratch (partial sums of a
+ * reduction, the pid -> tile table of a matmul) takes it from `scratch`, at least
+ * tsb_launch_scratch_bytes(...) bytes for the same plan, grid, range and scalars (0 = none needed);
+ * launches that share scratch must be ordered on one stream.  `status` is the int32[4] word of
+ * tsb_gemm (may be NULL).  A plan handle may be used from several threads.
+ * tsb_plan_create returns NULL on error; the other calls return 0 or a negative tsb_error.
+ */
+typedef struct tsb_plan tsb_plan;
+enum tsb_scalar_kind { TSB_SCALAR_NONE = 0, TSB_SCALAR_INT = 1, TSB_SCALAR_FLOAT = 2 };
+typedef struct tsb_scalar {
+  int32_t kind; /* enum tsb_scalar_kind */
+  int32_t pad_;
+  int64_t i;    /* value of an integer argument (i1 ... i64, u8 ... u64) */
+  double f;     /* value of a floating-point argument (fp32, fp64) */
+} tsb_scalar;
+
+tsb_plan *tsb_plan_create(const char *json, int64_t length /* < 0: NUL-terminated */);
+void tsb_plan_destroy(tsb_plan *plan);
+const char *tsb_plan_family(const tsb_plan *plan);
+const char *tsb_plan_kernel_name(const tsb_plan *plan);
+int64_t tsb_launch_scratch_bytes(const tsb_plan *plan, const int32_t grid[3], int64_t pid_lo, int64_t pid_hi,
+                                 const tsb_scalar *scalar_args, int n_args);
+int tsb_launch(const tsb_plan *plan, const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, void *stream,
+               void *const *ptr_args, const tsb_scalar *scalar_args, int n_args, void *scratch,
+               int64_t scratch_bytes, int32_t *status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -459,6 +459,37 @@ def test_launch_hooks_are_called():
     assert torch.equal(out, x + 1)
 
 
+def test_c_plan_evaluator_parses_every_family():
+    """tsb_plan_create reads the plan text of each kernel family (no GPU needed: nothing is launched)."""
+    import json
+    import kernels as K
+    from triton_shared_b200 import runtime as rt
+    L = rt.lib()
+    cases = [
+        (K.add_kernel, {"x_ptr": "*fp32", "y_ptr": "*fp32", "out_ptr": "*fp32", "n_elements": "i32", "BLOCK_SIZE": "constexpr"},
+         {"BLOCK_SIZE": 1024}),
+        (K.softmax_kernel, {"out_ptr": "*fp32", "in_ptr": "*fp32", "in_row_stride": "i32", "out_row_stride": "i32",
+                            "n_cols": "i32", "BLOCK_SIZE": "constexpr"}, {"BLOCK_SIZE": 1024}),
+        (K.layernorm_fwd_kernel, {"X": "*fp16", "Y": "*fp16", "W": "*fp16", "B": "*fp16", "Mean": "*fp32", "Rstd": "*fp32",
+                                  "stride": "i32", "N": "i32", "eps": "fp32", "BLOCK_SIZE": "constexpr"}, {"BLOCK_SIZE": 1024}),
+        (K.row_sum_kernel, {"x_ptr": "*fp32", "out_ptr": "*fp32", "M": "i32", "N": "i32", "stride_m": "i32", "stride_n": "i32",
+                            "BLOCK_M": "constexpr", "BLOCK_N": "constexpr"}, {"BLOCK_M": 64, "BLOCK_N": 64}),
+        (K.total_kernel, {"x_ptr": "*fp32", "out_ptr": "*fp32", "n": "i32", "BLOCK": "constexpr"}, {"BLOCK": 1024}),
+        (K.rmsnorm_kernel, {"x_ptr": "*fp16", "w_ptr": "*fp16", "y_ptr": "*fp16", "stride": "i32", "n_cols": "i32", "eps": "fp32",
+                            "BLOCK": "constexpr"}, {"BLOCK": 1024}),
+    ]
+    seen = set()
+    for fn, sig, ce in cases:
+        text = triton.compile(ASTSource(fn, sig, ce), target=TARGET).asm["plan"]
+        h = L.tsb_plan_create(text, len(text))
+        assert h, L.tsb_last_error()
+        assert L.tsb_plan_family(h).decode() == json.loads(text)["family"]
+        seen.add(L.tsb_plan_family(h).decode())
+        L.tsb_plan_destroy(h)
+    assert seen == {"elementwise", "softmax", "layernorm", "reduce_rows", "reduce_all", "block_program"}
+    assert not L.tsb_plan_create(b"[1, 2", -1) and b"JSON" in L.tsb_last_error()
+
+
 # ------------------------------------------------------------------ the reference's own example tests
 def _reference_cases():
     import reference_examples as R

@@ -133,6 +133,7 @@ class LaunchArgs:
     def __init__(self, memory, values):
         self.scalars, self.floats, self._ptrs = {}, {}, {}
         self._mem = memory
+        self.n_args = len(values)
         for k, (ty, v) in enumerate(values):
             if ty[0] == '*':
                 self._ptrs[k] = v
@@ -160,6 +161,9 @@ class LaunchArgs:
         if not isinstance(p, int):
             raise TypeError("data_ptr method of Pointer object must return 64-bit int")
         return p
+
+    def pointer_positions(self):
+        return self._ptrs.keys()
 
     def scratch(self, nbytes: int, stream) -> int:
         return self._mem.scratch(nbytes, int(stream or 0))
@@ -246,7 +250,9 @@ class B200Launcher(object):
             drv = B200Driver.current
             lo, hi = (0, total) if drv is None else drv.range_for(total)
             if hi > lo:
-                plan.launch(LaunchArgs(B200Launcher.memory, values), grid, lo, hi, stream or 0)
+                largs = LaunchArgs(B200Launcher.memory, values)
+                if not plan.launch_native(largs, grid, lo, hi, stream or 0):
+                    plan.launch(largs, grid, lo, hi, stream or 0)
         if staging is not None:
             staging.finish()
         if launch_exit_hook is not None:

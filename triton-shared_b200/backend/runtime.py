@@ -93,6 +93,11 @@ class Op(ctypes.Structure):
     ]
 
 
+class Scalar(ctypes.Structure):
+    """struct tsb_scalar"""
+    _fields_ = [("kind", ctypes.c_int32), ("pad_", ctypes.c_int32), ("i", ctypes.c_int64), ("f", ctypes.c_double)]
+
+
 class TsbError(RuntimeError):
     pass
 
@@ -102,7 +107,8 @@ _lib = None
 # every symbol include/tsb200.h declares
 SYMBOLS = ["tsb_last_error", "tsb_version", "tsb_sm_count", "tsb_elementwise", "tsb_block_program", "tsb_block_copy",
            "tsb_softmax_rows", "tsb_layernorm_fwd", "tsb_reduce_rows_scratch_bytes", "tsb_reduce_rows",
-           "tsb_reduce_rows_static", "tsb_reduce_all", "tsb_gemm", "tsb_gemm_paired"]
+           "tsb_reduce_rows_static", "tsb_reduce_all", "tsb_gemm", "tsb_gemm_paired", "tsb_plan_create",
+           "tsb_plan_destroy", "tsb_plan_family", "tsb_plan_kernel_name", "tsb_launch_scratch_bytes", "tsb_launch"]
 
 
 def lib():
@@ -143,6 +149,19 @@ def lib():
     L.tsb_gemm.argtypes = [vp, vp, vp, i32] + [i64] * 9 + [i32, i32, i32, vp, i64, i64, i64, vp, vp]
     L.tsb_gemm_paired.restype = ctypes.c_int
     L.tsb_gemm_paired.argtypes = [vp, vp, vp, i32] + [i64] * 9 + [i32, i32, i32, vp, i64, vp, vp]
+    L.tsb_plan_create.restype = vp
+    L.tsb_plan_create.argtypes = [ctypes.c_char_p, i64]
+    L.tsb_plan_destroy.restype = None
+    L.tsb_plan_destroy.argtypes = [vp]
+    L.tsb_plan_family.restype = ctypes.c_char_p
+    L.tsb_plan_family.argtypes = [vp]
+    L.tsb_plan_kernel_name.restype = ctypes.c_char_p
+    L.tsb_plan_kernel_name.argtypes = [vp]
+    L.tsb_launch_scratch_bytes.restype = i64
+    L.tsb_launch_scratch_bytes.argtypes = [vp, ctypes.POINTER(i32), i64, i64, ctypes.POINTER(Scalar), ctypes.c_int]
+    L.tsb_launch.restype = ctypes.c_int
+    L.tsb_launch.argtypes = [vp, ctypes.POINTER(i32), i64, i64, vp, ctypes.POINTER(vp), ctypes.POINTER(Scalar), ctypes.c_int,
+                             vp, i64, vp]
     _lib = L
     return L
 
