@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the B200 execution backend on the workloads BASELINE.json names.
+"""Benchmark of the B200 execution backend on its five configured workloads.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 

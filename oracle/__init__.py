@@ -21,10 +21,11 @@ F32, F16, BF16 = 0, 1, 2
 
 
 def build(reference_root=None):
-    """Compile liborc.so; also the reference's own memrefCopy when its sources exist."""
+    """Compile liborc.so; also the reference's own memrefCopy when a checkout of the reference is named
+    (argument, or the environment variable TSB_REFERENCE_ROOT)."""
     subprocess.check_call(["make", "-s", "-C", HERE, "liborc.so"])
-    ref = reference_root or "/root/reference"
-    if os.path.exists(os.path.join(ref, "backend/include/ExecutionEngine/CRunnerUtils.cpp")):
+    ref = reference_root or os.environ.get("TSB_REFERENCE_ROOT", "")
+    if ref and os.path.exists(os.path.join(ref, "backend/include/ExecutionEngine/CRunnerUtils.cpp")):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", f"REF={ref}"],
                               stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
 

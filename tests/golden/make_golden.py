@@ -15,7 +15,8 @@ import sys
 import types
 
 assert os.environ.get("TRITON_INTERPRET") == "1", "run with TRITON_INTERPRET=1"
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+assert len(sys.argv) > 1, "usage: make_golden.py /path/to/triton-shared"
+ref = sys.argv[1]
 
 import numpy as np
 import torch

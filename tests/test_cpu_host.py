@@ -459,6 +459,46 @@ def test_launch_hooks_are_called():
     assert torch.equal(out, x + 1)
 
 
+def test_tile_tables_are_keyed_by_content():
+    """Two specialisations of one kernel (same name, scalars and grid, different GROUP_M) must not
+    share an uploaded pid -> tile table, also under a partial program range."""
+    import kernels as K
+    M = N = 512
+    Kd = 128
+    torch.manual_seed(5)
+    A = (2 * torch.rand(M, Kd) - 1).half()
+    B = (2 * torch.rand(Kd, N) - 1).half()
+    ref = (A.float() @ B.float())
+    outs = []
+    with fake_device():
+        drv = tsb.activate()
+        for gm in (8, 1):
+            C = torch.zeros(M, N, dtype=torch.float16)
+            with drv.program_range(0, 5):  # 5 of the 8 programs: which tiles those are depends on GROUP_M
+                K.matmul_kernel[(8,)](A, B, C, M, N, Kd, Kd, 1, N, 1, N, 1, BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=gm)
+            outs.append(C)
+    tiles_of = {8: [(0, 0), (1, 0), (2, 0), (3, 0), (0, 1)], 1: [(0, 0), (0, 1), (1, 0), (1, 1), (2, 0)]}
+    for gm, C in zip((8, 1), outs):
+        for tm in range(4):
+            for tn in range(2):
+                blk = C[tm * 128:(tm + 1) * 128, tn * 256:(tn + 1) * 256].float()
+                want = ref[tm * 128:(tm + 1) * 128, tn * 256:(tn + 1) * 256] if (tm, tn) in tiles_of[gm] else torch.zeros(128, 256)
+                assert torch.allclose(blk, want, rtol=1e-2, atol=1e-2), (gm, tm, tn)
+
+
+def test_driver_check_reports_a_device_side_timeout():
+    """B200Driver.check() turns the status word a timed-out device wait leaves behind into an exception."""
+    from triton_shared_b200.backend.driver import B200Launcher
+    from triton_shared_b200.backend.runtime import TsbError
+    with fake_device():
+        drv = tsb.activate()
+        drv.check()  # nothing recorded: passes
+        B200Launcher.memory._status[:] = [-4, 1, 17, 3]
+        with pytest.raises(TsbError, match="tile 17"):
+            drv.check()
+        drv.check()  # the word was cleared
+
+
 def test_c_plan_evaluator_parses_every_family():
     """tsb_plan_create reads the plan text of each kernel family (no GPU needed: nothing is launched)."""
     import json

@@ -113,7 +113,7 @@ def test_vec_add_golden_bit_exact(oracle_lib, gold):
 
 
 def test_vec_add_config_and_threads(oracle_lib):
-    """BASELINE config 1: n = 98,432, 97 programs, last block 128 valid; thread count does not change results."""
+    """Configured workload 1: n = 98,432, 97 programs, last block 128 valid; thread count does not change results."""
     rng = np.random.default_rng(0)
     x, y = rng.random(98_432, dtype=np.float32), rng.random(98_432, dtype=np.float32)
     z1 = oracle_lib.vec_add(x, y, 98_432, 1024, threads=1)
@@ -148,7 +148,7 @@ def test_matmul_golden(oracle_lib, gold):
 
 
 def test_reduce_rows_and_total(oracle_lib):
-    """BASELINE config 5, CPU-check size: 512 x 768 viewed with strides [1, 512], ragged to 740 columns."""
+    """Configured workload 5, CPU-check size: 512 x 768 viewed with strides [1, 512], ragged to 740 columns."""
     rng = np.random.default_rng(4)
     flat = rng.standard_normal(512 * 768).astype(np.float32)
     rows = oracle_lib.reduce_rows(flat, 512, 740, 1, 512, 64, 64)

@@ -51,7 +51,7 @@ def _check(c, a, b, oracle_lib, BM, BN, BK, GM=8):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_matmul_512_vs_oracle(drv, oracle_lib, dtype):
-    """BASELINE config 4, CPU-check size: M=N=K=512, blocks 128/256/64."""
+    """Configured workload 4, CPU-check size: M=N=K=512, blocks 128/256/64."""
     torch.manual_seed(3)
     a = (2 * torch.rand(512, 512) - 1).to(dtype).cuda()
     b = (2 * torch.rand(512, 512) - 1).to(dtype).cuda()
@@ -137,3 +137,23 @@ def test_matmul_other_block_shapes(drv, oracle_lib, BN, BK):
     b = (2 * torch.rand(512, 640) - 1).bfloat16().cuda()
     c = _run(K.matmul_kernel, a, b, 128, BN, BK)
     _check(c, a, b, oracle_lib, 128, BN, BK)
+
+
+def test_second_device_after_first(tsb_driver):
+    """Kernel attributes (dynamic shared memory limits) are per device: a matmul on device 1 after one
+    on device 0 in the same process must launch (skipped on a single-GPU lease)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import kernels as K
+    outs = []
+    for dev in (0, 1):
+        torch.cuda.set_device(dev)
+        torch.manual_seed(3)
+        A = (2 * torch.rand(256, 128, device="cuda") - 1).bfloat16()
+        B = (2 * torch.rand(128, 512, device="cuda") - 1).bfloat16()
+        C = torch.zeros(256, 512, dtype=torch.bfloat16, device="cuda")
+        K.matmul_kernel[(4,)](A, B, C, 256, 512, 128, 128, 1, 512, 1, 512, 1, BLOCK_M=128, BLOCK_N=256, BLOCK_K=64, GROUP_M=8)
+        torch.cuda.synchronize()
+        ref = A.float() @ B.float()
+        assert ((C.float() - ref).abs().max() / ref.abs().max()).item() <= 1e-2
+    torch.cuda.set_device(0)
