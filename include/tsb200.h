@@ -159,8 +159,10 @@ enum tsb_opcode {
   TSB_OP_REDUCE = 100, /* tsb_block_program only: dst <- fold of reg a along dim imm2 with combiner opcode imm */
   TSB_OP_LOOP_BEGIN = 101, /* loop slot a runs imm iterations; tsb_block_program: b = index of the op after its LOOP_END */
   TSB_OP_LOOP_END = 102,   /* closes loop slot a */
-  TSB_OP_ARGREDUCE = 103   /* tsb_block_program only: (dst, c) <- (value, index) of the largest (imm = 1) or smallest
+  TSB_OP_ARGREDUCE = 103,  /* tsb_block_program only: (dst, c) <- (value, index) of the largest (imm = 1) or smallest
                               (imm = 0) element of reg a along dim imm2, indices from reg b, ties to the smaller index */
+  TSB_OP_SCAN = 104        /* tsb_block_program only: dst <- inclusive running combination of reg a along dim imm2 with
+                              combiner opcode imm (TSB_OP_ADDF or TSB_OP_ADDI: tl.cumsum, ConversionPatterns.hpp:1941-2007) */
 };
 
 enum tsb_cmp {

@@ -191,3 +191,91 @@ def reduce_all(x, block=1024):
     x = np.ascontiguousarray(x, dtype=np.float32)
     lib().orc_reduce_all(_p(x), _p(out), x.size, block)
     return out[0]
+
+
+# --------------------------------------------------------------------------------------------------
+# Restatements in numpy of the lowered forms beyond the five configured workloads.  Every fold runs
+# left to right over the reduced axis (one numpy operation per step, vectorised over the other
+# axes), which is the order of the reference's linalg.reduce loops.
+
+_F32 = np.float32
+
+
+def fold(x, axis, comb):
+    """tt.reduce with a single-op combiner: acc = comb(x_i, acc) from the combiner's identity, i
+    ascending (ReduceConverter, ConversionPatterns.hpp:1203-1440; identities 1227-1278)."""
+    x = np.asarray(x)
+    fl = x.dtype.kind == "f"
+    ident = {"addf": 0.0, "mulf": 1.0, "maxnumf": -np.inf, "maximumf": -np.inf, "minnumf": np.inf, "minimumf": np.inf,
+             "addi": 0, "muli": 1, "andi": -1, "ori": 0, "xori": 0, "maxsi": np.iinfo(np.int32).min,
+             "minsi": np.iinfo(np.int32).max}[comb]
+    op = {"addf": np.add, "mulf": np.multiply, "maxnumf": np.fmax, "minnumf": np.fmin, "maximumf": np.maximum,
+          "minimumf": np.minimum, "addi": np.add, "muli": np.multiply, "andi": np.bitwise_and, "ori": np.bitwise_or,
+          "xori": np.bitwise_xor, "maxsi": np.maximum, "minsi": np.minimum}[comb]
+    acc = np.full(np.take(x, 0, axis=axis).shape, ident, dtype=x.dtype)
+    with np.errstate(all="ignore"):
+        for i in range(x.shape[axis]):
+            acc = op(np.take(x, i, axis=axis), acc).astype(x.dtype)
+    return acc if fl else acc.astype(x.dtype)
+
+
+def argfold(x, axis, want_max):
+    """tl.argmax / tl.argmin: fold of (value, index) pairs from (-inf | +inf, -1); an element replaces the
+    running pair when it is strictly better, or equal with a smaller index, so NaNs never win and a
+    line of only -inf (+inf) keeps index -1 (ArgMinMaxBaseConverter, ConversionPatterns.hpp:1442-1769)."""
+    x = np.asarray(x, dtype=_F32)
+    shape = np.take(x, 0, axis=axis).shape
+    bv = np.full(shape, -np.inf if want_max else np.inf, dtype=_F32)
+    bi = np.full(shape, -1, dtype=np.int32)
+    with np.errstate(invalid="ignore"):
+        for i in range(x.shape[axis]):
+            v = np.take(x, i, axis=axis)
+            upd = ((v > bv) if want_max else (v < bv)) | ((v == bv) & (i < bi))
+            bv, bi = np.where(upd, v, bv), np.where(upd, np.int32(i), bi)
+    return bv, bi
+
+
+def cumsum(x, axis):
+    """tl.cumsum -> ttx.cumsum: out[i] = out[i-1] + x[i] along the axis, in the element type
+    (CumSumConverter, ConversionPatterns.hpp:1941-2007)."""
+    x = np.asarray(x)
+    out = np.empty_like(x)
+    run = np.zeros(np.take(x, 0, axis=axis).shape, dtype=x.dtype)
+    idx = [slice(None)] * x.ndim
+    for i in range(x.shape[axis]):
+        run = (run + np.take(x, i, axis=axis)).astype(x.dtype)
+        idx[axis] = i
+        out[tuple(idx)] = run
+    return out
+
+
+def layernorm_bwd_dx(x, dy, w, mean, rstd):
+    """Row-wise input gradient of LayerNorm in fp32 with separately rounded products, sums folded left
+    to right: xhat = (x - mean) * rstd; wdy = w * dy; c1 = sum(xhat * wdy) / N; c2 = sum(wdy) / N;
+    dx = (wdy - (xhat * c1 + c2)) * rstd (the dx kernel of the LayerNorm tutorial the reference's
+    examples follow, without its lock-protected partial accumulation)."""
+    x, dy, w = (np.asarray(a, dtype=_F32) for a in (x, dy, w))
+    n = _F32(x.shape[1])
+    xhat = ((x - mean[:, None]).astype(_F32) * rstd[:, None]).astype(_F32)
+    wdy = (w[None, :] * dy).astype(_F32)
+    c1 = (fold((xhat * wdy).astype(_F32), 1, "addf") / n).astype(_F32)
+    c2 = (fold(wdy, 1, "addf") / n).astype(_F32)
+    inner = ((xhat * c1[:, None]).astype(_F32) + c2[:, None]).astype(_F32)
+    return ((wdy - inner).astype(_F32) * rstd[:, None]).astype(_F32)
+
+
+def layernorm_bwd_dwdb(dw_part, db_part, block_m):
+    """Column sums of the partial weight / bias gradients: lane accumulators over row blocks of
+    `block_m`, then a left-to-right fold over the block's rows
+    (test/Conversion/StructuredToMemref/kernel-05-layer-norm-dwdb.mlir)."""
+    out = []
+    for part in (dw_part, db_part):
+        part = np.asarray(part, dtype=_F32)
+        m = part.shape[0]
+        acc = np.zeros((block_m, part.shape[1]), dtype=_F32)
+        for r0 in range(0, m, block_m):
+            blk = np.zeros_like(acc)
+            blk[: min(block_m, m - r0)] = part[r0:r0 + block_m]
+            acc = (acc + blk).astype(_F32)
+        out.append(fold(acc, 0, "addf"))
+    return out

@@ -248,13 +248,25 @@ class FakeLib:
                     shp = tuple(max(a, b) for a, b in zip(R[o.a].shape, R[o.b].shape))
                     val = np.broadcast_to(R[o.a], shp).view(np.float32)
                     ind = np.broadcast_to(R[o.b], shp).view(np.int32)
-                    key = np.where(np.isnan(val), -np.inf if want_max else np.inf, val)
-                    best = key.max(axis=d, keepdims=True) if want_max else key.min(axis=d, keepdims=True)
-                    cand = np.where(key == best, ind, np.iinfo(np.int32).max)
-                    bi = cand.min(axis=d, keepdims=True)
-                    pick = np.argmax((key == best) & (ind == bi), axis=d)
-                    R[o.dst] = np.take_along_axis(val, np.expand_dims(pick, d), axis=d).view(np.uint32).copy()
-                    R[o.c] = bi.astype(np.int32).view(np.uint32)
+                    # left-to-right fold from (-inf | +inf, -1): strictly better, or equal with a smaller index
+                    n = val.shape[d]
+                    bv = np.full(np.take(val, [0], axis=d).shape, -np.inf if want_max else np.inf, dtype=np.float32)
+                    bi = np.full(bv.shape, -1, dtype=np.int32)
+                    with np.errstate(invalid="ignore"):
+                        for j in range(n):
+                            v, ix = np.take(val, [j], axis=d), np.take(ind, [j], axis=d)
+                            upd = ((v > bv) if want_max else (v < bv)) | ((v == bv) & (ix < bi))
+                            bv, bi = np.where(upd, v, bv), np.where(upd, ix, bi)
+                    R[o.dst] = np.ascontiguousarray(bv.astype(np.float32)).view(np.uint32).copy()
+                    R[o.c] = np.ascontiguousarray(bi.astype(np.int32)).view(np.uint32)
+                elif name == "scan":
+                    src = R[o.a]
+                    d = int(o.imm2)
+                    if _OPNAME[o.imm] == "addf":
+                        acc = np.cumsum(src.view(np.float32), axis=d, dtype=np.float32).view(np.uint32)
+                    else:
+                        acc = np.cumsum(src.view(np.int32).astype(np.int64), axis=d).astype(np.int32).view(np.uint32)
+                    R[o.dst] = np.ascontiguousarray(acc)
                 elif name == "reduce":
                     comb, d = _OPNAME[o.imm], int(o.imm2)
                     src = R[o.a]

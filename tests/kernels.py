@@ -419,3 +419,64 @@ def tile_argmin_kernel(x_ptr, idx_ptr, stride_m, BM: tl.constexpr, BN: tl.conste
     offs_n = tl.arange(0, BN)
     x = tl.load(x_ptr + offs_m[:, None] * stride_m + offs_n[None, :])
     tl.store(idx_ptr + offs_m, tl.argmin(x, axis=1))
+
+
+@triton.jit
+def row_cumsum_kernel(x_ptr, y_ptr, stride, n, BLOCK: tl.constexpr):
+    """Inclusive running sum of each row (tl.cumsum -> tt.scan with an add region)."""
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK)
+    m = cols < n
+    x = tl.load(x_ptr + row * stride + cols, mask=m, other=0.0)
+    tl.store(y_ptr + row * stride + cols, tl.cumsum(x, axis=0), mask=m)
+
+
+@triton.jit
+def tile_cumsum_kernel(x_ptr, y_ptr, stride_m, BM: tl.constexpr, BN: tl.constexpr):
+    """Running sum along axis 1 of a 2-D int32 tile per program."""
+    rows = tl.program_id(0) * BM + tl.arange(0, BM)
+    cols = tl.arange(0, BN)
+    offs = rows[:, None] * stride_m + cols[None, :]
+    tl.store(y_ptr + offs, tl.cumsum(tl.load(x_ptr + offs), axis=1))
+
+
+@triton.jit
+def layernorm_bwd_dx_kernel(DX, DY, X, W, Mean, Rstd, stride, N, BLOCK_N: tl.constexpr):
+    """Input gradient of LayerNorm, one row per program (the dx part of the tutorial's backward
+    kernel; its lock-protected dw/db partial accumulation is not part of the reference's lowering)."""
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK_N)
+    mask = cols < N
+    x = tl.load(X + row * stride + cols, mask=mask, other=0).to(tl.float32)
+    dy = tl.load(DY + row * stride + cols, mask=mask, other=0).to(tl.float32)
+    w = tl.load(W + cols, mask=mask).to(tl.float32)
+    mean = tl.load(Mean + row)
+    rstd = tl.load(Rstd + row)
+    xhat = (x - mean) * rstd
+    wdy = w * dy
+    xhat = tl.where(mask, xhat, 0.)
+    wdy = tl.where(mask, wdy, 0.)
+    c1 = tl.sum(xhat * wdy, axis=0) / N
+    c2 = tl.sum(wdy, axis=0) / N
+    dx = (wdy - (xhat * c1 + c2)) * rstd
+    tl.store(DX + row * stride + cols, dx, mask=mask)
+
+
+@triton.jit
+def layernorm_bwd_dwdb_kernel(DW, DB, FINAL_DW, FINAL_DB, M, N, BLOCK_SIZE_M: tl.constexpr, BLOCK_SIZE_N: tl.constexpr):
+    """Column sums of the partial weight / bias gradients (python/examples/test_layernorm.py's
+    _layer_norm_bwd_dwdb; lowered form in kernel-05-layer-norm-dwdb.mlir)."""
+    pid = tl.program_id(0)
+    cols = pid * BLOCK_SIZE_N + tl.arange(0, BLOCK_SIZE_N)
+    dw = tl.zeros((BLOCK_SIZE_M, BLOCK_SIZE_N), dtype=tl.float32)
+    db = tl.zeros((BLOCK_SIZE_M, BLOCK_SIZE_N), dtype=tl.float32)
+    for i in range(0, M, BLOCK_SIZE_M):
+        rows = i + tl.arange(0, BLOCK_SIZE_M)
+        mask = (rows[:, None] < M) & (cols[None, :] < N)
+        offs = rows[:, None] * N + cols[None, :]
+        dw += tl.load(DW + offs, mask=mask, other=0.)
+        db += tl.load(DB + offs, mask=mask, other=0.)
+    sum_dw = tl.sum(dw, axis=0)
+    sum_db = tl.sum(db, axis=0)
+    tl.store(FINAL_DW + cols, sum_dw, mask=cols < N)
+    tl.store(FINAL_DB + cols, sum_db, mask=cols < N)

@@ -335,7 +335,10 @@ def _block_program_cases(dev):
     x = torch.randn(9, 300, device=dev)
     s = torch.zeros(9, device=dev)
     K.block_sum_kernel[(9,)](x, s, 300, 290, BLOCK_SIZE=512)
-    out.append(("block_sum", s.cpu(), x[:, :290].sum(dim=1).cpu(), 1e-4))
+    import oracle as O
+    npf = lambda t: t.detach().cpu().numpy()
+    # left-to-right folds of the oracle; the GPU folds in a tree, so float sums agree within rounding
+    out.append(("block_sum", s.cpu(), torch.from_numpy(O.fold(npf(x[:, :290]), 1, "addf")), 1e-4))
     # the reference's own block-pointer test: 32 programs of 16 elements (test_reduce.py:33-43, rtol 1e-3)
     xb = torch.rand(32, 16, device=dev)
     sb = torch.zeros(32, device=dev)
@@ -352,40 +355,75 @@ def _block_program_cases(dev):
     rmax = torch.full((50,), -7, dtype=torch.int32, device=dev)
     cmin = torch.full((4 * 32,), -7, dtype=torch.int32, device=dev)
     K.tile_max_kernel[(4,)](xi, rmax, cmin, 24, 50, 24, BM=16, BN=32)
-    out.append(("tile_rowmax", rmax.cpu(), torch.maximum(xi.max(dim=1).values, torch.zeros(1, dtype=torch.int32, device=dev)).cpu(), 0))
+    # masked lanes load other = 0 and take part in the fold (the reference reduces the whole filled block)
+    blk_rows = np.zeros((50, 32), dtype=np.int32)
+    blk_rows[:, :24] = npf(xi)
+    out.append(("tile_rowmax", rmax.cpu(), torch.from_numpy(O.fold(blk_rows, 1, "maxsi")), 0))
     exp_cmin = torch.full((4, 32), -7, dtype=torch.int32)
     xc = xi.cpu()
     for pid in range(4):
         blk = torch.zeros(16, 32, dtype=torch.int32)
         rows = xc[pid * 16:(pid + 1) * 16]
         blk[:rows.shape[0], :24] = rows
-        exp_cmin[pid, :24] = blk.min(dim=0).values[:24]
+        exp_cmin[pid, :24] = torch.from_numpy(O.fold(blk.numpy(), 0, "minsi"))[:24]
     out.append(("tile_colmin", cmin.cpu().reshape(4, 32), exp_cmin, 0))
     # argmax / argmin: ties go to the smaller index
     xa = torch.randint(0, 5, (6, 100), device=dev).float()  # many ties
     av = torch.zeros(6, device=dev)
     ai = torch.zeros(6, dtype=torch.int32, device=dev)
     K.row_argmax_kernel[(6,)](xa, av, ai, 100, 90, BLOCK=128)
-    firsts = torch.tensor([int((r[:90] == r[:90].max()).nonzero()[0]) for r in xa.cpu()], dtype=torch.int32)
-    out.append(("argmax_val", av.cpu(), xa[:, :90].max(dim=1).values.cpu(), 0))
-    out.append(("argmax_idx", ai.cpu(), firsts, 0))
+    xa[1, 3] = float("nan")      # a NaN never wins the reference's fold
+    xa[2, :] = float("-inf")     # a line without any winner keeps index -1
+    K.row_argmax_kernel[(6,)](xa, av, ai, 100, 90, BLOCK=128)
+    padded = np.full((6, 128), -np.inf, dtype=np.float32)  # the kernel loads other = -inf beyond n
+    padded[:, :90] = npf(xa[:, :90])
+    ov, oi = O.argfold(padded, 1, True)
+    out.append(("argmax_val", av.cpu(), torch.from_numpy(ov), 0))
+    out.append(("argmax_idx", ai.cpu(), torch.from_numpy(oi), 0))
     xt = torch.randn(32, 16, device=dev)
     ti = torch.zeros(32, dtype=torch.int32, device=dev)
     K.tile_argmin_kernel[(4,)](xt, ti, 16, BM=8, BN=16)
-    out.append(("argmin_axis1", ti.cpu(), xt.argmin(dim=1).to(torch.int32).cpu(), 0))
+    out.append(("argmin_axis1", ti.cpu(), torch.from_numpy(O.argfold(npf(xt), 1, False)[1]), 0))
     # loops that carry block values (device-side loops of the block-program kernel)
     xr = torch.randn(7, 1000, device=dev)
     rs = torch.zeros(7, device=dev)
     rm = torch.zeros(7, device=dev)
     K.row_stats_kernel[(7,)](xr, rs, rm, 1000, 900, BLOCK=256)
-    out.append(("row_stats_sum", rs.cpu(), xr[:, :900].sum(dim=1).cpu(), 1e-4))
-    out.append(("row_stats_max", rm.cpu(), xr[:, :900].max(dim=1).values.cpu(), 0))
+    out.append(("row_stats_sum", rs.cpu(), torch.from_numpy(O.fold(npf(xr[:, :900]), 1, "addf")), 1e-4))
+    out.append(("row_stats_max", rm.cpu(), torch.from_numpy(O.fold(npf(xr[:, :900]), 1, "maxnumf")), 0))
     xs = torch.randn(6, 2500, device=dev)
     os_ = torch.full((6, 2500), -1.0, device=dev)
     K.wide_softmax_kernel[(6,)](os_, xs, 2500, 2400, BLOCK=512)
     exp = torch.full((6, 2500), -1.0)
     exp[:, :2400] = torch.softmax(xs[:, :2400].cpu(), dim=1)
     out.append(("wide_softmax", os_.cpu(), exp, 1e-5))
+    # running sums (tl.cumsum): float rows with a ragged tail, and an int32 tile along axis 1 (exact)
+    xc_ = torch.randn(5, 300, device=dev)
+    yc = torch.full((5, 300), -3.0, device=dev)
+    K.row_cumsum_kernel[(5,)](xc_, yc, 300, 260, BLOCK=512)
+    expc = torch.full((5, 300), -3.0)
+    expc[:, :260] = torch.from_numpy(O.cumsum(npf(xc_[:, :260]), 1))
+    out.append(("row_cumsum", yc.cpu(), expc, 1e-4))
+    ti_ = torch.randint(-50, 50, (16, 32), dtype=torch.int32, device=dev)
+    to = torch.zeros_like(ti_)
+    K.tile_cumsum_kernel[(2,)](ti_, to, 32, BM=8, BN=32)
+    out.append(("tile_cumsum_int", to.cpu(), torch.from_numpy(O.cumsum(npf(ti_), 1)), 0))
+    # LayerNorm backward: input gradient per row, and the column sums of the partial dw / db
+    Mb, Nb = 6, 200
+    xb_ = torch.randn(Mb, Nb, device=dev)
+    dyb = torch.randn(Mb, Nb, device=dev)
+    wb = torch.rand(Nb, device=dev) + 0.5
+    mean = xb_.mean(dim=1)
+    rstd = 1.0 / torch.sqrt(xb_.var(dim=1, unbiased=False) + 1e-5)
+    dxb = torch.zeros_like(xb_)
+    K.layernorm_bwd_dx_kernel[(Mb,)](dxb, dyb, xb_, wb, mean, rstd, Nb, Nb, BLOCK_N=256)
+    out.append(("ln_bwd_dx", dxb.cpu(), torch.from_numpy(O.layernorm_bwd_dx(npf(xb_), npf(dyb), npf(wb), npf(mean), npf(rstd))), 1e-4))
+    dwp, dbp = torch.randn(70, 300, device=dev), torch.randn(70, 300, device=dev)
+    fdw, fdb = torch.zeros(300, device=dev), torch.zeros(300, device=dev)
+    K.layernorm_bwd_dwdb_kernel[(3,)](dwp, dbp, fdw, fdb, 70, 300, BLOCK_SIZE_M=32, BLOCK_SIZE_N=128)
+    edw, edb = O.layernorm_bwd_dwdb(npf(dwp), npf(dbp), 32)
+    out.append(("ln_bwd_dw", fdw.cpu(), torch.from_numpy(edw), 1e-4))
+    out.append(("ln_bwd_db", fdb.cpu(), torch.from_numpy(edb), 1e-4))
     return out
 
 
@@ -397,7 +435,7 @@ def test_block_programs_on_host_stand_in():
             assert torch.equal(got, exp), name
         else:
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
-    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 8
+    assert [c[0] for c in lib.calls] == ["tsb_block_program"] * 13  # argmax runs twice (before and after the NaN / -inf rows)
 
 
 # ------------------------------------------------------------------ a spread of elementwise ops

@@ -611,7 +611,7 @@ def _reads(o):
     if opc in ("select", "fma"):
         return [o[3], o[4], o[5]]
     if opc in ("exp", "exp2", "log", "log2", "sqrt", "rsqrt", "sin", "cos", "tanh", "erf", "absf", "negf",
-               "floor", "ceil", "absi", "cast", "bitcast", "mov", "reduce"):
+               "floor", "ceil", "absi", "cast", "bitcast", "mov", "reduce", "scan"):
         return [o[3]]
     return [o[3], o[4]]
 
@@ -1083,6 +1083,9 @@ class _BpLowering(_EwLowering):
                 self.ops[-1][5] = ri
                 pair = self.arg_pairs[key] = (rv, ri)
             return pair[n.attr("out")]
+        if n.op == "scan":
+            src = self.value(n.args[0], dimmap)
+            return self.emit("scan", n.dtype, a=src, imm=n.attr("comb"), imm2=dimmap[n.attr("axis")], mask=self.vmask[src])
         if n.op == "reduce":
             ax, comb = n.attr("axis"), n.attr("comb")
             if comb not in ("addf", "mulf", "maxnumf", "minnumf", "maximumf", "minimumf", "addi", "muli", "maxsi",
@@ -1191,7 +1194,7 @@ class _BpLowering(_EwLowering):
                 m = self.vmask[o[2]]
                 # an elementwise result may overwrite an operand of the same mask that dies here; a
                 # reduction never writes into its own source
-                if o[0] not in ("reduce", "argreduce"):
+                if o[0] not in ("reduce", "argreduce", "scan"):
                     for r in set(reads):
                         if last_use[r] == i and r in phys:
                             free.setdefault(self.vmask[r], []).append(phys.pop(r))

@@ -32,7 +32,7 @@ OPCODES = {
     "addi": 50, "subi": 51, "muli": 52, "divsi": 53, "remsi": 54, "divui": 55, "remui": 56,
     "minsi": 57, "maxsi": 58, "minui": 59, "maxui": 60, "andi": 61, "ori": 62, "xori": 63,
     "shli": 64, "shrsi": 65, "shrui": 66, "absi": 67,
-    "cmpf": 80, "cmpi": 81, "select": 82, "cast": 90, "bitcast": 91, "fma": 92, "reduce": 100, "loop_begin": 101, "loop_end": 102, "argreduce": 103,
+    "cmpf": 80, "cmpi": 81, "select": 82, "cast": 90, "bitcast": 91, "fma": 92, "reduce": 100, "loop_begin": 101, "loop_end": 102, "argreduce": 103, "scan": 104,
 }
 CMPF = {"oeq": 1, "ogt": 2, "oge": 3, "olt": 4, "ole": 5, "one": 6, "ord": 7, "ueq": 8, "ugt": 9,
         "uge": 10, "ult": 11, "ule": 12, "une": 13, "uno": 14}

@@ -557,6 +557,8 @@ class Analyzer:
             self._store(op, env, effects, loop_stack, record)
         elif n == "tt.reduce":
             self._reduce(op, env)
+        elif n == "tt.scan":
+            self._scan(op, env)
         elif n == "tt.dot":
             a, b, c = (self.as_data(get(k)) for k in range(3))
             env[res] = TData(self.node("dot", (a, b, c), (), rty.shape, rty.elem))
@@ -890,6 +892,21 @@ class Analyzer:
         src = self.as_data(env[op.operands[0]])
         rty = op.results[0][1]
         env[op.results[0][0]] = TData(self.node("reduce", (src,), {"axis": op.attrs["axis"], "comb": comb},
+                                                rty.shape, rty.elem))
+
+    def _scan(self, op: Op, env):
+        """tl.cumsum: the one scan the reference lowers (a single add combining the two block
+        arguments, CumSumConverter, ConversionPatterns.hpp:1941-2007)."""
+        blk = op.regions[0]
+        body = [o for o in blk.ops if o.name != "tt.scan.return"]
+        if len(op.operands) != 1 or len(body) != 1 or body[0].name not in ("arith.addf", "arith.addi") or \
+                set(body[0].operands) != {a for a, _ in blk.args}:
+            raise UnsupportedTTIR("tt.scan other than a cumulative sum")
+        if op.attrs.get("reverse"):
+            raise UnsupportedTTIR("reverse tt.scan")
+        src = self.as_data(env[op.operands[0]])
+        rty = op.results[0][1]
+        env[op.results[0][0]] = TData(self.node("scan", (src,), {"axis": op.attrs["axis"], "comb": body[0].name.split(".")[1]},
                                                 rty.shape, rty.elem))
 
     def _arg_reduce(self, op: Op, env, blk: Block, body):

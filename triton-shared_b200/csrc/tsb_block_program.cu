@@ -241,26 +241,55 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         for (int o = warp; o < P.reg_n[op.dst]; o += BP_THREADS / 32) {
           int c[3];
           reg_coords(P.lg, md, o, c[0], c[1], c[2]);
-          bool have = false;
-          float bv = 0.f;
-          int bi = 0;
+          // the reference folds from (-inf | +inf, -1): an element replaces the running pair only if it is
+          // strictly better or ties with a smaller index, so NaNs never win and a line without any
+          // winner keeps index -1 (ConversionPatterns.hpp:1569-1672, 1734, 1765)
+          float bv = __uint_as_float(want_max ? 0xff800000u : 0x7f800000u);
+          int bi = -1;
           for (int j = lane; j < len; j += 32) {
             c[d] = j;
             const float v = __uint_as_float(vsrc[reg_index(P.lg, mv, c[0], c[1], c[2])]);
             const int ix = (int)isrc[reg_index(P.lg, mi, c[0], c[1], c[2])];
-            // fold order of the reference: acc = combine(element, acc)
-            if (!have || better(v, ix, bv, bi)) { bv = v; bi = ix; have = true; }
+            if (better(v, ix, bv, bi)) { bv = v; bi = ix; }
           }
 #pragma unroll
           for (int s = 16; s > 0; s >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, s);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, s);
-            const bool oh = __shfl_xor_sync(0xffffffffu, have ? 1 : 0, s) != 0;
-            if (oh && (!have || better(ov, oi, bv, bi))) { bv = ov; bi = oi; have = true; }
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
           }
           if (lane == 0) {
             vdst[o] = __float_as_uint(bv);
             idst[o] = (unsigned)bi;
+          }
+        }
+      } else if (op.opcode == TSB_OP_SCAN) {
+        // dst = inclusive running combination of src along dim imm2 (cumulative sum): one warp per
+        // line, 32 elements per step with a shuffle scan, the running total carried between steps
+        const int d = (int)op.imm2, comb = (int)op.imm;
+        const int m = P.reg_mask[op.a];
+        const unsigned *src = bp_smem + P.reg_off[op.a];
+        unsigned *dst = bp_smem + P.reg_off[op.dst];
+        const int len = (m & (1 << d)) ? P.size[d] : 1;
+        const int lines = P.reg_n[op.a] / len;
+        const int md = m & ~(1 << d);  // coordinates of a line: the register's dims without the scanned one
+        for (int o = warp; o < lines; o += BP_THREADS / 32) {
+          int c[3];
+          reg_coords(P.lg, md, o, c[0], c[1], c[2]);
+          unsigned carry = combine_identity(comb);
+          for (int j0 = 0; j0 < len; j0 += 32) {
+            const int j = j0 + lane;
+            c[d] = j < len ? j : 0;
+            const int at = reg_index(P.lg, m, c[0], c[1], c[2]);
+            unsigned v = j < len ? src[at] : combine_identity(comb);
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) {
+              const unsigned up = __shfl_up_sync(0xffffffffu, v, s);
+              if (lane >= s) v = combine(comb, op.type, up, v);
+            }
+            v = combine(comb, op.type, carry, v);
+            if (j < len) dst[at] = v;
+            carry = __shfl_sync(0xffffffffu, v, 31);
           }
         }
       } else if (op.opcode == TSB_OP_REDUCE) {
@@ -385,7 +414,9 @@ extern "C" int tsb_block_program(const tsb_access *acc, int n_acc, const tsb_op 
     if (o.opcode == TSB_OP_LOAD && acc[o.a].is_store == 1) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d loads from a store access", k);
     if (o.opcode == TSB_OP_STORE && acc[o.a].is_store != 1) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d stores to a load access", k);
     if (o.opcode == TSB_OP_STORE) o.imm = o.imm << (3 - rank);
-    if (o.opcode == TSB_OP_REDUCE || o.opcode == TSB_OP_ARGREDUCE) {
+    if (o.opcode == TSB_OP_SCAN && o.imm != TSB_OP_ADDF && o.imm != TSB_OP_ADDI)
+      return fail(TSB_ERR_UNSUPPORTED, "tsb_block_program: op %d scans with combiner %u (only sums)", k, o.imm);
+    if (o.opcode == TSB_OP_REDUCE || o.opcode == TSB_OP_ARGREDUCE || o.opcode == TSB_OP_SCAN) {
       if (o.imm2 >= (unsigned)rank) return fail(TSB_ERR_INVALID, "tsb_block_program: op %d reduces dim %u of rank %d", k, o.imm2, rank);
       o.imm2 += 3 - rank;
     }

@@ -323,7 +323,7 @@ static int opcode_of(const std::string &n) {
       {"shrui", TSB_OP_SHRUI}, {"absi", TSB_OP_ABSI}, {"cmpf", TSB_OP_CMPF}, {"cmpi", TSB_OP_CMPI},
       {"select", TSB_OP_SELECT}, {"cast", TSB_OP_CAST}, {"bitcast", TSB_OP_BITCAST}, {"fma", TSB_OP_FMA},
       {"reduce", TSB_OP_REDUCE}, {"loop_begin", TSB_OP_LOOP_BEGIN}, {"loop_end", TSB_OP_LOOP_END},
-      {"argreduce", TSB_OP_ARGREDUCE}};
+      {"argreduce", TSB_OP_ARGREDUCE}, {"scan", TSB_OP_SCAN}};
   auto it = m.find(n);
   return it == m.end() ? -1 : it->second;
 }
