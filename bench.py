@@ -46,8 +46,8 @@ MM = 8_192
 NCU_TRAFFIC_BYTES = {
     "softmax": 1.94216e9,         # 65,536 x 4,096: 4 x (268.46 MB read + 217.08 MB written) at 16,384 rows
     "vec_add": 12.5733e9,         # n = 2^30: 8 x (1.0738 GB + 497.8 MB) at n = 2^27
-    "layernorm": 121.35e6,        # 4,096 x 8,192 fp16: (268.55 MB + 216.84 MB) / 4 at 16,384 rows
-    "strided_reduce": 398.07e6,   # full size: 393.24 MB read + 4.83 MB written (row kernel)
+    "layernorm": 121.3e6,         # 4,096 x 8,192 fp16: 485.2 MB / 4 at 16,384 rows
+    "strided_reduce": 396.7e6,    # full size, the cluster row kernel
     "matmul": 1.57206e9,          # 8192^3 bf16, two-CTA kernel: 1.4427 GB read + 129.3 MB written
     "block_copy": 1.86488e9,      # 16,000 x 16,000 fp32: 4 x (256.04 MB + 210.18 MB) at 8,000 x 8,000
 }
