@@ -410,6 +410,25 @@ def main():
     e2e_ms, _ = timed(e2e_step, e2e_steps, 3, graph=False)
     e2e_value = alg_bytes * world * e2e_steps / (e2e_ms * 1e-3) / 1e9
     e2e_ok = bool(torch.allclose(hy.sum(dim=1), torch.ones(rows), rtol=1e-4))
+
+    # the host-side ceiling of that pipeline: the same chunked H2D and D2H copies with no kernel
+    # between them, all ranks at once (what the host's memory system and PCIe give N GPUs together)
+    def copy_only_step():
+        main = torch.cuda.current_stream()
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        for c in range(n_chunks):
+            r0, r1 = c * crow, (c + 1) * crow
+            with torch.cuda.stream(s_in):
+                x[r0:r1].copy_(hx[r0:r1], non_blocking=True)
+                ev_in[c].record(s_in)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_in[c])
+                hy[r0:r1].copy_(y[r0:r1], non_blocking=True)
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
+    copy_ms, _ = timed(copy_only_step, e2e_steps, 2, graph=False)
+    copy_value = alg_bytes * world * e2e_steps / (copy_ms * 1e-3) / 1e9
     clocks = sampler.stop()  # sampled across the headline and end-to-end timed regions
     del hx, hy
 
@@ -432,6 +451,8 @@ def main():
                 "d2h_bytes_per_step": rows * cols * 4 * world, "steps": e2e_steps,
                 "pipeline": f"{n_chunks} row chunks per step: H2D, kernel and D2H on three streams",
                 "host_numa": numa,
+                "copy_only": {"value": copy_value, "unit": "GB/s",
+                              "note": "same pinned H2D + D2H chunks with no kernel, all ranks at once: the host-side ceiling"},
                 "result_check": e2e_ok},
         "gpu_launches": args.steps,
         "clocks": clocks,
