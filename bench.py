@@ -463,7 +463,8 @@ def main():
     # ------------------------------------------------------------------ secondary workloads
     # the five configured workloads, the block copy, and three kernels that run on the general engines
     # (elementwise VM, block programs, device-side loops) rather than on dedicated kernels
-    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy", "gelu_bias", "rmsnorm", "wrap_rows"}
+    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy", "gelu_bias", "rmsnorm", "wrap_rows",
+             "gather_rows"}
     chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names}
     if chosen:
         wl = {}
@@ -685,6 +686,19 @@ def main():
                 wl["wrap_rows"]["result_check"] = bool(torch.equal(Cc, torch.cat([A[4090:], A[:58]])))
                 wl["wrap_rows"]["note"] = "a single program (one CTA) walks 256 column steps: bound by one SM, not by HBM"
 
+        def wl_gather_rows():
+            # row gather through a loaded int64 index (one unstructured dim, contiguous rows), fp32 65,536 x 1,024
+            R, C = (16384, 1024) if args.small else (65536, 1024)
+            x = torch.randn(R, C, device="cuda")
+            idx = torch.randperm(R, device="cuda")
+            o = torch.empty_like(x)
+
+            def step():
+                K.gather_rows_kernel[(R // 16, C // 128)](x, idx, o, R, C, C, C, BLOCK_M=16, BLOCK_N=128)
+            record("gather_rows", step, 8 * R * C + 8 * R, 1e9, "hbm", "GB/s")
+            if "value" in wl["gather_rows"]:
+                wl["gather_rows"]["result_check"] = bool(torch.equal(o, x[idx]))
+
         def wl_block_copy():
             # masked strided 2-D block copy, fp32 16,000 x 16,000 (ragged against 64 x 128 tiles), row-major to row-major
             M = N = 8000 if args.small else 16000
@@ -700,7 +714,7 @@ def main():
 
         for name, fn in (("vec_add", wl_vec_add), ("layernorm", wl_layernorm),
                          ("strided_reduce", wl_strided_reduce), ("matmul", wl_matmul),
-                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("wrap_rows", wl_wrap_rows),
+                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("wrap_rows", wl_wrap_rows), ("gather_rows", wl_gather_rows),
                          ("block_copy", wl_block_copy)):
             if name in chosen:
                 fn()

@@ -480,3 +480,16 @@ def layernorm_bwd_dwdb_kernel(DW, DB, FINAL_DW, FINAL_DB, M, N, BLOCK_SIZE_M: tl
     sum_db = tl.sum(db, axis=0)
     tl.store(FINAL_DW + cols, sum_dw, mask=cols < N)
     tl.store(FINAL_DB + cols, sum_db, mask=cols < N)
+
+
+@triton.jit
+def gather_rows_kernel(x_ptr, idx_ptr, out_ptr, n_rows, n_cols, stride_x, stride_o, BLOCK_M: tl.constexpr, BLOCK_N: tl.constexpr):
+    """out[r, :] = x[idx[r], :]: one unstructured dim (rows picked by a loaded index), contiguous rows
+    (the row form of the reference's index_select examples, tts.make_gather_scatter_tptr)."""
+    rows = tl.program_id(0) * BLOCK_M + tl.arange(0, BLOCK_M)
+    cols = tl.program_id(1) * BLOCK_N + tl.arange(0, BLOCK_N)
+    rmask = rows < n_rows
+    idx = tl.load(idx_ptr + rows, mask=rmask, other=0)
+    m = rmask[:, None] & (cols[None, :] < n_cols)
+    v = tl.load(x_ptr + idx[:, None] * stride_x + cols[None, :], mask=m, other=0.0)
+    tl.store(out_ptr + rows[:, None] * stride_o + cols[None, :], v, mask=m)

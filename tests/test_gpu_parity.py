@@ -390,3 +390,20 @@ def test_block_copy_2d(drv, dtype, M, N):
     dst_t = torch.zeros(N, M, dtype=dtype, device="cuda")
     K.copy_2d_kernel[grid](src, dst_t, M, N, N, 1, 1, M, BM=64, BN=128)
     assert torch.equal(dst_t.t(), src)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("rows,cols,src_rows", [(1000, 520, 777), (64, 100, 64)])
+def test_gather_rows_known_answer(drv, dtype, rows, cols, src_rows):
+    """Row gather through a loaded index (int64, as torch produces it): exact against indexing,
+    ragged against the 16 x 128 tiles, nothing written outside the mask."""
+    import kernels as K
+    torch.manual_seed(9)
+    x = torch.randn(src_rows, cols, device="cuda").to(dtype)
+    idx = torch.randint(0, src_rows, (rows,), device="cuda")
+    out = torch.full((rows + 3, cols + 5), -5.0, device="cuda", dtype=dtype)
+    K.gather_rows_kernel[((rows + 15) // 16, (cols + 127) // 128)](x, idx, out, rows, cols, x.stride(0), out.stride(0),
+                                                                   BLOCK_M=16, BLOCK_N=128)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:rows, :cols], x[idx])
+    assert torch.all(out[rows:] == -5.0) and torch.all(out[:, cols:] == -5.0)

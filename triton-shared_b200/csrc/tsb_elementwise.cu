@@ -232,38 +232,63 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
 // `items` lane-vectors is shared by G = items / U consecutive threads, each carrying U vectors G
 // apart (consecutive threads touch consecutive vectors); programs are dealt to thread groups in
 // the walk order of the launch, so a CTA of 256 threads works on 256 / G programs at once and
-// small blocks still fill it.  Each thread derives the program's access state itself when the
-// body reaches the load or store: no shared state, no barrier per program.
+// small blocks still fill it.  The access state of a pass's programs is derived once per
+// (program, access) and shared through shared memory when that fits the CTA (one barrier pair per
+// pass); otherwise each thread derives it itself when the body reaches the load or store.
 template <bool LOOPS>
 __global__ void __launch_bounds__(256, 4) ew_vm_packed_kernel(const __grid_constant__ EwParams P, int lg_g) {
   constexpr int VEC = 4, U = 4;
   extern __shared__ __align__(16) unsigned vm_smem[];
+  // access state of the programs of one pass, derived once per (program, access) by one thread each
+  // and read by the program's threads; used when programs-per-pass x accesses fits the CTA
+  __shared__ ProgState shared_state[256];
   const VmRegs<VEC, U> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
   const int G = 1 << lg_g;
+  const int per_pass = (int)blockDim.x >> lg_g;  // programs a CTA works on at once
+  const bool share = per_pass * P.n_acc <= 256;
   const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
-  const long long n_threads = (P.pid_hi - P.pid_lo) << lg_g;
+  const long long n_prog = P.pid_hi - P.pid_lo;
+  const long long n_threads = n_prog << lg_g;
   grid_dependency_wait();
   grid_launch_dependents();
   for (long long base = (long long)blockIdx.x * blockDim.x; base < n_threads; base += (long long)gridDim.x * blockDim.x) {
     const long long g = base + threadIdx.x;
     const bool live = g < n_threads;
     const int within = (int)(g & (G - 1));
+    const int slot = (int)threadIdx.x >> lg_g;
     long long px = 0, py = 0, pz = 0;
-    if (live) split_pid(P.grid, P.order, P.pid_lo + (g >> lg_g), px, py, pz);
+    if (live && !share) split_pid(P.grid, P.order, P.pid_lo + (g >> lg_g), px, py, pz);
     for (long long q = 0; q < (LOOPS ? P.total_trips : 1); ++q) {
       int it[TSB_MAX_LOOPS] = {0, 0, 0, 0};
-      if (LOOPS) {  // later iterations of a program see the stores of earlier ones (same CTA)
-        loop_counters(P, q, it);
-        __threadfence_block();
+      if (LOOPS) loop_counters(P, q, it);
+      if (LOOPS || share) {
+        // later iterations of a program see the stores of earlier ones (same CTA); the previous
+        // pass's shared state is no longer read
+        if (LOOPS) __threadfence_block();
+        __syncthreads();
+      }
+      if (share) {
+        const int t = (int)threadIdx.x;
+        if (t < per_pass * P.n_acc) {
+          const int sl = t / P.n_acc, a = t - sl * P.n_acc;
+          const long long prog = (base >> lg_g) + sl;
+          if (prog < n_prog) {
+            long long qx, qy, qz;
+            split_pid(P.grid, P.order, P.pid_lo + prog, qx, qy, qz);
+            if (LOOPS) program_state_loops(P.acc[a], P.size, qx, qy, qz, it, shared_state[t]);
+            else program_state(P.acc[a], P.size, qx, qy, qz, shared_state[t]);
+          }
+        }
         __syncthreads();
       }
       if (!live) continue;
       auto state = [&](int a, ProgState &ps) {
-        if (LOOPS) program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
+        if (share) ps = shared_state[slot * P.n_acc + a];
+        else if (LOOPS) program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
         else program_state(P.acc[a], P.size, px, py, pz, ps);
       };
       auto lane0 = [&](int u) { return (within + u * G) * VEC; };
-      // the access state is derived once per op (for sub-item 0) and kept for the other sub-items
+      // the access state is fetched once per op (for sub-item 0) and kept for the other sub-items
       ProgState ps;
       vm_exec<VEC, U>(
           P.ops, P.n_ops, R,

@@ -440,6 +440,25 @@ __device__ __forceinline__ void load_vec_indirect(const DAcc &A, const ProgState
   const bool outer = i0 < s.dim[0] && i1 < s.dim[1];
   const long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
   const unsigned fill = A.has_other ? A.other : 0u;
+  if (VEC == 4 && A.kind == 0 && !A.n_wrap && A.stride[2] == 1 && A.esize >= 2 && A.esize <= 4 && outer &&
+      i2 + VEC <= s.dim[2]) {
+    // row gather: the four lanes of the vector share one index (the index varies along another
+    // dim) and are all admitted: one 16-byte (8-byte) access when the row start is aligned
+    const bool same = !has_index || (index[0] == index[1 % VEC] && index[0] == index[2 % VEC] && index[0] == index[3 % VEC]);
+    const bool all = !has_mask || ((mask[0] & mask[1 % VEC] & mask[2 % VEC] & mask[3 % VEC]) & 1u);
+    const char *p = A.base + (e + (has_index ? (long long)(int)index[0] : 0ll)) * A.esize;
+    if (same && all && ((uintptr_t)p % (4u * A.esize)) == 0) {
+      if (A.esize == 4) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+        out[0] = v.x; out[1 % VEC] = v.y; out[2 % VEC] = v.z; out[3 % VEC] = v.w;
+      } else {
+        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
+        out[0] = v.x & 0xffffu; out[1 % VEC] = v.x >> 16; out[2 % VEC] = v.y & 0xffffu; out[3 % VEC] = v.y >> 16;
+      }
+      raw_to_reg<VEC>(A.dtype, out);
+      return;
+    }
+  }
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
     bool ok = outer && (i2 + k) < s.dim[2];
@@ -457,6 +476,21 @@ __device__ __forceinline__ void store_vec_indirect(const DAcc &A, const ProgStat
                                                    const unsigned (&mask)[VEC], const unsigned (&in)[VEC]) {
   if (!(i0 < s.dim[0] && i1 < s.dim[1])) return;
   const long long e = s.off + i0 * A.stride[0] + i1 * A.stride[1] + i2 * A.stride[2];
+  if (VEC == 4 && !A.n_wrap && A.stride[2] == 1 && A.esize >= 2 && A.esize <= 4 && i2 + VEC <= s.dim[2]) {
+    // row scatter: see load_vec_indirect
+    const bool same = !has_index || (index[0] == index[1 % VEC] && index[0] == index[2 % VEC] && index[0] == index[3 % VEC]);
+    const bool all = !has_mask || ((mask[0] & mask[1 % VEC] & mask[2 % VEC] & mask[3 % VEC]) & 1u);
+    char *p = A.base + (e + (has_index ? (long long)(int)index[0] : 0ll)) * A.esize;
+    if (same && all && ((uintptr_t)p % (4u * A.esize)) == 0) {
+      unsigned h[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) h[k] = in[k];
+      reg_to_raw<VEC>(A.dtype, h);
+      if (A.esize == 4) *reinterpret_cast<uint4 *>(p) = make_uint4(h[0], h[1 % VEC], h[2 % VEC], h[3 % VEC]);
+      else *reinterpret_cast<uint2 *>(p) = make_uint2(h[0] | (h[1 % VEC] << 16), h[2 % VEC] | (h[3 % VEC] << 16));
+      return;
+    }
+  }
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
     bool ok = (i2 + k) < s.dim[2];
