@@ -10,158 +10,10 @@
 //   elementwise op  lib/Conversion/TritonArithToLinalg/TritonArithToLinalg.cpp:104
 // The CPU backend materialises every block in a malloc'ed buffer and runs one
 // scalar loop per op; here a lane's values stay in registers from load to store.
-#include "tsb_ew.cuh"
+#include "tsb_vm_exec.cuh"
 #include <stdlib.h>
 
 namespace tsb {
-
-// ---- general body: a small register VM ----------------------------------------
-// One pass over the op list for VEC lanes; `ld(access, regs)` and `st(access, regs)`
-// are supplied by the kernel (blocked or flat addressing).
-// The VM's registers live in shared memory: register r of thread t is the VEC consecutive
-// words starting at (r*blockDim + t)*VEC, so one 16-byte access per register and thread (VEC = 4)
-// and consecutive threads touch consecutive 16-byte slots (conflict-free).  A register file
-// indexed by run-time register numbers cannot live in hardware registers; kept as a per-thread
-// local array it overflowed L1.  The kernels are bound by instruction issue, so the opcode
-// switch is taken once per op and thread, with operand count known inside each case.
-// Each thread carries U independent lane-vectors ("sub-items") through the op list, so the cost
-// of decoding an op is shared by U*VEC lanes and U loads per access are in flight per thread.
-template <int VEC, int U>
-struct VmRegs {
-  unsigned *base;  // shared memory
-  int nt, t;
-  __device__ __forceinline__ unsigned *slot(int reg, int u) const {
-    return base + (((size_t)reg * U + u) * nt + t) * VEC;
-  }
-  __device__ __forceinline__ void get(int reg, int u, unsigned (&v)[VEC]) const {
-    const unsigned *p = slot(reg, u);
-    if (VEC == 4) {
-      const uint4 q = *reinterpret_cast<const uint4 *>(p);
-      v[0] = q.x; v[1 % VEC] = q.y; v[2 % VEC] = q.z; v[3 % VEC] = q.w;
-    } else {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) v[k] = p[k];
-    }
-  }
-  __device__ __forceinline__ void put(int reg, int u, const unsigned (&v)[VEC]) const {
-    unsigned *p = slot(reg, u);
-    if (VEC == 4) {
-      *reinterpret_cast<uint4 *>(p) = make_uint4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
-    } else {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) p[k] = v[k];
-    }
-  }
-};
-
-// All sub-items of one operand: a shared-memory register, the accumulator (the previous op's
-// result, held in hardware registers), or an immediate.  The source is decoded once per op.
-template <int VEC, int U>
-__device__ __forceinline__ void vm_fetch(const tsb_op &op, int which, const VmRegs<VEC, U> &R,
-                                         const unsigned (&acc)[U][VEC], unsigned (&v)[U][VEC]) {
-  if (which == TSB_REG_ACC) {
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) v[u][k] = acc[u][k];
-  } else if (which == TSB_REG_IMM) {
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) v[u][k] = op.imm2;
-  } else {
-#pragma unroll
-    for (int u = 0; u < U; ++u) R.get(which, u, v[u]);
-  }
-}
-
-template <int OPC, int VEC, int U>
-__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R, unsigned (&acc)[U][VEC]) {
-  unsigned a[U][VEC], b[U][VEC], c[U][VEC];
-  vm_fetch<VEC, U>(op, op.a, R, acc, a);
-  if (alu_arity<OPC>() >= 2) vm_fetch<VEC, U>(op, op.b, R, acc, b);
-  if (alu_arity<OPC>() >= 3) vm_fetch<VEC, U>(op, op.c, R, acc, c);
-#pragma unroll
-  for (int u = 0; u < U; ++u)
-#pragma unroll
-    for (int v = 0; v < VEC; ++v)
-      acc[u][v] = alu_op<OPC, false>(op, a[u][v], alu_arity<OPC>() >= 2 ? b[u][v] : 0u,
-                                     alu_arity<OPC>() >= 3 ? c[u][v] : 0u);
-  if (alu_rounds<OPC>() && op.type != TSB_F32) {  // 16-bit float ops: one decision per op, not per lane
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) acc[u][v] = __float_as_uint(round_to(__uint_as_float(acc[u][v]), op.type));
-  }
-  if (op.dst >= 0) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) R.put(op.dst, u, acc[u]);
-  }
-}
-
-// ld(access, u, regs) / st(access, u, regs) address sub-item u; inactive sub-items load zeros and store nothing
-// ldx / stx: the same with a per-lane element index added to the address and / or a per-lane
-// mask bit (flags MEM_INDEX, MEM_MASK): the data-dependent accesses of gather / scatter kernels.
-template <int VEC, int U, typename LoadFn, typename StoreFn, typename LoadXFn, typename StoreXFn>
-__device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC, U> R, LoadFn ld, StoreFn st,
-                                        LoadXFn ldx, StoreXFn stx) {
-  unsigned acc[U][VEC];
-#pragma unroll
-  for (int u = 0; u < U; ++u)
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) acc[u][v] = 0u;
-  for (int k = 0; k < n_ops; ++k) {
-    const tsb_op &op = ops[k];
-    switch (op.opcode) {
-      case TSB_OP_LOAD:
-        if (op.imm & (MEM_INDEX | MEM_MASK)) {
-          unsigned ix[U][VEC], mk[U][VEC];
-          if (op.imm & MEM_INDEX) vm_fetch<VEC, U>(op, op.b, R, acc, ix);
-          if (op.imm & MEM_MASK) vm_fetch<VEC, U>(op, op.c, R, acc, mk);
-#pragma unroll
-          for (int u = 0; u < U; ++u) ldx(op.a, u, op.imm, ix[u], mk[u], acc[u]);
-        } else {
-#pragma unroll
-          for (int u = 0; u < U; ++u) ld(op.a, u, acc[u]);  // all loads issued before the first use
-        }
-        if (op.dst >= 0) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) R.put(op.dst, u, acc[u]);
-        }
-        break;
-      case TSB_OP_STORE:
-#pragma unroll
-        {
-          unsigned t[U][VEC];
-          vm_fetch<VEC, U>(op, op.b, R, acc, t);
-          if (op.imm & (MEM_INDEX | MEM_MASK)) {
-            unsigned ix[U][VEC], mk[U][VEC];
-            if (op.imm & MEM_INDEX) vm_fetch<VEC, U>(op, op.c, R, acc, ix);
-            if (op.imm & MEM_MASK) vm_fetch<VEC, U>(op, op.dst, R, acc, mk);
-#pragma unroll
-            for (int u = 0; u < U; ++u) stx(op.a, u, op.imm, ix[u], mk[u], t[u]);
-          } else {
-#pragma unroll
-            for (int u = 0; u < U; ++u) st(op.a, u, t[u]);
-          }
-        }
-        break;
-      case TSB_OP_CONST:
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) acc[u][v] = op.imm;
-          if (op.dst >= 0) R.put(op.dst, u, acc[u]);
-        }
-        break;
-#define TSB_VM_CASE(O) \
-  case O: vm_alu<O, VEC, U>(op, R, acc); break;
-        TSB_ALU_OPCODES(TSB_VM_CASE)
-#undef TSB_VM_CASE
-      default: break;
-    }
-  }
-}
 
 template <int VEC, int U>
 __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwParams P) {
@@ -193,20 +45,26 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
           i0 = l >> sh0;
           return itm < items;
         };
-        vm_exec<VEC, U>(
+        vm_exec<VEC, U, true>(
             P.ops, P.n_ops, R,
-            [&](int a, int u, unsigned(&r)[VEC]) {
-              int i0, i1, i2;
-              if (coords(u, i0, i1, i2)) {
-                load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
-              } else {
+            [&](int a, unsigned(&r)[U][VEC]) {
 #pragma unroll
-                for (int v = 0; v < VEC; ++v) r[v] = 0u;
+              for (int u = 0; u < U; ++u) {
+                int i0, i1, i2;
+                if (coords(u, i0, i1, i2)) {
+                  load_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r[u]);
+                } else {
+#pragma unroll
+                  for (int v = 0; v < VEC; ++v) r[u][v] = 0u;
+                }
               }
             },
-            [&](int a, int u, const unsigned(&r)[VEC]) {
-              int i0, i1, i2;
-              if (coords(u, i0, i1, i2)) store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r);
+            [&](int a, const unsigned(&r)[U][VEC]) {
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                int i0, i1, i2;
+                if (coords(u, i0, i1, i2)) store_vec<VEC>(P.acc[a], st[a], i0, i1, i2, r[u]);
+              }
             },
             [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC], unsigned(&r)[VEC]) {
               int i0, i1, i2;
@@ -228,96 +86,6 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
   }
 }
 
-// Packed form of the blocked VM kernel for programs of at most 1024 lane-vectors.  A program of
-// `items` lane-vectors is shared by G = items / U consecutive threads, each carrying U vectors G
-// apart (consecutive threads touch consecutive vectors); programs are dealt to thread groups in
-// the walk order of the launch, so a CTA of 256 threads works on 256 / G programs at once and
-// small blocks still fill it.  The access state of a pass's programs is derived once per
-// (program, access) and shared through shared memory when that fits the CTA (one barrier pair per
-// pass); otherwise each thread derives it itself when the body reaches the load or store.
-template <bool LOOPS>
-__global__ void __launch_bounds__(256, 4) ew_vm_packed_kernel(const __grid_constant__ EwParams P, int lg_g) {
-  constexpr int VEC = 4, U = 4;
-  extern __shared__ __align__(16) unsigned vm_smem[];
-  // access state of the programs of one pass, derived once per (program, access) by one thread each
-  // and read by the program's threads; used when programs-per-pass x accesses fits the CTA
-  __shared__ ProgState shared_state[256];
-  const VmRegs<VEC, U> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
-  const int G = 1 << lg_g;
-  const int per_pass = (int)blockDim.x >> lg_g;  // programs a CTA works on at once
-  const bool share = per_pass * P.n_acc <= 256;
-  const int sh1 = P.lg[2], sh0 = P.lg[2] + P.lg[1];
-  const long long n_prog = P.pid_hi - P.pid_lo;
-  const long long n_threads = n_prog << lg_g;
-  grid_dependency_wait();
-  grid_launch_dependents();
-  for (long long base = (long long)blockIdx.x * blockDim.x; base < n_threads; base += (long long)gridDim.x * blockDim.x) {
-    const long long g = base + threadIdx.x;
-    const bool live = g < n_threads;
-    const int within = (int)(g & (G - 1));
-    const int slot = (int)threadIdx.x >> lg_g;
-    long long px = 0, py = 0, pz = 0;
-    if (live && !share) split_pid(P.grid, P.order, P.pid_lo + (g >> lg_g), px, py, pz);
-    for (long long q = 0; q < (LOOPS ? P.total_trips : 1); ++q) {
-      int it[TSB_MAX_LOOPS] = {0, 0, 0, 0};
-      if (LOOPS) loop_counters(P, q, it);
-      if (LOOPS || share) {
-        // later iterations of a program see the stores of earlier ones (same CTA); the previous
-        // pass's shared state is no longer read
-        if (LOOPS) __threadfence_block();
-        __syncthreads();
-      }
-      if (share) {
-        const int t = (int)threadIdx.x;
-        if (t < per_pass * P.n_acc) {
-          const int sl = t / P.n_acc, a = t - sl * P.n_acc;
-          const long long prog = (base >> lg_g) + sl;
-          if (prog < n_prog) {
-            long long qx, qy, qz;
-            split_pid(P.grid, P.order, P.pid_lo + prog, qx, qy, qz);
-            if (LOOPS) program_state_loops(P.acc[a], P.size, qx, qy, qz, it, shared_state[t]);
-            else program_state(P.acc[a], P.size, qx, qy, qz, shared_state[t]);
-          }
-        }
-        __syncthreads();
-      }
-      if (!live) continue;
-      auto state = [&](int a, ProgState &ps) {
-        if (share) ps = shared_state[slot * P.n_acc + a];
-        else if (LOOPS) program_state_loops(P.acc[a], P.size, px, py, pz, it, ps);
-        else program_state(P.acc[a], P.size, px, py, pz, ps);
-      };
-      auto lane0 = [&](int u) { return (within + u * G) * VEC; };
-      // the access state is fetched once per op (for sub-item 0) and kept for the other sub-items
-      ProgState ps;
-      vm_exec<VEC, U>(
-          P.ops, P.n_ops, R,
-          [&](int a, int u, unsigned(&r)[VEC]) {
-            if (u == 0) state(a, ps);
-            const int l = lane0(u);
-            load_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r);
-          },
-          [&](int a, int u, const unsigned(&r)[VEC]) {
-            if (u == 0) state(a, ps);
-            const int l = lane0(u);
-            store_vec<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1), r);
-          },
-          [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC], unsigned(&r)[VEC]) {
-            if (u == 0) state(a, ps);
-            const int l = lane0(u);
-            load_vec_indirect<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1),
-                                   flags & MEM_INDEX, flags & MEM_MASK, ix, mk, r);
-          },
-          [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC],
-              const unsigned(&r)[VEC]) {
-            if (u == 0) state(a, ps);
-            const int l = lane0(u);
-            store_vec_indirect<VEC>(P.acc[a], ps, l >> sh0, (l >> sh1) & (P.size[1] - 1), l & (P.size[2] - 1),
-                                    flags & MEM_INDEX, flags & MEM_MASK, ix, mk, r);
-          });
-    }
-  }
-}
 
 // ---- fast body: out = binop(load0, load1), all fp32 ---------------------------
 // Two programs per CTA iteration so that each thread has four 16-byte loads in
@@ -546,19 +314,25 @@ __global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__
   const long long n_vec = (P.g_hi - P.g_lo) >> 2;
   const long long step = (long long)gridDim.x * blockDim.x * FLAT_VM_U;
   for (long long v0 = (long long)blockIdx.x * blockDim.x * FLAT_VM_U + threadIdx.x; v0 < n_vec; v0 += step) {
-    vm_exec<4, FLAT_VM_U>(
+    vm_exec<4, FLAT_VM_U, false>(
         P.ops, P.n_ops, R,
-        [&](int a, int u, unsigned(&r)[4]) {
-          const long long v = v0 + (long long)u * blockDim.x;
-          if (v < n_vec) {
-            flat_load(P.acc[a], P.g_lo + v * 4, r);
-          } else {
-            r[0] = r[1] = r[2] = r[3] = 0u;
+        [&](int a, unsigned(&r)[FLAT_VM_U][4]) {
+#pragma unroll
+          for (int u = 0; u < FLAT_VM_U; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < n_vec) {
+              flat_load(P.acc[a], P.g_lo + v * 4, r[u]);
+            } else {
+              r[u][0] = r[u][1] = r[u][2] = r[u][3] = 0u;
+            }
           }
         },
-        [&](int a, int u, const unsigned(&r)[4]) {
-          const long long v = v0 + (long long)u * blockDim.x;
-          if (v < n_vec) flat_store(P.acc[a], P.g_lo + v * 4, r);
+        [&](int a, const unsigned(&r)[FLAT_VM_U][4]) {
+#pragma unroll
+          for (int u = 0; u < FLAT_VM_U; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v < n_vec) flat_store(P.acc[a], P.g_lo + v * 4, r[u]);
+          }
         },
         [&](int, int, unsigned, const unsigned(&)[4], const unsigned(&)[4], unsigned(&)[4]) {},
         [&](int, int, unsigned, const unsigned(&)[4], const unsigned(&)[4], const unsigned(&)[4]) {});
@@ -833,22 +607,9 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     return TSB_OK;
   }
   if (vec == 4 && items >= 4 && items <= 1024) {
-    // packed form: items / 4 threads per program, 256 / that many programs per CTA pass
-    int lg_g = 0;
-    while ((4 << (lg_g + 1)) <= items) ++lg_g;  // G = items / 4, at most 256
-    const size_t smem = (size_t)regs_used * 4 * 4 * 256 * sizeof(unsigned);
-    if (smem <= 200 * 1024) {
-      static SmemLimit lim_p0, lim_p1;
-      TSB_CUDA_OK(allow_dynamic_smem(ew_vm_packed_kernel<false>, 200 * 1024, lim_p0));
-      TSB_CUDA_OK(allow_dynamic_smem(ew_vm_packed_kernel<true>, 200 * 1024, lim_p1));
-      const long long n_thr = n_prog << lg_g;
-      long long ctas = (n_thr + 255) / 256;
-      const long long cap = (long long)sm_count() * 4 * 8;
-      if (ctas > cap) ctas = cap;
-      if (P.n_loops) TSB_CUDA_OK(launch_pdl(ew_vm_packed_kernel<true>, dim3((unsigned)ctas), dim3(256), smem, s, P, lg_g));
-      else TSB_CUDA_OK(launch_pdl(ew_vm_packed_kernel<false>, dim3((unsigned)ctas), dim3(256), smem, s, P, lg_g));
-      return TSB_OK;
-    }
+    // packed form: items / 4 threads per program, several programs per CTA
+    rc = launch_ew_packed(P, items, regs_used, s);
+    if (rc != TSB_ERR_UNSUPPORTED) return rc;
   }
   // four lane-vectors per thread when the block is large enough to keep at least a warp busy
   const int U = (vec == 4 && items >= 128) ? 4 : 1;

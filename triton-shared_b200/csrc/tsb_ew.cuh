@@ -111,6 +111,9 @@ __device__ __forceinline__ void flat_store(const FlatAcc &A, long long g, const 
     if (g + k < A.limit) st_elem(p + k * A.esize, A.dtype, in[k]);
 }
 
+// tsb_ew_packed.cu
+int launch_ew_packed(const EwParams &P, int items, int regs_used, cudaStream_t s);
+
 constexpr int FLAT_VM_U = 4;  // lane-vectors per thread of the flat VM kernel
 
 }  // namespace tsb

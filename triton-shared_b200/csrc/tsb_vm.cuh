@@ -323,6 +323,8 @@ __device__ __forceinline__ void program_state_loops(const DAcc &A, const int siz
   }
 }
 
+// Plain (coherent) loads: a later loop iteration, or a later op of the same body, may read what an
+// earlier one stored.
 template <int VEC>
 __device__ __forceinline__ void load_vec(const DAcc &A, const ProgState &s, int i0, int i1, int i2,
                                          unsigned (&out)[VEC]) {
@@ -355,14 +357,14 @@ __device__ __forceinline__ void load_vec(const DAcc &A, const ProgState &s, int 
   if (VEC == 4 && A.vec_ok && outer && i2 + VEC <= s.dim[2]) {
     const char *p = A.base + e * A.esize;
     if (A.esize == 4) {
-      uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+      uint4 v = *reinterpret_cast<const uint4 *>(p);
       out[0] = v.x; out[1 % VEC] = v.y; out[2 % VEC] = v.z; out[3 % VEC] = v.w;
     } else if (A.esize == 2) {
-      uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
+      uint2 v = *reinterpret_cast<const uint2 *>(p);
       out[0] = v.x & 0xffffu; out[1 % VEC] = v.x >> 16; out[2 % VEC] = v.y & 0xffffu; out[3 % VEC] = v.y >> 16;
       raw_to_reg<VEC>(A.dtype, out);
     } else {
-      unsigned v = __ldg(reinterpret_cast<const unsigned *>(p));
+      unsigned v = *reinterpret_cast<const unsigned *>(p);
 #pragma unroll
       for (int k = 0; k < VEC; ++k) out[k] = (v >> (8 * k)) & 0xffu;
       raw_to_reg<VEC>(A.dtype, out);
@@ -449,10 +451,10 @@ __device__ __forceinline__ void load_vec_indirect(const DAcc &A, const ProgState
     const char *p = A.base + (e + (has_index ? (long long)(int)index[0] : 0ll)) * A.esize;
     if (same && all && ((uintptr_t)p % (4u * A.esize)) == 0) {
       if (A.esize == 4) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint4 v = *reinterpret_cast<const uint4 *>(p);
         out[0] = v.x; out[1 % VEC] = v.y; out[2 % VEC] = v.z; out[3 % VEC] = v.w;
       } else {
-        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
+        const uint2 v = *reinterpret_cast<const uint2 *>(p);
         out[0] = v.x & 0xffffu; out[1 % VEC] = v.x >> 16; out[2 % VEC] = v.y & 0xffffu; out[3 % VEC] = v.y >> 16;
       }
       raw_to_reg<VEC>(A.dtype, out);
@@ -500,6 +502,134 @@ __device__ __forceinline__ void store_vec_indirect(const DAcc &A, const ProgStat
     if (A.n_wrap) ek += wrap_addend(A, s, i0, i1, i2 + k);
     if (has_index) ek += (long long)(int)index[k];
     st_elem(A.base + ek * A.esize, A.dtype, in[k]);
+  }
+}
+
+// ---- lean accessors ------------------------------------------------------------
+// The common case of an access (memory load or store, no wrap terms, contiguous innermost dim with
+// aligned 4-lane vectors, in-block offsets that fit 32 bits) in 32 bytes, so that a kernel can keep
+// it in shared memory and address a whole-vector sub-item with a handful of 32-bit instructions.
+// A body whose accesses are all of this kind runs a kernel variant that holds only these paths.
+struct LeanAcc {
+  char *base;
+  int s0, s1;      // element strides of dims 0 and 1 (dim 2 has stride 1)
+  unsigned other;  // fill value in register representation (0 when the access has none)
+  unsigned char esize, dtype, fast, pad_;
+  unsigned pad2_[2];
+};
+static_assert(sizeof(LeanAcc) == 32, "LeanAcc is read as two 16-byte words");
+
+__host__ __device__ inline bool lean_ok(const DAcc &A, const int size[3]) {
+  const long long a0 = A.stride[0] < 0 ? -A.stride[0] : A.stride[0];
+  const long long a1 = A.stride[1] < 0 ? -A.stride[1] : A.stride[1];
+  const bool fits = a0 < (1ll << 31) && a1 < (1ll << 31) &&
+                    (size[0] - 1) * a0 + (size[1] - 1) * a1 + size[2] < (1ll << 31);
+  return A.kind < 2 && !A.n_wrap && A.vec_ok && A.esize <= 4 && fits;
+}
+
+__device__ __forceinline__ void make_lean(const DAcc &A, const int size[3], LeanAcc &L) {
+  L.base = A.base;
+  L.s0 = (int)A.stride[0];
+  L.s1 = (int)A.stride[1];
+  L.other = A.has_other ? A.other : 0u;
+  L.esize = (unsigned char)A.esize;
+  L.dtype = (unsigned char)A.dtype;
+  L.fast = lean_ok(A, size) ? 1 : 0;
+  L.pad_ = 0;
+  L.pad2_[0] = L.pad2_[1] = 0u;
+}
+
+// All U sub-items of one load of a lean access (lean_ok).  Whole vectors inside the mask are one
+// 16/8/4-byte access each; a ragged sub-item reads its admitted lanes one by one and the others
+// take the fill value.
+template <int U>
+__device__ __forceinline__ void lean_load(const LeanAcc &L, const ProgState &S, const int (&c0)[U],
+                                          const int (&c1)[U], const int (&c2)[U], unsigned (&out)[U][4]) {
+  const int d0 = S.dim[0], d1 = S.dim[1], d2 = S.dim[2];
+  const int es = L.esize;
+  const char *p = L.base + S.off * es;
+  bool ragged = false;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const bool outer = c0[u] < d0 && c1[u] < d1;
+    const char *q = p + (long long)(c0[u] * L.s0 + c1[u] * L.s1 + c2[u]) * es;
+    if (outer && c2[u] + 4 <= d2) {
+      if (es == 4) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(q);
+        out[u][0] = v.x; out[u][1] = v.y; out[u][2] = v.z; out[u][3] = v.w;
+      } else if (es == 2) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(q);
+        out[u][0] = v.x & 0xffffu; out[u][1] = v.x >> 16; out[u][2] = v.y & 0xffffu; out[u][3] = v.y >> 16;
+      } else {
+        const unsigned v = *reinterpret_cast<const unsigned *>(q);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out[u][k] = (v >> (8 * k)) & 0xffu;
+      }
+    } else {
+      ragged = true;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) out[u][k] = (outer && c2[u] + k < d2) ? ld_raw(q + k * es, es) : 0u;
+    }
+  }
+  if (es != 4) {
+    if (L.dtype == TSB_F16) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) raw_to_reg<4>(TSB_F16, out[u]);
+    } else if (L.dtype == TSB_BF16) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) raw_to_reg<4>(TSB_BF16, out[u]);
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) raw_to_reg<4>(L.dtype, out[u]);
+    }
+  }
+  if (ragged) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool outer = c0[u] < d0 && c1[u] < d1;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (!(outer && c2[u] + k < d2)) out[u][k] = L.other;
+    }
+  }
+}
+
+template <int U>
+__device__ __forceinline__ void lean_store(const LeanAcc &L, const ProgState &S, const int (&c0)[U],
+                                           const int (&c1)[U], const int (&c2)[U], const unsigned (&in)[U][4]) {
+  const int d0 = S.dim[0], d1 = S.dim[1], d2 = S.dim[2];
+  const int es = L.esize;
+  char *p = L.base + S.off * es;
+  unsigned h[U][4];
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[u][k] = in[u][k];
+  if (es != 4) {
+    if (L.dtype == TSB_F16) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) reg_to_raw<4>(TSB_F16, h[u]);
+    } else if (L.dtype == TSB_BF16) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) reg_to_raw<4>(TSB_BF16, h[u]);
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) reg_to_raw<4>(L.dtype, h[u]);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (!(c0[u] < d0 && c1[u] < d1)) continue;
+    char *q = p + (long long)(c0[u] * L.s0 + c1[u] * L.s1 + c2[u]) * es;
+    if (c2[u] + 4 <= d2) {
+      if (es == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(h[u][0], h[u][1], h[u][2], h[u][3]);
+      else if (es == 2) *reinterpret_cast<uint2 *>(q) = make_uint2(h[u][0] | (h[u][1] << 16), h[u][2] | (h[u][3] << 16));
+      else *reinterpret_cast<unsigned *>(q) = h[u][0] | (h[u][1] << 8) | (h[u][2] << 16) | (h[u][3] << 24);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (c2[u] + k < d2) st_raw(q + k * es, es, h[u][k]);
+    }
   }
 }
 
@@ -676,6 +806,7 @@ inline int convert_access(const tsb_access *acc, int a, int rank, const int size
   const long long vb = 4ll * es;
   bool ok = vec == 4 && es <= 4 && d.stride[2] == 1 && ((uintptr_t)d.base % vb) == 0 && d.off0 % 4 == 0;
   for (int k = 0; k < 3; ++k) ok = ok && (grid[k] <= 1 || d.off_pid[k] % 4 == 0);
+  for (int l = 0; l < TSB_MAX_LOOPS; ++l) ok = ok && d.off_loop[l] % 4 == 0;
   ok = ok && (size[1] <= 1 || d.stride[1] % 4 == 0) && (size[0] <= 1 || d.stride[0] % 4 == 0);
   ok = ok && !d.wrap_inner && !wrap_unaligned;
   d.vec_ok = ok ? 1 : 0;
