@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtsb200.so")
 STAMP = os.path.join(HERE, "build", "libtsb200.stamp")
 
-SOURCES = ["tsb_api.cu", "tsb_elementwise.cu", "tsb_ew_packed.cu", "tsb_rows.cu", "tsb_reduce.cu", "tsb_gemm.cu", "tsb_gemm2.cu", "tsb_block_program.cu", "tsb_plan.cu"]
+SOURCES = ["tsb_api.cu", "tsb_elementwise.cu", "tsb_ew_packed.cu", "tsb_ew_packed_loops.cu", "tsb_ew_packed_general.cu", "tsb_ew_flat.cu", "tsb_rows.cu", "tsb_reduce.cu", "tsb_gemm.cu", "tsb_gemm2.cu", "tsb_block_program.cu", "tsb_plan.cu"]
 
 # -fmad=false: the reference lowers mul and add as separate linalg ops with no
 # contraction (backend/compiler.py:83-115 has no fast-math or fp-contract flag),

@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(256) ew_vm_kernel(const __grid_constant__ EwPa
           i0 = l >> sh0;
           return itm < items;
         };
-        vm_exec<VEC, U, true>(
+        vm_exec<VEC, U, true, false>(
             P.ops, P.n_ops, R,
             [&](int a, unsigned(&r)[U][VEC]) {
 #pragma unroll
@@ -308,37 +308,6 @@ __global__ void __launch_bounds__(256) ew_flat_binary_f32_kernel(const __grid_co
 }
 
 
-__global__ void __launch_bounds__(256) ew_flat_vm_kernel(const __grid_constant__ FlatParams P) {
-  extern __shared__ __align__(16) unsigned vm_smem[];
-  const VmRegs<4, FLAT_VM_U> R{vm_smem, (int)blockDim.x, (int)threadIdx.x};
-  const long long n_vec = (P.g_hi - P.g_lo) >> 2;
-  const long long step = (long long)gridDim.x * blockDim.x * FLAT_VM_U;
-  for (long long v0 = (long long)blockIdx.x * blockDim.x * FLAT_VM_U + threadIdx.x; v0 < n_vec; v0 += step) {
-    vm_exec<4, FLAT_VM_U, false>(
-        P.ops, P.n_ops, R,
-        [&](int a, unsigned(&r)[FLAT_VM_U][4]) {
-#pragma unroll
-          for (int u = 0; u < FLAT_VM_U; ++u) {
-            const long long v = v0 + (long long)u * blockDim.x;
-            if (v < n_vec) {
-              flat_load(P.acc[a], P.g_lo + v * 4, r[u]);
-            } else {
-              r[u][0] = r[u][1] = r[u][2] = r[u][3] = 0u;
-            }
-          }
-        },
-        [&](int a, const unsigned(&r)[FLAT_VM_U][4]) {
-#pragma unroll
-          for (int u = 0; u < FLAT_VM_U; ++u) {
-            const long long v = v0 + (long long)u * blockDim.x;
-            if (v < n_vec) flat_store(P.acc[a], P.g_lo + v * 4, r[u]);
-          }
-        },
-        [&](int, int, unsigned, const unsigned(&)[4], const unsigned(&)[4], unsigned(&)[4]) {},
-        [&](int, int, unsigned, const unsigned(&)[4], const unsigned(&)[4], const unsigned(&)[4]) {});
-  }
-}
-
 static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int n_ops,
                         const int32_t grid[3], int64_t pid_lo, int64_t pid_hi, EwParams &P,
                         int &vec) {  // on return P.ops / P.n_ops hold the body without its loop ops
@@ -578,15 +547,15 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     if (fast) {
       ew_flat_binary_f32_kernel<<<(unsigned)ctas, 256, 0, s>>>(F);
     } else {
-      const size_t smem = regs_bytes * flat_threads;
-      static SmemLimit lim_flat;
-      if (smem > 48 * 1024) TSB_CUDA_OK(allow_dynamic_smem(ew_flat_vm_kernel, 200 * 1024, lim_flat));
-      ew_flat_vm_kernel<<<(unsigned)ctas, flat_threads, smem, s>>>(F);
+      rc = launch_flat_vm(F, (unsigned)ctas, flat_threads, regs_bytes * flat_threads, s);
+      if (rc != TSB_OK) return rc;
     }
     TSB_LAUNCH_OK("ew_flat_kernel");
     return TSB_OK;
   }
-  if (fast_binary) {
+  // the blocked binary kernel derives its access state per thread: worth it only when a thread
+  // then moves several vectors per program; smaller blocks go to the packed kernel below
+  if (fast_binary && (items > 256 || vec != 4)) {
     long long ctas = (n_prog + 1) / 2;
     if (ctas > max_ctas) ctas = max_ctas;
     if (vec == 4) ew_binary_f32_kernel<4><<<(unsigned)ctas, threads, 0, s>>>(P);

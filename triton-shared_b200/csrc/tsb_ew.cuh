@@ -116,4 +116,7 @@ int launch_ew_packed(const EwParams &P, int items, int regs_used, cudaStream_t s
 
 constexpr int FLAT_VM_U = 4;  // lane-vectors per thread of the flat VM kernel
 
+// tsb_ew_flat.cu
+int launch_flat_vm(const FlatParams &F, unsigned ctas, int threads, size_t smem, cudaStream_t s);
+
 }  // namespace tsb

@@ -65,19 +65,26 @@ __device__ __forceinline__ void vm_fetch(const tsb_op &op, int which, const VmRe
   }
 }
 
+// One ALU op on all sub-items.  The result always lands in `acc`.  Fetching every operand into
+// a register array of its own costs a move per lane and operand wherever the three sources
+// (register file, accumulator, immediate) merge; the cheap unary and binary opcodes are therefore
+// compiled once per combination of sources and compute straight from them.
+// The direct forms are compiled for the cheap opcodes only (FORMS, alu_light): an expensive op
+// gains little from them and its code would be repeated per form.
+template <int OPC>
+__device__ __forceinline__ constexpr bool alu_light() {
+  return OPC == TSB_OP_MOV || OPC == TSB_OP_BITCAST || OPC == TSB_OP_ADDF || OPC == TSB_OP_SUBF ||
+         OPC == TSB_OP_MULF || (OPC >= TSB_OP_MAXNUMF && OPC <= TSB_OP_MINIMUMF) || OPC == TSB_OP_ABSF ||
+         OPC == TSB_OP_NEGF || OPC == TSB_OP_FLOOR || OPC == TSB_OP_CEIL || OPC == TSB_OP_ADDI ||
+         OPC == TSB_OP_SUBI || OPC == TSB_OP_MULI || (OPC >= TSB_OP_MINSI && OPC <= TSB_OP_ABSI) ||
+         OPC == TSB_OP_CMPF || OPC == TSB_OP_CMPI;
+}
+
+// Result handling shared by all forms: 16-bit float ops round once per op, then the optional
+// write to the register file.
 template <int OPC, int VEC, int U>
-__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R, unsigned (&acc)[U][VEC]) {
-  unsigned a[U][VEC], b[U][VEC], c[U][VEC];
-  vm_fetch<VEC, U>(op, op.a, R, acc, a);
-  if (alu_arity<OPC>() >= 2) vm_fetch<VEC, U>(op, op.b, R, acc, b);
-  if (alu_arity<OPC>() >= 3) vm_fetch<VEC, U>(op, op.c, R, acc, c);
-#pragma unroll
-  for (int u = 0; u < U; ++u)
-#pragma unroll
-    for (int v = 0; v < VEC; ++v)
-      acc[u][v] = alu_op<OPC, false>(op, a[u][v], alu_arity<OPC>() >= 2 ? b[u][v] : 0u,
-                                     alu_arity<OPC>() >= 3 ? c[u][v] : 0u);
-  if (alu_rounds<OPC>() && op.type != TSB_F32) {  // 16-bit float ops: one decision per op, not per lane
+__device__ __forceinline__ void vm_alu_finish(const tsb_op &op, const VmRegs<VEC, U> &R, unsigned (&acc)[U][VEC]) {
+  if (alu_rounds<OPC>() && op.type != TSB_F32) {  // one decision per op, not per lane
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -89,12 +96,77 @@ __device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R
   }
 }
 
+// A unary or binary op whose operand sources are known at compile time
+// (0 accumulator, 1 immediate, 2 register file): straight from the sources into the accumulator.
+template <int OPC, int SA, int SB, int VEC, int U>
+__device__ __forceinline__ void vm_alu_direct(const tsb_op &op, const VmRegs<VEC, U> &R, unsigned (&acc)[U][VEC]) {
+  const unsigned imm = op.imm2;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    unsigned x[VEC], y[VEC];
+    if (SA == 2) R.get(op.a, u, x);
+    if (SB == 2) R.get(op.b, u, y);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const unsigned xa = SA == 0 ? acc[u][v] : (SA == 1 ? imm : x[v]);
+      const unsigned yb = SB == 0 ? acc[u][v] : (SB == 1 ? imm : (SB == 2 ? y[v] : 0u));
+      acc[u][v] = alu_op<OPC, false>(op, xa, yb, 0u);
+    }
+  }
+  // The forms of one opcode differ only in where the operands come from; the optimiser would
+  // merge them back into one computation behind per-lane operand selects, which is the cost the
+  // forms exist to avoid.  An empty asm statement per lane is not merged.
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) asm volatile("" : "+r"(acc[u][v]));
+  vm_alu_finish<OPC, VEC, U>(op, R, acc);
+}
+
+template <int OPC, int VEC, int U, bool FORMS>
+__device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R, unsigned (&acc)[U][VEC]) {
+  constexpr int AR = alu_arity<OPC>();
+  if constexpr (FORMS && alu_light<OPC>() && AR <= 2) {
+    const int sa = op.a == TSB_REG_ACC ? 0 : (op.a == TSB_REG_IMM ? 1 : 2);
+    if constexpr (AR == 1) {
+      if (sa == 0) vm_alu_direct<OPC, 0, 3, VEC, U>(op, R, acc);
+      else if (sa == 2) vm_alu_direct<OPC, 2, 3, VEC, U>(op, R, acc);
+      else vm_alu_direct<OPC, 1, 3, VEC, U>(op, R, acc);
+    } else {
+      const int sb = op.b == TSB_REG_ACC ? 0 : (op.b == TSB_REG_IMM ? 1 : 2);
+      switch (sa * 3 + sb) {
+        case 0: vm_alu_direct<OPC, 0, 0, VEC, U>(op, R, acc); break;
+        case 1: vm_alu_direct<OPC, 0, 1, VEC, U>(op, R, acc); break;
+        case 2: vm_alu_direct<OPC, 0, 2, VEC, U>(op, R, acc); break;
+        case 3: vm_alu_direct<OPC, 1, 0, VEC, U>(op, R, acc); break;
+        case 5: vm_alu_direct<OPC, 1, 2, VEC, U>(op, R, acc); break;
+        case 6: vm_alu_direct<OPC, 2, 0, VEC, U>(op, R, acc); break;
+        case 7: vm_alu_direct<OPC, 2, 1, VEC, U>(op, R, acc); break;
+        case 8: vm_alu_direct<OPC, 2, 2, VEC, U>(op, R, acc); break;
+        default: vm_alu_direct<OPC, 1, 1, VEC, U>(op, R, acc); break;
+      }
+    }
+  } else {
+    unsigned a[U][VEC], b[U][VEC], c[U][VEC];
+    vm_fetch<VEC, U>(op, op.a, R, acc, a);
+    if (AR >= 2) vm_fetch<VEC, U>(op, op.b, R, acc, b);
+    if (AR >= 3) vm_fetch<VEC, U>(op, op.c, R, acc, c);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        acc[u][v] = alu_op<OPC, false>(op, a[u][v], AR >= 2 ? b[u][v] : 0u, AR >= 3 ? c[u][v] : 0u);
+    vm_alu_finish<OPC, VEC, U>(op, R, acc);
+  }
+}
+
 // ld(access, regs[U][VEC]) / st(access, regs[U][VEC]) move all sub-items of one access; inactive
 // sub-items load zeros and store nothing
 // ldx / stx (access, u, flags, index, mask, regs): sub-item u with a per-lane element index added to the address and / or a per-lane
 // mask bit (flags MEM_INDEX, MEM_MASK): the data-dependent accesses of gather / scatter kernels.
 // INDIRECT = false compiles the flagged forms out (the flat kernel never has them).
-template <int VEC, int U, bool INDIRECT, typename LoadFn, typename StoreFn, typename LoadXFn, typename StoreXFn>
+// FORMS: see vm_alu.
+template <int VEC, int U, bool INDIRECT, bool FORMS, typename LoadFn, typename StoreFn, typename LoadXFn, typename StoreXFn>
 __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC, U> R, LoadFn ld, StoreFn st,
                                         LoadXFn ldx, StoreXFn stx) {
   unsigned acc[U][VEC];
@@ -145,7 +217,7 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRe
         }
         break;
 #define TSB_VM_CASE(O) \
-  case O: vm_alu<O, VEC, U>(op, R, acc); break;
+  case O: vm_alu<O, VEC, U, FORMS>(op, R, acc); break;
         TSB_ALU_OPCODES(TSB_VM_CASE)
 #undef TSB_VM_CASE
       default: break;
