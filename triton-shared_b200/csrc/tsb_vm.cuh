@@ -549,6 +549,8 @@ __device__ __forceinline__ void lean_load(const LeanAcc &L, const ProgState &S, 
   const int es = L.esize;
   const char *p = L.base + S.off * es;
   bool ragged = false;
+  // raw bits first: one word per lane for 4- and 1-byte elements, two packed words (out[u][0..1])
+  // for 2-byte elements
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const bool outer = c0[u] < d0 && c1[u] < d1;
@@ -559,7 +561,7 @@ __device__ __forceinline__ void lean_load(const LeanAcc &L, const ProgState &S, 
         out[u][0] = v.x; out[u][1] = v.y; out[u][2] = v.z; out[u][3] = v.w;
       } else if (es == 2) {
         const uint2 v = *reinterpret_cast<const uint2 *>(q);
-        out[u][0] = v.x & 0xffffu; out[u][1] = v.x >> 16; out[u][2] = v.y & 0xffffu; out[u][3] = v.y >> 16;
+        out[u][0] = v.x; out[u][1] = v.y;
       } else {
         const unsigned v = *reinterpret_cast<const unsigned *>(q);
 #pragma unroll
@@ -567,21 +569,43 @@ __device__ __forceinline__ void lean_load(const LeanAcc &L, const ProgState &S, 
       }
     } else {
       ragged = true;
+      unsigned r[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) out[u][k] = (outer && c2[u] + k < d2) ? ld_raw(q + k * es, es) : 0u;
+      for (int k = 0; k < 4; ++k) r[k] = (outer && c2[u] + k < d2) ? ld_raw(q + k * es, es) : 0u;
+      if (es == 2) {
+        out[u][0] = r[0] | (r[1] << 16); out[u][1] = r[2] | (r[3] << 16);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out[u][k] = r[k];
+      }
     }
   }
-  if (es != 4) {
+  if (es == 2) {
     if (L.dtype == TSB_F16) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) raw_to_reg<4>(TSB_F16, out[u]);
+      for (int u = 0; u < U; ++u) {  // two lanes per conversion
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&out[u][0]));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&out[u][1]));
+        out[u][0] = __float_as_uint(f0.x); out[u][1] = __float_as_uint(f0.y);
+        out[u][2] = __float_as_uint(f1.x); out[u][3] = __float_as_uint(f1.y);
+      }
     } else if (L.dtype == TSB_BF16) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) raw_to_reg<4>(TSB_BF16, out[u]);
+      for (int u = 0; u < U; ++u) {
+        const unsigned w0 = out[u][0], w1 = out[u][1];
+        out[u][0] = w0 << 16; out[u][1] = w0 & 0xffff0000u; out[u][2] = w1 << 16; out[u][3] = w1 & 0xffff0000u;
+      }
     } else {
 #pragma unroll
-      for (int u = 0; u < U; ++u) raw_to_reg<4>(L.dtype, out[u]);
+      for (int u = 0; u < U; ++u) {
+        const unsigned w0 = out[u][0], w1 = out[u][1];
+        out[u][0] = w0 & 0xffffu; out[u][1] = w0 >> 16; out[u][2] = w1 & 0xffffu; out[u][3] = w1 >> 16;
+        raw_to_reg<4>(L.dtype, out[u]);
+      }
     }
+  } else if (es == 1) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) raw_to_reg<4>(L.dtype, out[u]);
   }
   if (ragged) {
 #pragma unroll
@@ -605,13 +629,24 @@ __device__ __forceinline__ void lean_store(const LeanAcc &L, const ProgState &S,
   for (int u = 0; u < U; ++u)
 #pragma unroll
     for (int k = 0; k < 4; ++k) h[u][k] = in[u][k];
+  // 16-bit floats: two lanes per conversion, already packed (pk[u] holds the four lanes of sub-item u)
+  uint2 pk[U];
+  const bool packed16 = L.dtype == TSB_F16 || L.dtype == TSB_BF16;
   if (es != 4) {
     if (L.dtype == TSB_F16) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) reg_to_raw<4>(TSB_F16, h[u]);
+      for (int u = 0; u < U; ++u) {
+        const __half2 lo = __floats2half2_rn(__uint_as_float(h[u][0]), __uint_as_float(h[u][1]));
+        const __half2 hi = __floats2half2_rn(__uint_as_float(h[u][2]), __uint_as_float(h[u][3]));
+        pk[u] = make_uint2(*reinterpret_cast<const unsigned *>(&lo), *reinterpret_cast<const unsigned *>(&hi));
+      }
     } else if (L.dtype == TSB_BF16) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) reg_to_raw<4>(TSB_BF16, h[u]);
+      for (int u = 0; u < U; ++u) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(__uint_as_float(h[u][0]), __uint_as_float(h[u][1]));
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(__uint_as_float(h[u][2]), __uint_as_float(h[u][3]));
+        pk[u] = make_uint2(*reinterpret_cast<const unsigned *>(&lo), *reinterpret_cast<const unsigned *>(&hi));
+      }
     } else {
 #pragma unroll
       for (int u = 0; u < U; ++u) reg_to_raw<4>(L.dtype, h[u]);
@@ -621,8 +656,12 @@ __device__ __forceinline__ void lean_store(const LeanAcc &L, const ProgState &S,
   for (int u = 0; u < U; ++u) {
     if (!(c0[u] < d0 && c1[u] < d1)) continue;
     char *q = p + (long long)(c0[u] * L.s0 + c1[u] * L.s1 + c2[u]) * es;
+    if (packed16 && c2[u] + 4 > d2) {  // ragged: back to one raw value per lane
+      h[u][0] = pk[u].x & 0xffffu; h[u][1] = pk[u].x >> 16; h[u][2] = pk[u].y & 0xffffu; h[u][3] = pk[u].y >> 16;
+    }
     if (c2[u] + 4 <= d2) {
       if (es == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(h[u][0], h[u][1], h[u][2], h[u][3]);
+      else if (packed16) *reinterpret_cast<uint2 *>(q) = pk[u];
       else if (es == 2) *reinterpret_cast<uint2 *>(q) = make_uint2(h[u][0] | (h[u][1] << 16), h[u][2] | (h[u][3] << 16));
       else *reinterpret_cast<unsigned *>(q) = h[u][0] | (h[u][1] << 8) | (h[u][2] << 16) | (h[u][3] << 24);
     } else {
