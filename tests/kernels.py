@@ -493,3 +493,15 @@ def gather_rows_kernel(x_ptr, idx_ptr, out_ptr, n_rows, n_cols, stride_x, stride
     m = rmask[:, None] & (cols[None, :] < n_cols)
     v = tl.load(x_ptr + idx[:, None] * stride_x + cols[None, :], mask=m, other=0.0)
     tl.store(out_ptr + rows[:, None] * stride_o + cols[None, :], v, mask=m)
+
+
+@triton.jit
+def pad_scale_kernel(x_ptr, b_ptr, out_ptr, n_cols, out_stride, BLOCK: tl.constexpr):
+    """out[row, c] = x[row, c] * 2 + b[c] with masked loads filled by 3; the store is NOT masked, so
+    the padded lanes of the last column block land in the (block-padded) output too."""
+    row = tl.program_id(0)
+    cols = tl.program_id(1) * BLOCK + tl.arange(0, BLOCK)
+    m = cols < n_cols
+    x = tl.load(x_ptr + row * n_cols + cols, mask=m, other=3)
+    b = tl.load(b_ptr + cols, mask=m, other=3)
+    tl.store(out_ptr + row * out_stride + cols, x * 2 + b)

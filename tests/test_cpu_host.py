@@ -477,6 +477,25 @@ def test_mixed_ops_on_host_stand_in():
             assert torch.allclose(got, exp, rtol=tol, atol=tol), name
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int16, torch.uint8], ids=lambda d: str(d)[6:])
+@pytest.mark.parametrize("n_cols", [1000, 1001, 3])
+def test_padded_scale_2d_on_host_stand_in(dtype, n_cols):
+    """The plan of the padded scale kernel (masked loads with a fill, unmasked store) on the host
+    stand-in: the same cases the GPU suite runs through the lean and general accessors."""
+    BLOCK, rows = 256, 5
+    nb = (n_cols + BLOCK - 1) // BLOCK
+    g = torch.Generator().manual_seed(n_cols)
+    x = torch.randint(0, 20, (rows, n_cols), generator=g).to(dtype)
+    b = torch.randint(0, 20, (n_cols,), generator=g).to(dtype)
+    out = torch.full((rows + 1, nb * BLOCK), 99, dtype=dtype)
+    with fake_device():
+        K.pad_scale_kernel[(rows, nb)](x, b, out, n_cols, nb * BLOCK, BLOCK=BLOCK)
+    exp = torch.full((rows, nb * BLOCK), 9, dtype=torch.int64)
+    exp[:, :n_cols] = x.to(torch.int64) * 2 + b.to(torch.int64)
+    assert torch.equal(out[:rows].to(torch.int64), exp)
+    assert torch.all(out[rows] == 99)
+
+
 def test_launch_hooks_are_called():
     """launch_enter_hook / launch_exit_hook around every launch, as the reference launcher does
     (backend/driver.py:197-218 there)."""

@@ -407,3 +407,47 @@ def test_gather_rows_known_answer(drv, dtype, rows, cols, src_rows):
     torch.cuda.synchronize()
     assert torch.equal(out[:rows, :cols], x[idx])
     assert torch.all(out[rows:] == -5.0) and torch.all(out[:, cols:] == -5.0)
+
+
+# ---------------------------------------------------------------- packed VM kernel: accessor modes
+_PAD_DTYPES = [torch.float32, torch.float16, torch.bfloat16, torch.int32, torch.int16, torch.int8, torch.uint8]
+
+
+@pytest.mark.parametrize("dtype", _PAD_DTYPES, ids=lambda d: str(d)[6:])
+@pytest.mark.parametrize("n_cols", [1024, 1000, 1001, 4, 3])
+def test_padded_scale_2d_exact(drv, dtype, n_cols):
+    """x*2 + b over a (row, column block) grid with masked loads filled by 3 and an unmasked store.
+    n_cols a multiple of 4 keeps every vector aligned (lean accessors, ragged last sub-items);
+    odd n_cols makes rows unaligned (general accessors).  Small integers: every type computes exactly."""
+    BLOCK, rows = 256, 37
+    nb = (n_cols + BLOCK - 1) // BLOCK
+    g = torch.Generator().manual_seed(n_cols)
+    x = torch.randint(0, 20, (rows, n_cols), generator=g).to(dtype)
+    b = torch.randint(0, 20, (n_cols,), generator=g).to(dtype)
+    out = torch.full((rows + 1, nb * BLOCK), 99, dtype=dtype, device="cuda")  # one guard row
+    K.pad_scale_kernel[(rows, nb)](x.cuda(), b.cuda(), out, n_cols, nb * BLOCK, BLOCK=BLOCK)
+    torch.cuda.synchronize()
+    exp = torch.full((rows, nb * BLOCK), 3 * 2 + 3, dtype=torch.int64)
+    exp[:, :n_cols] = x.to(torch.int64) * 2 + b.to(torch.int64)
+    assert torch.equal(out[:rows].cpu().to(torch.int64), exp)
+    assert torch.all(out[rows] == 99), "stored outside the grid's blocks"
+    assert _loaded_native()
+
+
+def test_bias_add_beyond_32bit_offsets(drv):
+    """A 2-D body whose element offsets pass 2^31 (and whose byte offsets pass 2^32): program and
+    block offsets are 64-bit, only the offset inside one block is 32-bit."""
+    rows, cols = 66_000, 32_768  # 2.16e9 elements of fp16 = 4.3 GB per tensor
+    x = torch.empty(rows, cols, dtype=torch.float16, device="cuda")
+    x.copy_((torch.arange(rows, device="cuda") % 64).to(torch.float16)[:, None].expand(rows, cols))
+    b = (torch.arange(cols, device="cuda") % 32).to(torch.float16)
+    out = torch.empty_like(x)
+    K.pad_scale_kernel[(rows, cols // 1024)](x, b, out, cols, cols, BLOCK=1024)
+    torch.cuda.synchronize()
+    for r in (0, 1, 65_535, 65_536, rows - 1):  # rows either side of the 2^31-element line
+        exp = (r % 64) * 2.0 + (torch.arange(cols) % 32).to(torch.float32)
+        assert torch.equal(out[r].float().cpu(), exp), r
+    # checksum of the whole result: sum over rows of (2*(r%64)*cols + sum(b))
+    total = out.double().sum().item()
+    want = sum(2.0 * (r % 64) for r in range(rows)) * cols + rows * float((torch.arange(cols) % 32).sum())
+    assert total == want
