@@ -161,6 +161,15 @@ class FakeLib:
                         if o.imm & rt.MEM_MASK:
                             valid = valid & ((regs[o.dst] & 1) != 0)
                         self._store(A, elem, valid, regs[o.b])
+                    elif name == "reduce":
+                        # fold over all lanes of the program (left to right); every lane takes the total
+                        comb = _OPNAME[o.imm]
+                        src = regs[o.a]
+                        op = type("O", (), {"type": o.type, "a": 0, "b": 1, "c": 0, "imm": 0, "imm2": 0})()
+                        tot = src[0:1].copy()
+                        for j in range(1, lanes):
+                            tot = self._alu(comb, op, {0: tot, 1: src[j:j + 1]}, 1)
+                        regs.write(o.dst, np.full(lanes, tot[0], dtype=np.uint32))
                     else:
                         regs.write(o.dst, self._alu(name, o, regs, lanes))
         return 0

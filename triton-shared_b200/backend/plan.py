@@ -494,6 +494,22 @@ class _EwLowering:
                     (kind == "extsi" and n.dtype == "i32" and src.dtype in ("i8", "i16")):
                 return a
             return self.emit("cast", n.dtype, a=a, imm=rt.DTYPES[src.dtype], imm2=mode)
+        if op == "reduce":
+            # a full fold of a 1-D block whose lanes are the whole iteration space: every lane of the
+            # result holds the total (the packed kernel folds across the threads of a program)
+            src, comb = n.args[0], n.attr("comb")
+            lanes = int(np.prod(self.space)) if self.space else 1
+            if len(src.shape) != 1 or dimmap != () or src.shape[0] != lanes or self.space[-1] != lanes:
+                raise UnsupportedTTIR("elementwise family: only full folds of the 1-D block the kernel stores")
+            if lanes % 4 or not 16 <= lanes <= 4096:
+                raise UnsupportedTTIR("elementwise family: a fold needs a block of 16 to 4096 lanes, a multiple of 4")
+            if comb not in ("addf", "mulf", "maxnumf", "minnumf", "maximumf", "minimumf", "addi", "muli", "maxsi",
+                            "minsi", "maxui", "minui", "andi", "ori", "xori"):
+                raise UnsupportedTTIR(f"elementwise family: reduction with combiner {comb}")
+            if type(self) is not _EwLowering:
+                raise UnsupportedTTIR("not an elementwise lowering")
+            a = self.value(src, (len(self.space) - 1,))
+            return self.emit("reduce", n.dtype, a=a, imm=comb)
         raise UnsupportedTTIR(f"operation {op} has no elementwise lowering")
 
     def lane_operands(self, acc: Access, dimmap):
@@ -546,7 +562,7 @@ class _EwLowering:
         consts = {o[2]: o for o in ops if o[0] == "const"}
         marks: Dict[tuple, int] = {}  # (op index, slot) -> ACC / IMM
         for i, o in enumerate(ops):
-            if o[0] in ("store", "cast", "load", "const"):
+            if o[0] in ("store", "cast", "load", "const", "reduce"):
                 continue
             for sl in read_slots(o):
                 if o[sl] in consts and not any(marks.get((i, s2)) == IMM for s2 in read_slots(o)):

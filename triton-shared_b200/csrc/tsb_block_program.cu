@@ -93,48 +93,48 @@ __device__ __forceinline__ void ew_loop(const tsb_op &op, const int lg[3], unsig
   }
 }
 
-__device__ __forceinline__ unsigned combine(int comb, int type, unsigned a, unsigned b) {
-  if (comb >= TSB_OP_ADDF && comb < TSB_OP_EXP)
-    return __float_as_uint(round_to(binf(comb, __uint_as_float(a), __uint_as_float(b)), type));
-  return wrap_to(bini(comb, a, b), type);
-}
-// identity of the combiner (what the reference initialises the accumulator with,
-// ConversionPatterns.hpp:1227-1278)
-__device__ __forceinline__ unsigned combine_identity(int comb) {
-  switch (comb) {
-    case TSB_OP_ADDF: return 0u;
-    case TSB_OP_MULF: return 0x3f800000u;
-    case TSB_OP_MAXNUMF: case TSB_OP_MAXIMUMF: return 0xff800000u;
-    case TSB_OP_MINNUMF: case TSB_OP_MINIMUMF: return 0x7f800000u;
-    case TSB_OP_MULI: return 1u;
-    case TSB_OP_ANDI: return 0xffffffffu;
-    case TSB_OP_MAXSI: return 0x80000000u;
-    case TSB_OP_MINSI: return 0x7fffffffu;
-    case TSB_OP_MINUI: return 0xffffffffu;
-  }
-  return 0u;  // addi, ori, xori, maxui
-}
-
 __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_constant__ BpParams P) {
   extern __shared__ __align__(16) unsigned bp_smem[];
   __shared__ unsigned red[BP_THREADS / 32];
+  // The op list and the register tables are read once per op by every thread: from shared memory
+  // (indexed reads of kernel parameters were the busiest pipe of this kernel).
+  __shared__ __align__(16) tsb_op s_ops[TSB_MAX_OPS];
+  __shared__ int s_mask[BP_MAX_REGS], s_off[BP_MAX_REGS], s_n[BP_MAX_REGS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int k = tid; k < P.n_ops; k += BP_THREADS) s_ops[k] = P.ops[k];
+  if (tid < BP_MAX_REGS) {
+    s_mask[tid] = P.reg_mask[tid];
+    s_off[tid] = P.reg_off[tid];
+    s_n[tid] = P.reg_n[tid];
+  }
+  __syncthreads();
   for (long long prog = P.pid_lo + blockIdx.x; prog < P.pid_hi; prog += gridDim.x) {
     long long px, py, pz;
     split_pid(P.grid, P.order, prog, px, py, pz);
+    // loop state in registers: the slot is selected by comparison, never by indexing
     int it[TSB_MAX_LOOPS] = {0, 0, 0, 0}, trip[TSB_MAX_LOOPS] = {0, 0, 0, 0}, begin[TSB_MAX_LOOPS] = {0, 0, 0, 0};
     for (int k = 0; k < P.n_ops;) {
-      const tsb_op &op = P.ops[k];
+      const tsb_op op = s_ops[k];
       // loops: uniform control flow, the same for every thread of the CTA
       if (op.opcode == TSB_OP_LOOP_BEGIN) {
-        it[op.a] = 0;
-        trip[op.a] = (int)op.imm;
-        begin[op.a] = k + 1;
-        k = trip[op.a] > 0 ? k + 1 : op.b;
+        int next = k + 1;
+#pragma unroll
+        for (int l = 0; l < TSB_MAX_LOOPS; ++l)
+          if (l == op.a) {
+            it[l] = 0;
+            trip[l] = (int)op.imm;
+            begin[l] = k + 1;
+            if (trip[l] <= 0) next = op.b;
+          }
+        k = next;
         continue;
       }
       if (op.opcode == TSB_OP_LOOP_END) {
-        k = (++it[op.a] < trip[op.a]) ? begin[op.a] : k + 1;
+        int next = k + 1;
+#pragma unroll
+        for (int l = 0; l < TSB_MAX_LOOPS; ++l)
+          if (l == op.a && ++it[l] < trip[l]) next = begin[l];
+        k = next;
         continue;
       }
       ++k;
@@ -143,15 +143,15 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         const DAcc &A = P.acc[op.a];
         ProgState st;
         program_state_loops(A, P.size, px, py, pz, it, st);
-        const int m = P.reg_mask[op.dst];
-        unsigned *dst = bp_smem + P.reg_off[op.dst];
+        const int m = s_mask[op.dst];
+        unsigned *dst = bp_smem + s_off[op.dst];
         if (op.imm2 & 3u) {
           // data-dependent access (flags in imm2: 1 = per-lane index in register b, 2 = per-lane mask
           // in register c): one element per thread and step
           const bool hi = op.imm2 & 1u, hm = op.imm2 & 2u;
-          const unsigned *ri = bp_smem + P.reg_off[hi ? op.b : 0], *rm = bp_smem + P.reg_off[hm ? op.c : 0];
-          const int mi = P.reg_mask[hi ? op.b : 0], mm = P.reg_mask[hm ? op.c : 0];
-          for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
+          const unsigned *ri = bp_smem + s_off[hi ? op.b : 0], *rm = bp_smem + s_off[hm ? op.c : 0];
+          const int mi = s_mask[hi ? op.b : 0], mm = s_mask[hm ? op.c : 0];
+          for (int e = tid; e < s_n[op.dst]; e += BP_THREADS) {
             int i0, i1, i2;
             reg_coords(P.lg, m, e, i0, i1, i2);
             const unsigned ix[1] = {hi ? ri[reg_index(P.lg, mi, i0, i1, i2)] : 0u};
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
           }
         } else if ((m & 4) && (P.size[2] & 3) == 0) {
           // 4-lane vectors along the innermost dim, four independent loads in flight per thread
-          const int n4 = P.reg_n[op.dst] >> 2;
+          const int n4 = s_n[op.dst] >> 2;
           for (int e0 = tid; e0 < n4; e0 += BP_THREADS * 4) {
             unsigned v[4][4];
 #pragma unroll
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
             }
           }
         } else {
-          for (int e = tid; e < P.reg_n[op.dst]; e += BP_THREADS) {
+          for (int e = tid; e < s_n[op.dst]; e += BP_THREADS) {
             int i0, i1, i2;
             reg_coords(P.lg, m, e, i0, i1, i2);
             unsigned v[1];
@@ -194,14 +194,14 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         ProgState st;
         program_state_loops(A, P.size, px, py, pz, it, st);
         const int m = (int)op.imm;  // dims the store extends along
-        const int ms = P.reg_mask[op.b];
-        const unsigned *src = bp_smem + P.reg_off[op.b];
+        const int ms = s_mask[op.b];
+        const unsigned *src = bp_smem + s_off[op.b];
         const int n = ((m & 1) ? P.size[0] : 1) * ((m & 2) ? P.size[1] : 1) * ((m & 4) ? P.size[2] : 1);
         if (op.imm2 & 3u) {
           // data-dependent store: per-lane index in register c, per-lane mask in register dst
           const bool hi = op.imm2 & 1u, hm = op.imm2 & 2u;
-          const unsigned *ri = bp_smem + P.reg_off[hi ? op.c : 0], *rm = bp_smem + P.reg_off[hm ? op.dst : 0];
-          const int mi = P.reg_mask[hi ? op.c : 0], mm = P.reg_mask[hm ? op.dst : 0];
+          const unsigned *ri = bp_smem + s_off[hi ? op.c : 0], *rm = bp_smem + s_off[hm ? op.dst : 0];
+          const int mi = s_mask[hi ? op.c : 0], mm = s_mask[hm ? op.dst : 0];
           for (int e = tid; e < n; e += BP_THREADS) {
             int i0, i1, i2;
             reg_coords(P.lg, m, e, i0, i1, i2);
@@ -230,15 +230,15 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         // (dst, c) = (value, index) of the extreme element along dim imm2; one warp per output
         const int d = (int)op.imm2;
         const bool want_max = op.imm != 0;
-        const int mv = P.reg_mask[op.a], mi = P.reg_mask[op.b], md = P.reg_mask[op.dst];
-        const unsigned *vsrc = bp_smem + P.reg_off[op.a], *isrc = bp_smem + P.reg_off[op.b];
-        unsigned *vdst = bp_smem + P.reg_off[op.dst], *idst = bp_smem + P.reg_off[op.c];
+        const int mv = s_mask[op.a], mi = s_mask[op.b], md = s_mask[op.dst];
+        const unsigned *vsrc = bp_smem + s_off[op.a], *isrc = bp_smem + s_off[op.b];
+        unsigned *vdst = bp_smem + s_off[op.dst], *idst = bp_smem + s_off[op.c];
         const int len = P.size[d];
         // a over b iff a is strictly better, or equal with the smaller index (the region of tl.argmax / tl.argmin)
         auto better = [&](float va, int ia, float vb, int ib) {
           return (want_max ? va > vb : va < vb) || (va == vb && ia < ib);
         };
-        for (int o = warp; o < P.reg_n[op.dst]; o += BP_THREADS / 32) {
+        for (int o = warp; o < s_n[op.dst]; o += BP_THREADS / 32) {
           int c[3];
           reg_coords(P.lg, md, o, c[0], c[1], c[2]);
           // the reference folds from (-inf | +inf, -1): an element replaces the running pair only if it is
@@ -267,11 +267,11 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
         // dst = inclusive running combination of src along dim imm2 (cumulative sum): one warp per
         // line, 32 elements per step with a shuffle scan, the running total carried between steps
         const int d = (int)op.imm2, comb = (int)op.imm;
-        const int m = P.reg_mask[op.a];
-        const unsigned *src = bp_smem + P.reg_off[op.a];
-        unsigned *dst = bp_smem + P.reg_off[op.dst];
+        const int m = s_mask[op.a];
+        const unsigned *src = bp_smem + s_off[op.a];
+        unsigned *dst = bp_smem + s_off[op.dst];
         const int len = (m & (1 << d)) ? P.size[d] : 1;
-        const int lines = P.reg_n[op.a] / len;
+        const int lines = s_n[op.a] / len;
         const int md = m & ~(1 << d);  // coordinates of a line: the register's dims without the scanned one
         for (int o = warp; o < lines; o += BP_THREADS / 32) {
           int c[3];
@@ -295,11 +295,11 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
       } else if (op.opcode == TSB_OP_REDUCE) {
         // dst = fold of src along dim imm2 with combiner imm; one warp per output element
         const int d = (int)op.imm2, comb = (int)op.imm;
-        const int ms = P.reg_mask[op.a], md = P.reg_mask[op.dst];
-        const unsigned *src = bp_smem + P.reg_off[op.a];
-        unsigned *dst = bp_smem + P.reg_off[op.dst];
+        const int ms = s_mask[op.a], md = s_mask[op.dst];
+        const unsigned *src = bp_smem + s_off[op.a];
+        unsigned *dst = bp_smem + s_off[op.dst];
         const int len = P.size[d];
-        const int n_out = P.reg_n[op.dst];
+        const int n_out = s_n[op.dst];
         if (n_out < BP_THREADS / 32) {
           // few outputs (a 1-D block folded to a scalar): the whole CTA works on each of them
           for (int o = 0; o < n_out; ++o) {
@@ -336,11 +336,14 @@ __global__ void __launch_bounds__(BP_THREADS) block_program_kernel(const __grid_
           }
         }
       } else {
-        const int md = P.reg_mask[op.dst];
-        unsigned *dst = bp_smem + P.reg_off[op.dst];
-        const int ma = P.reg_mask[op.a], mb = P.reg_mask[op.b], mc = P.reg_mask[op.c];
-        const unsigned *ra = bp_smem + P.reg_off[op.a], *rb = bp_smem + P.reg_off[op.b], *rc = bp_smem + P.reg_off[op.c];
-        const int n = P.reg_n[op.dst];
+        const int md = s_mask[op.dst];
+        unsigned *dst = bp_smem + s_off[op.dst];
+        // operand fields an op does not use may hold anything: keep the table reads in range
+        const int qa = (unsigned)op.a < BP_MAX_REGS ? op.a : 0, qb = (unsigned)op.b < BP_MAX_REGS ? op.b : 0,
+                  qc = (unsigned)op.c < BP_MAX_REGS ? op.c : 0;
+        const int ma = s_mask[qa], mb = s_mask[qb], mc = s_mask[qc];
+        const unsigned *ra = bp_smem + s_off[qa], *rb = bp_smem + s_off[qb], *rc = bp_smem + s_off[qc];
+        const int n = s_n[op.dst];
         if (op.opcode == TSB_OP_CONST) {
           for (int e = tid; e < n; e += BP_THREADS) dst[e] = op.imm;
         } else {

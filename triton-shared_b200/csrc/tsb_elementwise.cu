@@ -370,8 +370,8 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
     const tsb_op &o = ops[k];
     P.ops[k] = o;
     const bool is_mem = o.opcode == TSB_OP_LOAD || o.opcode == TSB_OP_STORE;
-    if (o.opcode == TSB_OP_LOOP_BEGIN || o.opcode == TSB_OP_LOOP_END || o.opcode == TSB_OP_REDUCE ||
-        o.opcode == TSB_OP_ARGREDUCE)
+    if (o.opcode == TSB_OP_LOOP_BEGIN || o.opcode == TSB_OP_LOOP_END || o.opcode == TSB_OP_ARGREDUCE ||
+        o.opcode == TSB_OP_SCAN)
       return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: op %d (opcode %d) is not an elementwise op", k, o.opcode);
     if (is_mem && (o.a < 0 || o.a >= n_acc))
       return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d names access %d of %d", k, o.a, n_acc);
@@ -389,6 +389,16 @@ static int build_params(const tsb_access *acc, int n_acc, const tsb_op *ops, int
         return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d index or mask operand out of range", k);
       if (o.opcode == TSB_OP_STORE && !reg_ok(o.b))
         return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, o.b);
+      continue;
+    }
+    if (o.opcode == TSB_OP_REDUCE) {
+      const int c = (int)o.imm;
+      const bool known = (c >= TSB_OP_ADDF && c <= TSB_OP_MINIMUMF && c != TSB_OP_SUBF && c != TSB_OP_DIVF) ||
+                         c == TSB_OP_ADDI || c == TSB_OP_MULI || (c >= TSB_OP_MINSI && c <= TSB_OP_XORI);
+      if (!known) return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: op %d folds with opcode %d", k, c);
+      if (!reg_ok(o.a) || o.a == TSB_REG_IMM || (o.a == TSB_REG_ACC && k == 0))
+        return fail(TSB_ERR_INVALID, "tsb_elementwise: op %d register %d out of range", k, o.a);
+      P.has_reduce = 1;
       continue;
     }
     const int regs[3] = {o.opcode == TSB_OP_CONST ? 0 : o.a, o.opcode == TSB_OP_CONST ? 0 : o.b,
@@ -523,7 +533,8 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
   int threads = items >= 256 ? 256 : (items >= 128 ? 128 : (items >= 64 ? 64 : 32));
   const long long max_ctas = (long long)sm_count() * (2048 / threads) * 4;
   cudaStream_t s = (cudaStream_t)stream;
-  const bool plain = P.n_loops == 0 && !P.indirect;  // eligible for the flat and the dedicated kernels
+  // eligible for the flat and the dedicated kernels
+  const bool plain = P.n_loops == 0 && !P.indirect && !P.has_reduce;
   bool swapped = false;
   const bool fast_binary = plain && is_fast_binary(acc, ops, n_ops, swapped);
   if (fast_binary && swapped) {  // the fast kernels take ops[0] as the load of operand a
@@ -580,6 +591,8 @@ extern "C" int tsb_elementwise(const tsb_access *acc, int n_acc, const tsb_op *o
     rc = launch_ew_packed(P, items, regs_used, s);
     if (rc != TSB_ERR_UNSUPPORTED) return rc;
   }
+  if (P.has_reduce)  // only the packed kernel's threads know the other threads of their program
+    return fail(TSB_ERR_UNSUPPORTED, "tsb_elementwise: a body with a fold needs blocks of 16 to 4096 lanes, a multiple of 4, and at most 12 live registers");
   // four lane-vectors per thread when the block is large enough to keep at least a warp busy
   const int U = (vec == 4 && items >= 128) ? 4 : 1;
   if (U == 4) {

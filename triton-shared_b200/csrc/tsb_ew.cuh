@@ -18,6 +18,7 @@ struct EwParams {
   int trip[TSB_MAX_LOOPS];
   long long total_trips;     // product of the trip counts
   int indirect;              // some load/store takes a per-lane index or mask operand
+  int has_reduce;            // some op folds a value over all lanes of its program (TSB_OP_REDUCE)
 };
 
 // flags in the imm field of TSB_OP_LOAD / TSB_OP_STORE

@@ -14,6 +14,59 @@ constexpr int PACKED_LEAN_U = 4;  // (program, access) states a CTA holds at a t
 //   PACKED_INDIRECT  PACKED_GENERAL plus data-dependent accesses
 enum { PACKED_LEAN = 0, PACKED_GENERAL = 1, PACKED_INDIRECT = 2 };
 
+// Barrier over the `threads` threads (a multiple of 32) of group `slot` (0..3) of a CTA: a named
+// barrier per group, with the ids written out so that the kernel reserves five barriers, not all 16.
+__device__ __forceinline__ void group_barrier(int slot, int threads) {
+  switch (slot) {
+    case 0: asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory"); break;
+    case 1: asm volatile("bar.sync 2, %0;" ::"r"(threads) : "memory"); break;
+    case 2: asm volatile("bar.sync 3, %0;" ::"r"(threads) : "memory"); break;
+    default: asm volatile("bar.sync 4, %0;" ::"r"(threads) : "memory"); break;
+  }
+}
+
+// One combination of a fold with the combiner known at compile time; NARROW: the type is less than
+// 32 bits wide and every partial result is rounded / wrapped to it.
+template <int COMB, bool NARROW>
+__device__ __forceinline__ unsigned fold2(int ty, unsigned a, unsigned b) {
+  if constexpr (COMB >= TSB_OP_ADDF && COMB < TSB_OP_EXP) {
+    const float r = binf(COMB, __uint_as_float(a), __uint_as_float(b));
+    return __float_as_uint(NARROW ? round_to(r, ty) : r);
+  } else {
+    const unsigned r = bini(COMB, a, b);
+    return NARROW ? wrap_to(r, ty) : r;
+  }
+}
+
+// TSB_OP_REDUCE in the packed kernel: every lane of v := the fold of v over all lanes of the program.
+// This thread's lanes in order, then the G threads of the program: shuffles inside a warp, one
+// partial per warp through shared memory behind a barrier that only the program's own warps join.
+template <int COMB, bool NARROW, int U>
+__device__ __forceinline__ void fold_group(unsigned (&v)[U][4], int ty, int G, int lg_g, int slot, unsigned *s_red) {
+  unsigned r = v[0][0];
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (u | k) r = fold2<COMB, NARROW>(ty, r, v[u][k]);
+  const int lane = (int)threadIdx.x & 31;
+  const int span = G < 32 ? G : 32;  // threads of this program inside the warp
+  const unsigned peers = span == 32 ? 0xffffffffu : (((1u << span) - 1u) << (lane & ~(span - 1)));
+  for (int s2 = span >> 1; s2 > 0; s2 >>= 1) r = fold2<COMB, NARROW>(ty, r, __shfl_xor_sync(peers, r, s2));
+  if (G > 32) {
+    const int warp = (int)threadIdx.x >> 5, first_warp = (slot << lg_g) >> 5, n_warps = G >> 5;
+    if (lane == 0) s_red[warp] = r;
+    group_barrier(slot, G);
+    r = s_red[first_warp];
+    for (int w = 1; w < n_warps; ++w) r = fold2<COMB, NARROW>(ty, r, s_red[first_warp + w]);
+    group_barrier(slot, G);  // partials read before reuse
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[u][k] = r;
+}
+
 // U lane-vectors per thread and 1024 / U threads per CTA.  U = 8 (32 lanes per decoded op, 128
 // registers per thread) measured slower than U = 4 on every body tried: the halved warp count
 // costs more than the shared decode saves.
@@ -25,6 +78,7 @@ __global__ void __launch_bounds__(1024 / U, MODE == PACKED_LEAN ? 3 : 4)
   __shared__ ProgState shared_state[PACKED_STATES];
   // the op list and the compact access descriptors, read from shared memory in the body: indexed
   // reads of kernel parameters (constant bank) are far slower than shared-memory reads
+  __shared__ unsigned s_red[32];  // one partial per warp of the CTA (TSB_OP_REDUCE across warps)
   __shared__ __align__(16) tsb_op s_ops[TSB_MAX_OPS];
   __shared__ __align__(16) LeanAcc s_lean[TSB_MAX_ACCESSES];
   for (int k = (int)threadIdx.x; k < P.n_ops; k += (int)blockDim.x) s_ops[k] = P.ops[k];
@@ -99,6 +153,23 @@ __global__ void __launch_bounds__(1024 / U, MODE == PACKED_LEAN ? 3 : 4)
             [&](int a, int u, unsigned flags, const unsigned(&ix)[VEC], const unsigned(&mk)[VEC],
                 const unsigned(&v)[VEC]) {
               store_vec_indirect<VEC>(P.acc[a], S[a], c0[u], c1[u], c2[u], flags & MEM_INDEX, flags & MEM_MASK, ix, mk, v);
+            },
+            [&](const tsb_op &op, unsigned(&v)[U][VEC]) {
+              const bool narrow = dtype_size(op.type) != 4;
+              switch ((int)op.imm) {  // one decision per op: the fold itself is straight-line code
+#define TSB_FOLD_CASE(C)                                                                   \
+  case C:                                                                                  \
+    if (narrow) fold_group<C, true, U>(v, op.type, G, lg_g, slot, s_red);                  \
+    else fold_group<C, false, U>(v, op.type, G, lg_g, slot, s_red);                        \
+    break;
+                TSB_FOLD_CASE(TSB_OP_ADDF) TSB_FOLD_CASE(TSB_OP_MULF) TSB_FOLD_CASE(TSB_OP_MAXNUMF)
+                TSB_FOLD_CASE(TSB_OP_MINNUMF) TSB_FOLD_CASE(TSB_OP_MAXIMUMF) TSB_FOLD_CASE(TSB_OP_MINIMUMF)
+                TSB_FOLD_CASE(TSB_OP_ADDI) TSB_FOLD_CASE(TSB_OP_MULI) TSB_FOLD_CASE(TSB_OP_MINSI)
+                TSB_FOLD_CASE(TSB_OP_MAXSI) TSB_FOLD_CASE(TSB_OP_MINUI) TSB_FOLD_CASE(TSB_OP_MAXUI)
+                TSB_FOLD_CASE(TSB_OP_ANDI) TSB_FOLD_CASE(TSB_OP_ORI) TSB_FOLD_CASE(TSB_OP_XORI)
+#undef TSB_FOLD_CASE
+                default: break;
+              }
             });
       }
     }

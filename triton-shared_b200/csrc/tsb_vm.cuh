@@ -505,6 +505,29 @@ __device__ __forceinline__ void store_vec_indirect(const DAcc &A, const ProgStat
   }
 }
 
+// ---- combiners of reductions and scans --------------------------------------------
+__device__ __forceinline__ unsigned combine(int comb, int type, unsigned a, unsigned b) {
+  if (comb >= TSB_OP_ADDF && comb < TSB_OP_EXP)
+    return __float_as_uint(round_to(binf(comb, __uint_as_float(a), __uint_as_float(b)), type));
+  return wrap_to(bini(comb, a, b), type);
+}
+// identity of the combiner (what the reference initialises the accumulator with,
+// ConversionPatterns.hpp:1227-1278)
+__device__ __forceinline__ unsigned combine_identity(int comb) {
+  switch (comb) {
+    case TSB_OP_ADDF: return 0u;
+    case TSB_OP_MULF: return 0x3f800000u;
+    case TSB_OP_MAXNUMF: case TSB_OP_MAXIMUMF: return 0xff800000u;
+    case TSB_OP_MINNUMF: case TSB_OP_MINIMUMF: return 0x7f800000u;
+    case TSB_OP_MULI: return 1u;
+    case TSB_OP_ANDI: return 0xffffffffu;
+    case TSB_OP_MAXSI: return 0x80000000u;
+    case TSB_OP_MINSI: return 0x7fffffffu;
+    case TSB_OP_MINUI: return 0xffffffffu;
+  }
+  return 0u;  // addi, ori, xori, maxui
+}
+
 // ---- lean accessors ------------------------------------------------------------
 // The common case of an access (memory load or store, no wrap terms, contiguous innermost dim with
 // aligned 4-lane vectors, in-block offsets that fit 32 bits) in 32 bytes, so that a kernel can keep

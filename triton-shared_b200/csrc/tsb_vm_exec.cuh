@@ -166,9 +166,17 @@ __device__ __forceinline__ void vm_alu(const tsb_op &op, const VmRegs<VEC, U> &R
 // mask bit (flags MEM_INDEX, MEM_MASK): the data-dependent accesses of gather / scatter kernels.
 // INDIRECT = false compiles the flagged forms out (the flat kernel never has them).
 // FORMS: see vm_alu.
-template <int VEC, int U, bool INDIRECT, bool FORMS, typename LoadFn, typename StoreFn, typename LoadXFn, typename StoreXFn>
+// red(op, regs): TSB_OP_REDUCE, every lane of regs := the fold (combiner op.imm) of regs over all
+// lanes of the program; kernels whose threads do not know their program pass vm_no_reduce.
+struct vm_no_reduce {
+  template <int U, int VEC>
+  __device__ __forceinline__ void operator()(const tsb_op &, unsigned (&)[U][VEC]) const {}
+};
+
+template <int VEC, int U, bool INDIRECT, bool FORMS, typename LoadFn, typename StoreFn, typename LoadXFn,
+          typename StoreXFn, typename ReduceFn = vm_no_reduce>
 __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRegs<VEC, U> R, LoadFn ld, StoreFn st,
-                                        LoadXFn ldx, StoreXFn stx) {
+                                        LoadXFn ldx, StoreXFn stx, ReduceFn red = ReduceFn()) {
   unsigned acc[U][VEC];
 #pragma unroll
   for (int u = 0; u < U; ++u)
@@ -206,6 +214,21 @@ __device__ __forceinline__ void vm_exec(const tsb_op *ops, int n_ops, const VmRe
           } else {
             st(op.a, t);
           }
+        }
+        break;
+      case TSB_OP_REDUCE:
+        if (op.a != TSB_REG_ACC) {
+          unsigned t[U][VEC];
+          vm_fetch<VEC, U>(op, op.a, R, acc, t);
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[u][v] = t[u][v];
+        }
+        red(op, acc);
+        if (op.dst >= 0) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) R.put(op.dst, u, acc[u]);
         }
         break;
       case TSB_OP_CONST:
