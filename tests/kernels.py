@@ -505,3 +505,14 @@ def pad_scale_kernel(x_ptr, b_ptr, out_ptr, n_cols, out_stride, BLOCK: tl.conste
     x = tl.load(x_ptr + row * n_cols + cols, mask=m, other=3)
     b = tl.load(b_ptr + cols, mask=m, other=3)
     tl.store(out_ptr + row * out_stride + cols, x * 2 + b)
+
+
+@triton.jit
+def row_center_kernel(x_ptr, y_ptr, stride, n_cols, BLOCK: tl.constexpr):
+    """y = x - max(x) + sum(x) per row: two full folds of the one block the kernel stores."""
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK)
+    m = cols < n_cols
+    x = tl.load(x_ptr + row * stride + cols, mask=m, other=0)
+    y = x - tl.max(x, axis=0) + tl.sum(x, axis=0)
+    tl.store(y_ptr + row * stride + cols, y, mask=m)

@@ -499,6 +499,21 @@ def test_padded_scale_2d_on_host_stand_in(dtype, n_cols):
     assert torch.all(out[rows] == 99)
 
 
+@pytest.mark.parametrize("block", [16, 128])
+def test_row_folds_on_host_stand_in(block):
+    """Full folds of the stored block lower to the elementwise family (TSB_OP_REDUCE)."""
+    rows, n_cols = 5, block - 3
+    x = torch.randint(-50, 1000, (rows, block), generator=torch.Generator().manual_seed(block), dtype=torch.int32)
+    y = torch.full_like(x, -7)
+    with fake_device() as lib:
+        K.row_center_kernel[(rows,)](x, y, block, n_cols, BLOCK=block)
+    assert [c[0] for c in lib.calls] == ["tsb_elementwise"]
+    xv = x[:, :n_cols].long()
+    exp = xv - torch.clamp(xv.max(dim=1, keepdim=True).values, min=0) + xv.sum(dim=1, keepdim=True)
+    assert torch.equal(y[:, :n_cols].long(), exp)
+    assert torch.all(y[:, n_cols:] == -7)
+
+
 def test_launch_hooks_are_called():
     """launch_enter_hook / launch_exit_hook around every launch, as the reference launcher does
     (backend/driver.py:197-218 there)."""

@@ -451,3 +451,30 @@ def test_bias_add_beyond_32bit_offsets(drv):
     total = out.double().sum().item()
     want = sum(2.0 * (r % 64) for r in range(rows)) * cols + rows * float((torch.arange(cols) % 32).sum())
     assert total == want
+
+
+@pytest.mark.parametrize("block", [16, 64, 128, 512, 1024, 4096])
+@pytest.mark.parametrize("dtype", [torch.int32, torch.float32], ids=["i32", "f32"])
+def test_row_folds_on_the_elementwise_engine(drv, dtype, block):
+    """x - max(x) + sum(x) per row for every size of thread group a program can have in the packed
+    kernel (1 thread to the whole CTA), ragged rows (masked lanes take part with the fill value 0, as in
+    the kernel text).  Integers exactly; floats against a float64 fold (rel 1e-5: the fold order differs)."""
+    rows, n_cols = 53, block - 3
+    g = torch.Generator().manual_seed(block)
+    if dtype == torch.int32:
+        x = torch.randint(-50, 1000, (rows, block), generator=g, dtype=torch.int32)
+    else:
+        x = torch.rand(rows, block, generator=g) + 0.5
+    xd = x.cuda()
+    y = torch.full_like(xd, -7)
+    K.row_center_kernel[(rows,)](xd, y, block, n_cols, BLOCK=block)
+    torch.cuda.synchronize()
+    xv = x[:, :n_cols].double()
+    mx = torch.clamp(xv.max(dim=1, keepdim=True).values, min=0.0)  # the masked lanes hold 0
+    exp = xv - mx + xv.sum(dim=1, keepdim=True)
+    got = y[:, :n_cols].cpu().double()
+    if dtype == torch.int32:
+        assert torch.equal(got, exp)
+    else:
+        assert torch.allclose(got, exp, rtol=1e-5, atol=0)
+    assert torch.all(y[:, n_cols:] == -7), "stored beyond the mask"
