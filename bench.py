@@ -463,7 +463,7 @@ def main():
     # ------------------------------------------------------------------ secondary workloads
     # the five configured workloads, the block copy, and three kernels that run on the general engines
     # (elementwise VM, block programs, device-side loops) rather than on dedicated kernels
-    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy", "gelu_bias", "rmsnorm", "wrap_rows",
+    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy", "gelu_bias", "rmsnorm", "row_stats", "wrap_rows",
              "gather_rows"}
     chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names}
     if chosen:
@@ -663,7 +663,7 @@ def main():
             record("gelu_bias", step, 4 * R * C + 2 * C, 1e9, "hbm", "GB/s")
 
         def wl_rmsnorm():
-            # block-program kernel (reduction in the body, values in shared memory), fp16 16,384 x 4,096
+            # a full fold inside the body (elementwise VM with a per-program fold), fp16 16,384 x 4,096
             R, C = (4096, 4096) if args.small else (16384, 4096)
             x = torch.randn(R, C, device="cuda").half()
             w = (torch.rand(C, device="cuda") + 0.5).half()
@@ -672,6 +672,20 @@ def main():
             def step():
                 K.rmsnorm_kernel[(R,)](x, w, y, C, C, 1e-6, BLOCK=4096)
             record("rmsnorm", step, 4 * R * C + 2 * C, 1e9, "hbm", "GB/s")
+
+        def wl_row_stats():
+            # block-program kernel (loop-carried block accumulators, folds to scalars), fp32 16,384 x 4,096
+            R, C = (4096, 4096) if args.small else (16384, 4096)
+            x = torch.randn(R, C, device="cuda")
+            sums = torch.empty(R, device="cuda")
+            maxs = torch.empty(R, device="cuda")
+
+            def step():
+                K.row_stats_kernel[(R,)](x, sums, maxs, C, C, BLOCK=1024)
+            record("row_stats", step, 4 * R * C + 8 * R, 1e9, "hbm", "GB/s")
+            if "value" in wl["row_stats"]:
+                wl["row_stats"]["result_check"] = bool(torch.equal(maxs, x.max(dim=1).values) and
+                                                       torch.allclose(sums.double(), x.double().sum(dim=1), rtol=1e-5, atol=1e-3))
 
         def wl_wrap_rows():
             # wrap-around row gather copy: 64 programs' worth in one program is tiny, so use many column steps
@@ -714,7 +728,7 @@ def main():
 
         for name, fn in (("vec_add", wl_vec_add), ("layernorm", wl_layernorm),
                          ("strided_reduce", wl_strided_reduce), ("matmul", wl_matmul),
-                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("wrap_rows", wl_wrap_rows), ("gather_rows", wl_gather_rows),
+                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("row_stats", wl_row_stats), ("wrap_rows", wl_wrap_rows), ("gather_rows", wl_gather_rows),
                          ("block_copy", wl_block_copy)):
             if name in chosen:
                 fn()
