@@ -156,7 +156,9 @@ enum tsb_opcode {
   TSB_OP_CAST = 90,
   TSB_OP_BITCAST = 91,
   TSB_OP_FMA = 92, /* math.fma: single rounding */
-  TSB_OP_REDUCE = 100, /* tsb_block_program only: dst <- fold of reg a along dim imm2 with combiner opcode imm */
+  TSB_OP_REDUCE = 100, /* tsb_block_program: dst <- fold of reg a along dim imm2 with combiner opcode imm;
+                          tsb_elementwise: every lane of dst <- fold of reg a over all lanes of the program
+                          with combiner opcode imm (blocks of 16 to 4096 lanes, a multiple of 4) */
   TSB_OP_LOOP_BEGIN = 101, /* loop slot a runs imm iterations; tsb_block_program: b = index of the op after its LOOP_END */
   TSB_OP_LOOP_END = 102,   /* closes loop slot a */
   TSB_OP_ARGREDUCE = 103,  /* tsb_block_program only: (dst, c) <- (value, index) of the largest (imm = 1) or smallest

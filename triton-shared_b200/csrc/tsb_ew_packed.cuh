@@ -71,7 +71,7 @@ __device__ __forceinline__ void fold_group(unsigned (&v)[U][4], int ty, int G, i
 // registers per thread) measured slower than U = 4 on every body tried: the halved warp count
 // costs more than the shared decode saves.
 template <bool LOOPS, int MODE, int U>
-__global__ void __launch_bounds__(1024 / U, MODE == PACKED_LEAN ? 3 : 4)
+__global__ void __launch_bounds__(1024 / U, 3)
     ew_vm_packed_kernel(const __grid_constant__ EwParams P, int lg_g, int per_pass, int rounds) {
   constexpr int VEC = 4;
   extern __shared__ __align__(16) unsigned vm_smem[];
