@@ -682,6 +682,10 @@ class ElementwisePlan(Plan):
                 raise UnsupportedTTIR(f"blocks of rank {rank} (max {rt.TSB_MAX_RANK})")
             low = _EwLowering(kernel, an, space)
             ops = low.lower(stores)
+            if any(o[0] == "reduce" for o in ops) and any(tuple(s.shape) != tuple(full) for s in stores):
+                # a scalar result stored beside the block (mean / rstd of a one-block LayerNorm) would be
+                # written by every lane: leave such bodies to the block-program engine
+                raise UnsupportedTTIR("elementwise family: a fold whose result is also stored as a scalar")
             segments.append({"space": list(space), "accs": low.accs, "ops": ops})
             stored_args.update(s.arg for s in stores)
             return len(segments) - 1
