@@ -463,7 +463,7 @@ def main():
     # ------------------------------------------------------------------ secondary workloads
     # the five configured workloads, the block copy, and three kernels that run on the general engines
     # (elementwise VM, block programs, device-side loops) rather than on dedicated kernels
-    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy", "gelu_bias", "rmsnorm", "row_stats", "wrap_rows",
+    names = {"vec_add", "layernorm", "strided_reduce", "matmul", "block_copy", "gelu_bias", "bias_chain", "rmsnorm", "row_stats", "wrap_rows",
              "gather_rows"}
     chosen = names if args.workload == "all" else {w for w in args.workload.split(",") if w in names}
     if chosen:
@@ -662,6 +662,22 @@ def main():
                 K.gelu_bias_kernel[(R, C // 1024)](x, b, o, C, BLOCK=1024)
             record("gelu_bias", step, 4 * R * C + 2 * C, 1e9, "hbm", "GB/s")
 
+        def wl_bias_chain():
+            # 5-op fp32 body with a row-broadcast operand on a 2-D grid (elementwise VM, lean accessors), 8,192 x 8,192
+            R, C = (4096, 8192) if args.small else (8192, 8192)
+            x = torch.randn(R, C, device="cuda")
+            b = torch.randn(C, device="cuda")
+            o = torch.empty_like(x)
+
+            def step():
+                K.bias_chain_kernel[(R, C // 1024)](x, b, o, C, NIT=2, BLOCK=1024)
+            record("bias_chain", step, 8 * R * C + 4 * C, 1e9, "hbm", "GB/s")
+            if "value" in wl["bias_chain"]:
+                v = x[:64] + b
+                for _ in range(2):
+                    v = v * 1.0001 + b
+                wl["bias_chain"]["result_check"] = bool(torch.equal(o[:64], v))
+
         def wl_rmsnorm():
             # a full fold inside the body (elementwise VM with a per-program fold), fp16 16,384 x 4,096
             R, C = (4096, 4096) if args.small else (16384, 4096)
@@ -728,7 +744,7 @@ def main():
 
         for name, fn in (("vec_add", wl_vec_add), ("layernorm", wl_layernorm),
                          ("strided_reduce", wl_strided_reduce), ("matmul", wl_matmul),
-                         ("gelu_bias", wl_gelu_bias), ("rmsnorm", wl_rmsnorm), ("row_stats", wl_row_stats), ("wrap_rows", wl_wrap_rows), ("gather_rows", wl_gather_rows),
+                         ("gelu_bias", wl_gelu_bias), ("bias_chain", wl_bias_chain), ("rmsnorm", wl_rmsnorm), ("row_stats", wl_row_stats), ("wrap_rows", wl_wrap_rows), ("gather_rows", wl_gather_rows),
                          ("block_copy", wl_block_copy)):
             if name in chosen:
                 fn()

@@ -516,3 +516,18 @@ def row_center_kernel(x_ptr, y_ptr, stride, n_cols, BLOCK: tl.constexpr):
     x = tl.load(x_ptr + row * stride + cols, mask=m, other=0)
     y = x - tl.max(x, axis=0) + tl.sum(x, axis=0)
     tl.store(y_ptr + row * stride + cols, y, mask=m)
+
+
+@triton.jit
+def bias_chain_kernel(x_ptr, b_ptr, o_ptr, C, NIT: tl.constexpr, BLOCK: tl.constexpr):
+    """(x + b) followed by NIT times (v * 1.0001 + b) over a (row, column block) grid: an elementwise
+    body of 1 + 2 * NIT ops whose length is a parameter."""
+    row = tl.program_id(0)
+    cols = tl.program_id(1) * BLOCK + tl.arange(0, BLOCK)
+    m = cols < C
+    x = tl.load(x_ptr + row * C + cols, mask=m).to(tl.float32)
+    b = tl.load(b_ptr + cols, mask=m).to(tl.float32)
+    v = x + b
+    for i in tl.static_range(NIT):
+        v = v * 1.0001 + b
+    tl.store(o_ptr + row * C + cols, v.to(o_ptr.dtype.element_ty), mask=m)
